@@ -1,0 +1,61 @@
+// Internal (non-exported) declarations shared by the .cu translation units.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+constexpr int kBM = 128;       // output tile rows (UMMA M, one TMEM lane per row)
+constexpr int kBK = 128;       // int8 elements per k-block = one 128-byte swizzle row
+constexpr int kMaxSeg = 8;     // operand-plane pairs accumulated into one tile
+constexpr int kChunkK = 1008;  // modulus-256 extraction interval of the reference
+constexpr int kChunkSeg = 1024;         // a chunk's segment, padded to whole k-blocks
+constexpr int kChunkExt = 3 * kChunkSeg;  // three segments per chunk (see split kernels)
+
+enum GemmEpilogue : int {
+  kEpiModI8 = 0,     // centred residue mod an odd modulus -> int8 plane
+  kEpiRawI32 = 1,    // raw int32 accumulator -> int32 plane
+  kEpiMod256 = 2,    // per-chunk reduction mod 256 with the reference's tie rule -> int16 plane
+};
+
+// One accumulation: sum over segments of A_plane[seg] * B_plane[seg]^T.
+struct GemmJob {
+  int n_seg;
+  int a_plane[kMaxSeg];
+  int b_plane[kMaxSeg];
+  int out_plane;
+  unsigned modulus;  // kEpiModI8 only
+  unsigned magic;    // floor(2^32 / modulus)
+  unsigned offset;   // multiple of modulus, >= the largest |accumulator|
+};
+
+struct GemmParams {
+  int tiles_m, tiles_n, n_jobs;
+  int kb_per_seg;    // k-blocks in one segment
+  int kb_per_unit;   // k-blocks per accumulator hand-off (whole job unless chunked)
+  int group_m;       // m-tiles per raster group
+  const GemmJob* jobs;
+  uint8_t* out;
+  long long out_plane_stride;  // bytes
+  int ldo;                     // elements per output row
+  int* status;
+};
+
+// Launchers (b200_modgemm.cu).  bn is 128 or 256.
+cudaError_t launch_modgemm(int bn, int epi, const CUtensorMap& tmA, const CUtensorMap& tmB,
+                           const GemmParams& prm, int total_work, int num_sms,
+                           cudaStream_t stream);
+cudaError_t modgemm_set_attributes();
+
+// Plain CUDA-core version of the same job table, used by tests to localise a
+// fault to the tensor-core kernel; never on the product path.
+struct SimtPlanes {
+  const int8_t* a_base; long long a_plane_stride; int lda;
+  const int8_t* b_base; long long b_plane_stride; int ldb;
+  int M, N;
+};
+cudaError_t launch_modgemm_simt(int epi, const SimtPlanes& pl, const GemmParams& prm,
+                                cudaStream_t stream);
+
+}  // namespace b200

@@ -1,0 +1,398 @@
+// Bandwidth-bound stages of the Ozaki-II exact f64 GEMM:
+//   scan      per-row max|A|, per-column max|B|
+//   scales    mu_i = E - floor(log2 amax_i), nu_j likewise, and the 2^(+/-mu) factors
+//   split     trunc(a * 2^mu) -> centred residues for every modulus, int8 planes
+//             (A planes row-major M x Kp, B planes TRANSPOSED to N x Kp so both GEMM
+//             operands are K-major), 128-bit loads, whole-word / 16-byte stores
+//   crt       S1/S2 accumulation over the residue planes of the products, Q, the two
+//             fma's of the reconstruction and the two exact descalings -> f64 C
+//
+// Arithmetic restated from the reference's host code, lib/backend/gpu/gpu_memory.mm:
+// scales :2514-2532, integerisation :2538-2547, residues :2573-2583, CRT accumulation
+// :2619-2641, reconstruction :2644-2655 (see the notes on each kernel).
+#include "b200_common.cuh"
+#include "b200_internal.h"
+#include "b200_ozaki2.h"
+#include "b200_residue.cuh"
+
+#include <math.h>
+
+namespace b200 {
+
+namespace {
+
+__device__ __forceinline__ double dmax_ref(double mx, double v) {
+  // the reference's update "if (v > mx) mx = v": a NaN never replaces the maximum
+  return (v > mx) ? v : mx;
+}
+
+// ------------------------------------------------------------------- row scan
+// One warp per row of A.
+__global__ void __launch_bounds__(256) scan_rows_kernel(const double* __restrict__ A, long long M,
+                                                        long long K, double* __restrict__ amax) {
+  const long long row = static_cast<long long>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  const double* p = A + row * K;
+  double mx = 0.0;
+  const long long head = ((reinterpret_cast<uintptr_t>(p) & 8) && K > 0) ? 1 : 0;
+  if (lane == 0 && head) mx = dmax_ref(mx, fabs(p[0]));
+  const long long npair = (K - head) >> 1;
+  const double2* p2 = reinterpret_cast<const double2*>(p + head);
+  long long i = lane;
+  for (; i + 96 < npair; i += 128) {  // four independent 16-byte loads in flight
+    const double2 v0 = __ldg(p2 + i), v1 = __ldg(p2 + i + 32), v2 = __ldg(p2 + i + 64),
+                  v3 = __ldg(p2 + i + 96);
+    mx = dmax_ref(mx, fabs(v0.x)); mx = dmax_ref(mx, fabs(v0.y));
+    mx = dmax_ref(mx, fabs(v1.x)); mx = dmax_ref(mx, fabs(v1.y));
+    mx = dmax_ref(mx, fabs(v2.x)); mx = dmax_ref(mx, fabs(v2.y));
+    mx = dmax_ref(mx, fabs(v3.x)); mx = dmax_ref(mx, fabs(v3.y));
+  }
+  for (; i < npair; i += 32) {
+    const double2 v = __ldg(p2 + i);
+    mx = dmax_ref(mx, fabs(v.x)); mx = dmax_ref(mx, fabs(v.y));
+  }
+  if (lane == 0 && ((K - head) & 1)) mx = dmax_ref(mx, fabs(p[K - 1]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = dmax_ref(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if (lane == 0) amax[row] = mx;
+}
+
+// ---------------------------------------------------------------- column scan
+// Block = 64 columns x 4 row phases over a slab of rows; partial maxima merge
+// through atomicMax on the bit pattern (order-preserving for non-negative doubles).
+constexpr int kColSlab = 256;
+__global__ void __launch_bounds__(256) scan_cols_kernel(const double* __restrict__ B, long long K,
+                                                        long long N,
+                                                        unsigned long long* __restrict__ bmax_bits) {
+  __shared__ double red[4][64];
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const long long j = static_cast<long long>(blockIdx.x) * 64 + tx;
+  const long long k0 = static_cast<long long>(blockIdx.y) * kColSlab;
+  const long long k1 = (k0 + kColSlab < K) ? k0 + kColSlab : K;
+  double mx = 0.0;
+  if (j < N) {
+    long long k = k0 + ty;
+    for (; k + 12 < k1; k += 16) {
+      const double v0 = __ldg(B + k * N + j), v1 = __ldg(B + (k + 4) * N + j),
+                   v2 = __ldg(B + (k + 8) * N + j), v3 = __ldg(B + (k + 12) * N + j);
+      mx = dmax_ref(mx, fabs(v0)); mx = dmax_ref(mx, fabs(v1));
+      mx = dmax_ref(mx, fabs(v2)); mx = dmax_ref(mx, fabs(v3));
+    }
+    for (; k < k1; k += 4) mx = dmax_ref(mx, fabs(__ldg(B + k * N + j)));
+  }
+  red[ty][tx] = mx;
+  __syncthreads();
+  if (ty == 0 && j < N) {
+    mx = dmax_ref(mx, red[1][tx]);
+    mx = dmax_ref(mx, red[2][tx]);
+    mx = dmax_ref(mx, red[3][tx]);
+    if (mx > 0.0) atomicMax(bmax_bits + j, static_cast<unsigned long long>(__double_as_longlong(mx)));
+  }
+}
+
+// floor(log2(x)) for finite x > 0 as a correctly rounded log2 followed by floor
+// returns it (the reference calls libm): equal to the exponent field except for
+// the few largest doubles below 2^t with |t| >= 3, whose logarithm rounds to t.
+__device__ int floor_log2_ref(double x) {
+  const unsigned long long bits = static_cast<unsigned long long>(__double_as_longlong(x));
+  const int ef = static_cast<int>((bits >> 52) & 0x7ff);
+  const unsigned long long man = bits & ((1ull << 52) - 1);
+  int e;
+  unsigned long long sig;
+  if (ef == 0) {
+    if (man == 0) return 0;
+    const int lz = __clzll(static_cast<long long>(man)) - 11;
+    sig = man << lz;
+    e = -1022 - lz;
+  } else {
+    sig = man | (1ull << 52);
+    e = ef - 1023;
+  }
+  const unsigned long long m = (1ull << 53) - sig;
+  const int t = e + 1;
+  if (t == 0 || m > 2048ull) return e;
+  const int a = t < 0 ? -t : t;
+  const int lg = 31 - __clz(a);
+  const bool pow2 = (a & (a - 1)) == 0;
+  const double thr = (t > 0 && pow2) ? ldexp(1.0, lg - 1) : ldexp(1.0, lg);
+  return (static_cast<double>(m) * 1.4426950408889634 < thr) ? t : e;
+}
+
+// gpu_memory.mm:2523/2531: shift = (max == 0) ? 0 : E - floor(log2(max))
+__global__ void scales_kernel(const double* __restrict__ vmax, long long n, int E,
+                              int* __restrict__ shift, double* __restrict__ scale,
+                              double* __restrict__ inv_scale) {
+  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const double mx = vmax[i];
+  const int s = (mx == 0.0) ? 0 : E - floor_log2_ref(mx);
+  shift[i] = s;
+  scale[i] = ldexp(1.0, s);
+  inv_scale[i] = ldexp(1.0, -s);
+}
+
+struct SplitGeom {
+  long long rows;      // M for A, N for B
+  long long K, Kp;     // logical and padded (multiple of 128) inner extent
+  long long K0;        // inner extent of the modulus-256 plane (three segments per chunk)
+  int n_chunks;        // ceil(K / 1008)
+  int last_seg;        // segment length of the last chunk, a multiple of 128
+  int n_odd;           // number of odd-modulus planes (n_mod - 1)
+  int8_t* plane0;      // rows x K0
+  int8_t* odd;         // n_odd planes of rows x Kp
+  long long odd_stride;
+};
+
+// column of element k of the first segment inside the modulus-256 plane
+__device__ __forceinline__ void ext_cols(const SplitGeom& g, long long k, long long* c0, int* seglen) {
+  const int c = static_cast<int>(k / kChunkK);
+  const int off = static_cast<int>(k - static_cast<long long>(c) * kChunkK);
+  *seglen = (c == g.n_chunks - 1) ? g.last_seg : kChunkSeg;
+  *c0 = static_cast<long long>(c) * kChunkExt + off;
+}
+
+// A: one thread per 4 consecutive k of one row.  grid = (rows, ceil(Kp/1024)).
+__global__ void __launch_bounds__(256) split_a_kernel(const double* __restrict__ A,
+                                                      const double* __restrict__ scale,
+                                                      const SplitGeom g,
+                                                      const __grid_constant__ Oz2DeviceConsts c) {
+  const long long row = blockIdx.x;
+  const long long k4 = (static_cast<long long>(blockIdx.y) * 256 + threadIdx.x) * 4;
+  if (k4 >= g.Kp) return;
+  const double* src = A + row * g.K + k4;
+  double a[4];
+  if (k4 + 3 < g.K && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const double2 v0 = __ldg(reinterpret_cast<const double2*>(src));
+    const double2 v1 = __ldg(reinterpret_cast<const double2*>(src) + 1);
+    a[0] = v0.x; a[1] = v0.y; a[2] = v1.x; a[3] = v1.y;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) a[e] = (k4 + e < g.K) ? __ldg(src + e) : 0.0;
+  }
+  const double s = scale[row];
+  double x[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) x[e] = trunc(a[e] * s);  // gpu_memory.mm:2541
+
+  const long long o = row * g.Kp + k4;
+  for (int l = 0; l < g.n_odd; ++l) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      word |= (static_cast<uint32_t>(residue_odd(x[e], c.p_d[l + 1], c.p_inv[l + 1], c.p_i[l + 1])) & 0xffu) << (8 * e);
+    *reinterpret_cast<uint32_t*>(g.odd + l * g.odd_stride + o) = word;
+  }
+  if (k4 < g.K) {
+    uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const Res256 r = residue_256(x[e]);
+      w0 |= r.lo8 << (8 * e);
+      w1 |= r.hi << (8 * e);   // pairs with B's odd flags
+      w2 |= r.odd << (8 * e);  // pairs with B's +128 flags
+    }
+    long long c0; int seglen;
+    ext_cols(g, k4, &c0, &seglen);
+    int8_t* dst = g.plane0 + row * g.K0 + c0;
+    *reinterpret_cast<uint32_t*>(dst) = w0;
+    *reinterpret_cast<uint32_t*>(dst + seglen) = w1;
+    *reinterpret_cast<uint32_t*>(dst + 2 * seglen) = w2;
+  }
+}
+
+// B (K x N row-major) -> planes N x Kp.  Block = 32 columns x 128 k; loads are
+// coalesced along j, residues are packed 4-per-word along k into shared memory
+// (row pitch 33 words: conflict-free both ways), then written out as 16-byte
+// vectors along k.
+constexpr int kSplitBJ = 32, kSplitBK = 128, kSplitBPitch = 33;
+__global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__ B,
+                                                      const double* __restrict__ scale,
+                                                      long long N, const SplitGeom g,
+                                                      const __grid_constant__ Oz2DeviceConsts c) {
+  extern __shared__ uint32_t sm[];  // [n_odd + 3][32][33]
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long long j = static_cast<long long>(blockIdx.x) * kSplitBJ + tx;
+  const long long kbase = static_cast<long long>(blockIdx.y) * kSplitBK;
+  const double s = (j < N) ? scale[j] : 0.0;
+  const int n_planes = g.n_odd + 3;
+#pragma unroll 1
+  for (int qd = ty; qd < kSplitBK / 4; qd += 8) {
+    const long long k = kbase + qd * 4;
+    double x[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const double b = (j < N && k + e < g.K) ? __ldg(B + (k + e) * N + j) : 0.0;
+      x[e] = trunc(b * s);  // gpu_memory.mm:2546
+    }
+    uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const Res256 r = residue_256(x[e]);
+      w0 |= r.lo8 << (8 * e);
+      w1 |= r.odd << (8 * e);  // pairs with A's +128 flags
+      w2 |= r.hi << (8 * e);   // pairs with A's odd flags
+    }
+    sm[(0 * kSplitBJ + tx) * kSplitBPitch + qd] = w0;
+    sm[(1 * kSplitBJ + tx) * kSplitBPitch + qd] = w1;
+    sm[(2 * kSplitBJ + tx) * kSplitBPitch + qd] = w2;
+    for (int l = 0; l < g.n_odd; ++l) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        word |= (static_cast<uint32_t>(residue_odd(x[e], c.p_d[l + 1], c.p_inv[l + 1], c.p_i[l + 1])) & 0xffu) << (8 * e);
+      sm[((3 + l) * kSplitBJ + tx) * kSplitBPitch + qd] = word;
+    }
+  }
+  __syncthreads();
+  // write-out: thread = (column jj, 16-byte group gq of the 128-k tile)
+  const int jj = threadIdx.x >> 3, gq = threadIdx.x & 7;
+  const long long jo = static_cast<long long>(blockIdx.x) * kSplitBJ + jj;
+  if (jo >= N) return;
+  const long long k16 = kbase + gq * 16;
+  for (int pl = 0; pl < n_planes; ++pl) {
+    const uint32_t* srcw = &sm[(pl * kSplitBJ + jj) * kSplitBPitch + gq * 4];
+    const uint4 v = make_uint4(srcw[0], srcw[1], srcw[2], srcw[3]);
+    if (pl >= 3) {
+      if (k16 < g.Kp)
+        *reinterpret_cast<uint4*>(g.odd + (pl - 3) * g.odd_stride + jo * g.Kp + k16) = v;
+    } else if (k16 < g.K) {
+      long long c0; int seglen;
+      ext_cols(g, k16, &c0, &seglen);
+      *reinterpret_cast<uint4*>(g.plane0 + jo * g.K0 + c0 + static_cast<long long>(pl) * seglen) = v;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------ CRT
+// One thread per 4 consecutive columns of one row.  grid = (M, ceil(N/1024)).
+// gpu_memory.mm:2632-2640 (S1/S2 in modulus order, fused) and :2650-2653.
+__global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
+                                                  const __grid_constant__ Oz2DeviceConsts c) {
+  const long long i = blockIdx.x;
+  const long long j4 = (static_cast<long long>(blockIdx.y) * 256 + threadIdx.x) * 4;
+  if (j4 >= a.N) return;
+  const long long wo = i * a.ldw + j4;
+  double S1[4] = {0.0, 0.0, 0.0, 0.0}, S2[4] = {0.0, 0.0, 0.0, 0.0};
+  {
+    const uint2 w = __ldg(reinterpret_cast<const uint2*>(a.w0 + wo));
+    const int v[4] = {static_cast<int16_t>(w.x & 0xffffu), static_cast<int16_t>(w.x >> 16),
+                      static_cast<int16_t>(w.y & 0xffffu), static_cast<int16_t>(w.y >> 16)};
+    const double s1 = c.sl1[0], s2 = c.sl2[0];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const double wd = static_cast<double>(v[e]);
+      S1[e] = fma(s1, wd, S1[e]);
+      S2[e] = fma(s2, wd, S2[e]);
+    }
+  }
+  for (int l = 1; l < a.n_mod; ++l) {
+    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(a.w_odd + (l - 1) * a.w_odd_stride + wo));
+    const double s1 = c.sl1[l], s2 = c.sl2[l];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const double wd = static_cast<double>(static_cast<int8_t>((w >> (8 * e)) & 0xffu));
+      S1[e] = fma(s1, wd, S1[e]);
+      S2[e] = fma(s2, wd, S2[e]);
+    }
+  }
+  const double mu_inv = a.inv_scale_a[i];
+  const double P1 = c.P1, P2 = c.P2, Pinv = c.Pinv;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const long long j = j4 + e;
+    if (j >= a.N) break;
+    const double s = __dadd_rn(S1[e], S2[e]);
+    const double Q = round(__dmul_rn(s, Pinv));  // half away from zero, as round()
+    const double c1 = fma(-P1, Q, S1[e]);
+    const double c2 = fma(-P2, Q, S2[e]);
+    double c = __dmul_rn(__dmul_rn(__dadd_rn(c1, c2), mu_inv), a.inv_scale_b[j]);
+    if (a.bias_mode == 1) c = __dadd_rn(c, a.bias[i]);
+    else if (a.bias_mode == 2) c = __dadd_rn(c, a.bias[j]);
+    if (a.activation == 1) c = (c > 0.0) ? c : 0.0;  // gpu_cuda_kernels.cu:37
+    long long o;
+    if (a.pixels_per_image > 0) {
+      const long long img = j / a.pixels_per_image, pix = j - img * a.pixels_per_image;
+      o = (img * a.M + i) * a.pixels_per_image + pix;  // [image][row][pixel]
+    } else {
+      o = i * a.ldc + j;
+    }
+    a.C[o] = c;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_scan_rows(const double* A, long long M, long long K, double* amax,
+                             cudaStream_t st) {
+  if (M <= 0) return cudaSuccess;
+  scan_rows_kernel<<<static_cast<unsigned>((M + 7) / 8), 256, 0, st>>>(A, M, K, amax);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scan_cols(const double* B, long long K, long long N,
+                             unsigned long long* bmax_bits, cudaStream_t st) {
+  if (N <= 0 || K <= 0) return cudaSuccess;
+  cudaError_t e = cudaMemsetAsync(bmax_bits, 0, static_cast<size_t>(N) * 8, st);
+  if (e != cudaSuccess) return e;
+  const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((K + kColSlab - 1) / kColSlab));
+  if (grid.y > 65535u) return cudaErrorInvalidValue;
+  scan_cols_kernel<<<grid, 256, 0, st>>>(B, K, N, bmax_bits);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scales(const double* vmax, long long n, int E, int* shift, double* scale,
+                          double* inv_scale, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  scales_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, st>>>(vmax, n, E, shift, scale,
+                                                                        inv_scale);
+  return cudaGetLastError();
+}
+
+static SplitGeom make_geom(const SplitPlanes& p) {
+  SplitGeom g;
+  g.rows = p.rows; g.K = p.K; g.Kp = p.Kp; g.K0 = p.K0;
+  g.n_chunks = p.n_chunks; g.last_seg = p.last_seg; g.n_odd = p.n_odd;
+  g.plane0 = p.plane0; g.odd = p.odd; g.odd_stride = p.odd_stride;
+  return g;
+}
+
+cudaError_t launch_split_a(const double* A, const double* scale, const SplitPlanes& p,
+                           const Oz2DeviceConsts& c, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(p.plane0, 0, static_cast<size_t>(p.rows) * p.K0, st);
+  if (e != cudaSuccess) return e;
+  const dim3 grid(static_cast<unsigned>(p.rows), static_cast<unsigned>((p.Kp + 1023) / 1024));
+  if (grid.y > 65535u) return cudaErrorInvalidValue;
+  split_a_kernel<<<grid, 256, 0, st>>>(A, scale, make_geom(p), c);
+  return cudaGetLastError();
+}
+
+size_t split_b_smem_bytes(int n_odd) {
+  return static_cast<size_t>(n_odd + 3) * kSplitBJ * kSplitBPitch * sizeof(uint32_t);
+}
+
+cudaError_t split_set_attributes() {
+  return cudaFuncSetAttribute(split_b_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              static_cast<int>(split_b_smem_bytes(15)));
+}
+
+cudaError_t launch_split_b(const double* B, const double* scale, long long N, const SplitPlanes& p,
+                           const Oz2DeviceConsts& c, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(p.plane0, 0, static_cast<size_t>(p.rows) * p.K0, st);
+  if (e != cudaSuccess) return e;
+  const dim3 grid(static_cast<unsigned>((N + kSplitBJ - 1) / kSplitBJ),
+                  static_cast<unsigned>(p.Kp / kSplitBK));
+  if (grid.y > 65535u) return cudaErrorInvalidValue;
+  split_b_kernel<<<grid, 256, split_b_smem_bytes(p.n_odd), st>>>(B, scale, N, make_geom(p), c);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_crt(const CrtArgs& a, const Oz2DeviceConsts& c, cudaStream_t st) {
+  if (a.M <= 0 || a.N <= 0) return cudaSuccess;
+  const dim3 grid(static_cast<unsigned>(a.M), static_cast<unsigned>((a.N + 1023) / 1024));
+  if (grid.y > 65535u) return cudaErrorInvalidValue;
+  crt_kernel<<<grid, 256, 0, st>>>(a, c);
+  return cudaGetLastError();
+}
+
+}  // namespace b200

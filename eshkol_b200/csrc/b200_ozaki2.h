@@ -1,0 +1,56 @@
+// Host-visible declarations of the scan / split / CRT stages (b200_ozaki2.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200 {
+
+struct Oz2DeviceConsts {
+  double P1, P2, Pinv;
+  double sl1[16], sl2[16];
+  double p_d[16], p_inv[16];
+  int p_i[16];
+  int q_i[16];  // (P/p_l)^-1 mod p_l
+  int n_mod;
+};
+
+// Residue planes of one operand.
+struct SplitPlanes {
+  long long rows;       // M (A) or N (B)
+  long long K, Kp, K0;  // logical, padded-to-128, and modulus-256-plane inner extents
+  int n_chunks, last_seg, n_odd;
+  int8_t* plane0;       // rows x K0
+  int8_t* odd;          // n_odd planes, each rows x Kp
+  long long odd_stride; // bytes between odd planes
+};
+
+struct CrtArgs {
+  const int16_t* w0;     // modulus-256 residues of the products, M_pad x ldw
+  const int8_t* w_odd;   // odd-modulus residues, (n_mod-1) planes of M_pad x ldw
+  long long w_odd_stride;
+  long long ldw;
+  int n_mod;
+  long long M, N;
+  const double* inv_scale_a;  // 2^-mu_i
+  const double* inv_scale_b;  // 2^-nu_j
+  double* C;
+  long long ldc;
+  int bias_mode;              // 0 none, 1 per row, 2 per column
+  const double* bias;
+  int activation;             // 0 none, 1 ReLU
+  long long pixels_per_image; // > 0: scatter columns to [image][row][pixel] (conv2d NCHW)
+};
+
+cudaError_t launch_scan_rows(const double* A, long long M, long long K, double* amax, cudaStream_t st);
+cudaError_t launch_scan_cols(const double* B, long long K, long long N,
+                             unsigned long long* bmax_bits, cudaStream_t st);
+cudaError_t launch_scales(const double* vmax, long long n, int E, int* shift, double* scale,
+                          double* inv_scale, cudaStream_t st);
+cudaError_t launch_split_a(const double* A, const double* scale, const SplitPlanes& p,
+                           const Oz2DeviceConsts& c, cudaStream_t st);
+cudaError_t launch_split_b(const double* B, const double* scale, long long N, const SplitPlanes& p,
+                           const Oz2DeviceConsts& c, cudaStream_t st);
+cudaError_t split_set_attributes();
+cudaError_t launch_crt(const CrtArgs& a, const Oz2DeviceConsts& c, cudaStream_t st);
+
+}  // namespace b200

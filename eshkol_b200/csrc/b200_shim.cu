@@ -1,0 +1,548 @@
+// Device-level C ABI (include/eshkol_b200_ext.h): stream and workspace ownership,
+// TMA tensor maps, and the drivers that chain scan -> split -> tensor-core
+// products -> reconstruction for each precision tier.
+#include "../../include/eshkol_b200_ext.h"
+
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <cuda_runtime.h>
+#include <math.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
+#include <vector>
+
+#include "b200_internal.h"
+#include "b200_ozaki2.h"
+#include "b200_tiers.h"
+
+namespace b200 {
+
+// ---------------------------------------------------------------- global state
+struct State {
+  bool ready = false;
+  int device = -1;
+  int num_sms = 0;
+  cudaStream_t stream = nullptr;
+  uint8_t* ws = nullptr;
+  size_t ws_bytes = 0;
+  int* d_status = nullptr;
+  unsigned long long launches = 0;
+  uint8_t* aux = nullptr;  // second scratch block (conv2d im2col operand)
+  size_t aux_bytes = 0;
+  PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  // layout of the last Ozaki-II GEMM, for eshkol_b200_debug_fetch
+  struct Last {
+    bool valid = false;
+    long long M = 0, K = 0, N = 0, Kp = 0, K0 = 0, Mp = 0, Np = 0;
+    int n_mod = 0, n_chunks = 0, last_seg = 0;
+    int* mu = nullptr; int* nu = nullptr;
+    int8_t* a0 = nullptr; int8_t* aodd = nullptr; long long aodd_stride = 0;
+    int8_t* b0 = nullptr; int8_t* bodd = nullptr; long long bodd_stride = 0;
+    int16_t* w0 = nullptr; int8_t* wodd = nullptr; long long wodd_stride = 0;
+  } last;
+};
+static State g;
+static std::mutex g_mu;
+
+#define B200_CHECK(call)                                                              \
+  do {                                                                                \
+    cudaError_t e_ = (call);                                                          \
+    if (e_ != cudaSuccess) {                                                          \
+      fprintf(stderr, "[eshkol-b200] %s failed: %s (%s:%d)\n", #call,                 \
+              cudaGetErrorString(e_), __FILE__, __LINE__);                            \
+      return -1;                                                                      \
+    }                                                                                 \
+  } while (0)
+
+static inline long long round_up(long long x, long long m) { return (x + m - 1) / m * m; }
+
+// Bump allocator over the workspace; every block is 1024-byte aligned so TMA
+// bases and swizzled tiles never need a second thought.
+struct Carver {
+  size_t off = 0;
+  size_t take(size_t bytes) {
+    const size_t o = off;
+    off += (bytes + 1023) & ~static_cast<size_t>(1023);
+    return o;
+  }
+};
+
+static int ensure_workspace(size_t bytes) {
+  if (bytes <= g.ws_bytes) return 0;
+  B200_CHECK(cudaStreamSynchronize(g.stream));
+  if (g.ws) B200_CHECK(cudaFree(g.ws));
+  g.ws = nullptr;
+  g.ws_bytes = 0;
+  g.last.valid = false;
+  const size_t want = bytes + (bytes >> 4);  // a little headroom against regrowth
+  cudaError_t e = cudaMalloc(&g.ws, want);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    e = cudaMalloc(&g.ws, bytes);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "[eshkol-b200] workspace allocation of %zu bytes failed: %s\n", bytes,
+              cudaGetErrorString(e));
+      cudaGetLastError();
+      return -1;
+    }
+    g.ws_bytes = bytes;
+    return 0;
+  }
+  g.ws_bytes = want;
+  return 0;
+}
+
+uint8_t* aux_reserve(size_t bytes) {
+  if (bytes <= g.aux_bytes) return g.aux;
+  if (cudaStreamSynchronize(g.stream) != cudaSuccess) return nullptr;
+  if (g.aux) cudaFree(g.aux);
+  g.aux = nullptr;
+  g.aux_bytes = 0;
+  if (cudaMalloc(&g.aux, bytes) != cudaSuccess) {
+    fprintf(stderr, "[eshkol-b200] scratch allocation of %zu bytes failed\n", bytes);
+    cudaGetLastError();
+    return nullptr;
+  }
+  g.aux_bytes = bytes;
+  return g.aux;
+}
+
+uint8_t* workspace_reserve(size_t bytes) { return ensure_workspace(bytes) == 0 ? g.ws : nullptr; }
+cudaStream_t lib_stream() { return g.stream; }
+int lib_num_sms() { return g.num_sms; }
+int* lib_status_word() { return g.d_status; }
+void count_launches(int n) { g.launches += static_cast<unsigned long long>(n); }
+
+// rows x inner_bytes int8 planes, `planes` of them `plane_stride` bytes apart,
+// tiled {128 bytes, box_rows, 1} with the 128-byte swizzle; out-of-range rows and
+// bytes read as zero.
+int make_plane_map(CUtensorMap* map, const void* base, long long inner_bytes, long long rows,
+                   long long planes, long long plane_stride, int box_rows) {
+  const cuuint64_t dims[3] = {static_cast<cuuint64_t>(inner_bytes), static_cast<cuuint64_t>(rows),
+                              static_cast<cuuint64_t>(planes)};
+  const cuuint64_t strides[2] = {static_cast<cuuint64_t>(inner_bytes),
+                                 static_cast<cuuint64_t>(plane_stride)};
+  const cuuint32_t box[3] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows), 1u};
+  const cuuint32_t estr[3] = {1u, 1u, 1u};
+  const CUresult r = g.encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims,
+                              strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "[eshkol-b200] cuTensorMapEncodeTiled failed (%d): inner=%lld rows=%lld planes=%lld\n",
+            static_cast<int>(r), inner_bytes, rows, planes);
+    return -1;
+  }
+  return 0;
+}
+
+static void fill_mod_job(GemmJob* j, int a_plane, int b_plane, int out_plane, unsigned p) {
+  memset(j, 0, sizeof(*j));
+  j->n_seg = 1;
+  j->a_plane[0] = a_plane;
+  j->b_plane[0] = b_plane;
+  j->out_plane = out_plane;
+  j->modulus = p;
+  if (p) {
+    j->magic = static_cast<unsigned>((1ull << 32) / p);
+    const unsigned long long bound = 2114044160ull;  // > 131071 * 127 * 127
+    j->offset = static_cast<unsigned>((bound + p - 1) / p * p);
+  }
+}
+
+// ------------------------------------------------------- Ozaki-II CRT constants
+static const int kModuli[16] = {256, 255, 253, 251, 247, 241, 239, 233,
+                                229, 227, 223, 217, 211, 199, 197, 193};
+
+static long long egcd(long long a, long long b, long long& x, long long& y) {
+  if (a == 0) { x = 0; y = 1; return b; }
+  long long x1, y1;
+  const long long gg = egcd(b % a, a, x1, y1);
+  x = y1 - (b / a) * x1;
+  y = x1;
+  return gg;
+}
+static int mod_inverse(long long a, long long m) {
+  long long x, y;
+  egcd(a % m, m, x, y);
+  return static_cast<int>((x % m + m) % m);
+}
+
+// P, its double-double split, 1/P, and the split CRT weights s_l = (P/p_l) *
+// ((P/p_l)^-1 mod p_l); the high part keeps 53 - (8 + ceil(log2 n) + 1) bits.
+// Restates precompute_ozaki_constants, lib/backend/gpu/gpu_memory.mm:301-341.
+void oz2_host_consts(int n_mod, Oz2DeviceConsts* c, double* log2P) {
+  memset(c, 0, sizeof(*c));
+  c->n_mod = n_mod;
+  __int128 P = 1;
+  for (int l = 0; l < n_mod; ++l) P *= kModuli[l];
+  c->P1 = static_cast<double>(P);
+  c->P2 = static_cast<double>(P - static_cast<__int128>(c->P1));
+  c->Pinv = 1.0 / static_cast<double>(P);
+  if (log2P) *log2P = log2(static_cast<double>(P));
+  const int bits_to_remove = 8 + static_cast<int>(ceil(log2(static_cast<double>(n_mod))));
+  for (int l = 0; l < n_mod; ++l) {
+    const int p = kModuli[l];
+    const __int128 Pp = P / p;
+    const int q = mod_inverse(static_cast<long long>(Pp % p), p);
+    const __int128 s = Pp * static_cast<__int128>(q);
+    const double s_d = static_cast<double>(s);
+    const double factor = static_cast<double>(1LL << (bits_to_remove + 1)) + 1.0;
+    volatile double t = factor * s_d;
+    volatile double u = t - s_d;
+    c->sl1[l] = t - u;
+    c->sl2[l] = static_cast<double>(s - static_cast<__int128>(c->sl1[l]));
+    c->p_d[l] = static_cast<double>(p);
+    c->p_inv[l] = 1.0 / static_cast<double>(p);
+    c->p_i[l] = p;
+    c->q_i[l] = q;
+  }
+}
+
+// E = clamp(floor((log2 P - 1 - log2 K - fracA - fracB) / 2), 0, 52), with fracA
+// the largest fractional part of log2 of a nonzero row maximum, fracB likewise
+// for columns.  Restates gpu_memory.mm:403-417 and :2510-2512 on the host.
+static int oz2_exponent(double log2P, long long K, const double* amax, long long M,
+                        const double* bmax, long long N) {
+  double fa = 0.0, fb = 0.0;
+  for (long long i = 0; i < M; ++i)
+    if (amax[i] > 0.0) { const double lg = log2(amax[i]); const double f = lg - floor(lg); if (f > fa) fa = f; }
+  for (long long j = 0; j < N; ++j)
+    if (bmax[j] > 0.0) { const double lg = log2(bmax[j]); const double f = lg - floor(lg); if (f > fb) fb = f; }
+  int E = static_cast<int>(floor((log2P - 1.0 - log2(static_cast<double>(K)) - fa - fb) / 2.0));
+  if (E > 52) E = 52;
+  if (E < 0) E = 0;
+  return E;
+}
+
+// ------------------------------------------------------------ Ozaki-II driver
+static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long M, long long K,
+                       long long N, int n_mod, const EshkolB200GemmOpts& o) {
+  if (n_mod < 2 || n_mod > 16) {
+    fprintf(stderr, "[eshkol-b200] Ozaki-II: moduli count %d outside [2,16]\n", n_mod);
+    return -1;
+  }
+  // int32 accumulation of K products of magnitude <= 127^2 is exact below this bound
+  if (K > 131071) {
+    fprintf(stderr, "[eshkol-b200] Ozaki-II: K=%lld exceeds the int32-exact bound 131071\n", K);
+    return -1;
+  }
+  if (M > 0x7fffff00LL || N > 0x7fffff00LL) return -1;
+  const int bn = (o.gemm_tile_n == 128) ? 128 : 256;
+  const long long Kp = round_up(K, kBK);
+  const int n_chunks = static_cast<int>((K + kChunkK - 1) / kChunkK);
+  const int last_len = static_cast<int>(K - static_cast<long long>(n_chunks - 1) * kChunkK);
+  const int last_seg = static_cast<int>(round_up(last_len, kBK));
+  const long long K0 = static_cast<long long>(n_chunks - 1) * kChunkExt + 3LL * last_seg;
+  const int tiles_m = static_cast<int>((M + kBM - 1) / kBM);
+  const int tiles_n = static_cast<int>((N + bn - 1) / bn);
+  const long long Mp = static_cast<long long>(tiles_m) * kBM, Np = static_cast<long long>(tiles_n) * bn;
+  const int n_odd = n_mod - 1;
+  if (static_cast<long long>(tiles_m) * tiles_n * n_mod > 0x7fffffffLL) return -1;
+
+  Carver cv;
+  const size_t o_amax = cv.take(M * 8), o_bmax = cv.take(N * 8);
+  const size_t o_mu = cv.take(M * 4), o_nu = cv.take(N * 4);
+  const size_t o_sa = cv.take(M * 8), o_sai = cv.take(M * 8);
+  const size_t o_sb = cv.take(N * 8), o_sbi = cv.take(N * 8);
+  const size_t o_jobs = cv.take(sizeof(GemmJob) * 16);
+  const size_t o_a0 = cv.take(static_cast<size_t>(M) * K0), o_b0 = cv.take(static_cast<size_t>(N) * K0);
+  const size_t a_stride = static_cast<size_t>(M) * Kp, b_stride = static_cast<size_t>(N) * Kp;
+  const size_t o_aodd = cv.take(a_stride * n_odd), o_bodd = cv.take(b_stride * n_odd);
+  const size_t w_stride = static_cast<size_t>(Mp) * Np;
+  const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
+  if (ensure_workspace(cv.off) != 0) return -1;
+  uint8_t* ws = g.ws;
+  double* amax = reinterpret_cast<double*>(ws + o_amax);
+  double* bmax = reinterpret_cast<double*>(ws + o_bmax);
+  int* mu = reinterpret_cast<int*>(ws + o_mu);
+  int* nu = reinterpret_cast<int*>(ws + o_nu);
+  double* sa = reinterpret_cast<double*>(ws + o_sa);
+  double* sai = reinterpret_cast<double*>(ws + o_sai);
+  double* sb = reinterpret_cast<double*>(ws + o_sb);
+  double* sbi = reinterpret_cast<double*>(ws + o_sbi);
+  GemmJob* d_jobs = reinterpret_cast<GemmJob*>(ws + o_jobs);
+  int8_t* a0 = reinterpret_cast<int8_t*>(ws + o_a0);
+  int8_t* b0 = reinterpret_cast<int8_t*>(ws + o_b0);
+  int8_t* aodd = reinterpret_cast<int8_t*>(ws + o_aodd);
+  int8_t* bodd = reinterpret_cast<int8_t*>(ws + o_bodd);
+  int16_t* w0 = reinterpret_cast<int16_t*>(ws + o_w0);
+  int8_t* wodd = reinterpret_cast<int8_t*>(ws + o_wodd);
+  cudaStream_t st = g.stream;
+
+  double log2P = 0.0;
+  Oz2DeviceConsts hc;
+  oz2_host_consts(n_mod, &hc, &log2P);
+
+  B200_CHECK(launch_scan_rows(dA, M, K, amax, st));
+  B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(bmax), st));
+  g.launches += 2;
+
+  // With all 16 moduli, log2 P - 1 - log2 K - 2 > 104 for every admissible K, so E
+  // clamps to 52 whatever the data; fewer moduli need the data-dependent bound.
+  int E = 52;
+  if (n_mod < 16) {
+    std::vector<double> ha(M), hb(N);
+    B200_CHECK(cudaMemcpyAsync(ha.data(), amax, M * 8, cudaMemcpyDeviceToHost, st));
+    B200_CHECK(cudaMemcpyAsync(hb.data(), bmax, N * 8, cudaMemcpyDeviceToHost, st));
+    B200_CHECK(cudaStreamSynchronize(st));
+    E = oz2_exponent(log2P, K, ha.data(), M, hb.data(), N);
+  }
+  B200_CHECK(launch_scales(amax, M, E, mu, sa, sai, st));
+  B200_CHECK(launch_scales(bmax, N, E, nu, sb, sbi, st));
+  g.launches += 2;
+
+  SplitPlanes pa{M, K, Kp, K0, n_chunks, last_seg, n_odd, a0, aodd, static_cast<long long>(a_stride)};
+  SplitPlanes pb{N, K, Kp, K0, n_chunks, last_seg, n_odd, b0, bodd, static_cast<long long>(b_stride)};
+  B200_CHECK(launch_split_a(dA, sa, pa, hc, st));
+  B200_CHECK(launch_split_b(dB, sb, N, pb, hc, st));
+  g.launches += 2;
+
+  GemmJob jobs[16];
+  fill_mod_job(&jobs[0], 0, 0, 0, 0);
+  for (int l = 1; l < n_mod; ++l) fill_mod_job(&jobs[l], l - 1, l - 1, l - 1, kModuli[l]);
+  B200_CHECK(cudaMemcpyAsync(d_jobs, jobs, sizeof(GemmJob) * n_mod, cudaMemcpyHostToDevice, st));
+
+  GemmParams p0;
+  p0.tiles_m = tiles_m; p0.tiles_n = tiles_n; p0.n_jobs = 1;
+  p0.kb_per_seg = static_cast<int>(K0 / kBK);
+  p0.kb_per_unit = kChunkExt / kBK;
+  p0.group_m = 16;
+  p0.jobs = d_jobs;
+  p0.out = reinterpret_cast<uint8_t*>(w0);
+  p0.out_plane_stride = 0;
+  p0.ldo = static_cast<int>(Np);
+  p0.status = g.d_status;
+  GemmParams p1 = p0;
+  p1.n_jobs = n_odd;
+  p1.kb_per_seg = static_cast<int>(Kp / kBK);
+  p1.kb_per_unit = 1 << 28;
+  p1.jobs = d_jobs + 1;
+  p1.out = reinterpret_cast<uint8_t*>(wodd);
+  p1.out_plane_stride = static_cast<long long>(w_stride);
+
+  if (o.use_simt_products) {
+    SimtPlanes s0{a0, 0, static_cast<int>(K0), b0, 0, static_cast<int>(K0), static_cast<int>(M), static_cast<int>(N)};
+    SimtPlanes s1{aodd, static_cast<long long>(a_stride), static_cast<int>(Kp), bodd,
+                  static_cast<long long>(b_stride), static_cast<int>(Kp), static_cast<int>(M), static_cast<int>(N)};
+    B200_CHECK(launch_modgemm_simt(kEpiMod256, s0, p0, st));
+    B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
+  } else {
+    CUtensorMap mA0, mB0, mA1, mB1;
+    if (make_plane_map(&mA0, a0, K0, M, 1, static_cast<long long>(M) * K0, kBM)) return -1;
+    if (make_plane_map(&mB0, b0, K0, N, 1, static_cast<long long>(N) * K0, bn)) return -1;
+    if (make_plane_map(&mA1, aodd, Kp, M, n_odd, static_cast<long long>(a_stride), kBM)) return -1;
+    if (make_plane_map(&mB1, bodd, Kp, N, n_odd, static_cast<long long>(b_stride), bn)) return -1;
+    B200_CHECK(launch_modgemm(bn, kEpiMod256, mA0, mB0, p0, tiles_m * tiles_n, g.num_sms, st));
+    B200_CHECK(launch_modgemm(bn, kEpiModI8, mA1, mB1, p1, tiles_m * tiles_n * n_odd, g.num_sms, st));
+  }
+  g.launches += 2;
+
+  CrtArgs ca;
+  ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = Np;
+  ca.n_mod = n_mod; ca.M = M; ca.N = N;
+  ca.inv_scale_a = sai; ca.inv_scale_b = sbi;
+  ca.C = dC; ca.ldc = N;
+  ca.bias_mode = o.bias ? o.bias_mode : 0; ca.bias = o.bias;
+  ca.activation = o.activation;
+  ca.pixels_per_image = o.pixels_per_image;
+  B200_CHECK(launch_crt(ca, hc, st));
+  g.launches += 1;
+
+  State::Last& L = g.last;
+  L.valid = true; L.M = M; L.K = K; L.N = N; L.Kp = Kp; L.K0 = K0; L.Mp = Mp; L.Np = Np;
+  L.n_mod = n_mod; L.n_chunks = n_chunks; L.last_seg = last_seg;
+  L.mu = mu; L.nu = nu; L.a0 = a0; L.aodd = aodd; L.aodd_stride = static_cast<long long>(a_stride);
+  L.b0 = b0; L.bodd = bodd; L.bodd_stride = static_cast<long long>(b_stride);
+  L.w0 = w0; L.wodd = wodd; L.wodd_stride = static_cast<long long>(w_stride);
+  return 0;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int eshkol_b200_init(int device) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (g.ready) return 0;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) { cudaGetLastError(); return -1; }
+  if (device < 0 || device >= count) return -1;
+  B200_CHECK(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  B200_CHECK(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10) {
+    fprintf(stderr, "[eshkol-b200] device %d is sm_%d%d; this library carries sm_100a code only\n",
+            device, prop.major, prop.minor);
+    return -1;
+  }
+  g.device = device;
+  g.num_sms = prop.multiProcessorCount;
+  B200_CHECK(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
+  B200_CHECK(cudaMalloc(&g.d_status, sizeof(int)));
+  B200_CHECK(cudaMemset(g.d_status, 0, sizeof(int)));
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  B200_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+  if (!fn || qres != cudaDriverEntryPointSuccess) {
+    fprintf(stderr, "[eshkol-b200] cuTensorMapEncodeTiled is not available from this driver\n");
+    return -1;
+  }
+  g.encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
+  B200_CHECK(modgemm_set_attributes());
+  B200_CHECK(split_set_attributes());
+  B200_CHECK(tiers_set_attributes());
+  g.ready = true;
+  return 0;
+}
+
+void eshkol_b200_shutdown(void) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  if (!g.ready) return;
+  cudaStreamSynchronize(g.stream);
+  if (g.ws) cudaFree(g.ws);
+  if (g.aux) cudaFree(g.aux);
+  if (g.d_status) cudaFree(g.d_status);
+  cudaStreamDestroy(g.stream);
+  g = State();
+}
+
+void* eshkol_b200_stream(void) { return g.ready ? static_cast<void*>(g.stream) : nullptr; }
+
+int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC, uint64_t M,
+                                uint64_t K, uint64_t N, const EshkolB200GemmOpts* opts) {
+  if (!g.ready) {
+    fprintf(stderr, "[eshkol-b200] gemm called before eshkol_b200_init succeeded\n");
+    return -1;
+  }
+  if (!dA || !dB || !dC || M == 0 || K == 0 || N == 0) return -1;
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  if (opts) o = *opts;
+  const long long m = static_cast<long long>(M), k = static_cast<long long>(K), n = static_cast<long long>(N);
+  switch (o.tier) {
+    case ESHKOL_B200_TIER_OZAKI2:
+      return ozaki2_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 16, o);
+    case ESHKOL_B200_TIER_OZAKI1:
+      return ozaki1_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 6, o);
+    case ESHKOL_B200_TIER_OZAKI2_FAST:
+      return ozaki2_fast_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 11, o);
+    case ESHKOL_B200_TIER_DGEMM:
+      return native_dgemm(dA, dB, dC, m, k, n, o);
+    default:
+      fprintf(stderr, "[eshkol-b200] unknown tier %d\n", o.tier);
+      return -1;
+  }
+}
+
+int eshkol_b200_conv2d_f64_device(const double* d_in, int64_t batch, int64_t in_c, int64_t H,
+                                  int64_t W, const double* d_ker, int64_t out_c, int64_t kH,
+                                  int64_t kW, int64_t stride, int64_t pad, double* d_out,
+                                  const EshkolB200GemmOpts* opts) {
+  if (!g.ready) {
+    fprintf(stderr, "[eshkol-b200] conv2d called before eshkol_b200_init succeeded\n");
+    return -1;
+  }
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  if (opts) o = *opts;
+  return conv2d_lowered(d_in, batch, in_c, H, W, d_ker, out_c, kH, kW, stride, pad, d_out, o);
+}
+
+int eshkol_b200_mem_alloc(int kind, size_t bytes, void** out_ptr) {
+  if (!g.ready || !out_ptr || bytes == 0) return -1;
+  cudaError_t e;
+  switch (kind) {
+    case 0: e = cudaMalloc(out_ptr, bytes); break;
+    case 1: e = cudaMallocManaged(out_ptr, bytes); break;
+    case 2: e = cudaMallocHost(out_ptr, bytes); break;
+    default: return -1;
+  }
+  if (e != cudaSuccess) { cudaGetLastError(); *out_ptr = nullptr; return -1; }
+  return 0;
+}
+
+void eshkol_b200_mem_free(int kind, void* ptr) {
+  if (!g.ready || !ptr) return;
+  cudaStreamSynchronize(g.stream);
+  if (kind == 2) cudaFreeHost(ptr); else cudaFree(ptr);
+}
+
+int eshkol_b200_copy_h2d(void* device_dst, const void* host_src, size_t bytes) {
+  if (!g.ready) return -1;
+  B200_CHECK(cudaMemcpyAsync(device_dst, host_src, bytes, cudaMemcpyHostToDevice, g.stream));
+  return 0;
+}
+
+int eshkol_b200_copy_d2h(void* host_dst, const void* device_src, size_t bytes) {
+  if (!g.ready) return -1;
+  B200_CHECK(cudaMemcpyAsync(host_dst, device_src, bytes, cudaMemcpyDeviceToHost, g.stream));
+  return 0;
+}
+
+int eshkol_b200_elementwise_f64_device(const double* a, const double* b, double* out,
+                                       uint64_t n, int op) {
+  if (!g.ready || !a || !out || n == 0 || op < 0 || op > 14) return -1;
+  B200_CHECK(launch_elementwise(a, b, out, static_cast<long long>(n), op, g.stream));
+  g.launches += 1;
+  return 0;
+}
+
+int eshkol_b200_sync_status(void) {
+  if (!g.ready) return -1;
+  int h = 0;
+  if (cudaMemcpyAsync(&h, g.d_status, sizeof(int), cudaMemcpyDeviceToHost, g.stream) != cudaSuccess ||
+      cudaStreamSynchronize(g.stream) != cudaSuccess) {
+    fprintf(stderr, "[eshkol-b200] stream failed: %s\n", cudaGetErrorString(cudaGetLastError()));
+    return -1;
+  }
+  if (h != 0) {
+    fprintf(stderr, "[eshkol-b200] a kernel gave up a bounded wait (status %d)\n", h);
+    cudaMemsetAsync(g.d_status, 0, sizeof(int), g.stream);
+    cudaStreamSynchronize(g.stream);
+  }
+  return h;
+}
+
+uint64_t eshkol_b200_launch_count(void) { return g.launches; }
+uint64_t eshkol_b200_workspace_bytes(void) { return g.ws_bytes + g.aux_bytes; }
+
+int eshkol_b200_debug_fetch(int what, int index, void* host_dst, uint64_t capacity_bytes,
+                            uint64_t info[6]) {
+  if (!g.ready || !g.last.valid || !host_dst || !info) return -1;
+  const State::Last& L = g.last;
+  const void* src = nullptr;
+  uint64_t rows = 0, pitch = 0, esz = 1;
+  const int n_odd = L.n_mod - 1;
+  switch (what) {
+    case 0: src = L.mu; rows = 1; pitch = L.M; esz = 4; break;
+    case 1: src = L.nu; rows = 1; pitch = L.N; esz = 4; break;
+    case 2: src = L.a0; rows = L.M; pitch = L.K0; break;
+    case 3: if (index < 0 || index >= n_odd) return -1;
+            src = L.aodd + index * L.aodd_stride; rows = L.M; pitch = L.Kp; break;
+    case 4: src = L.b0; rows = L.N; pitch = L.K0; break;
+    case 5: if (index < 0 || index >= n_odd) return -1;
+            src = L.bodd + index * L.bodd_stride; rows = L.N; pitch = L.Kp; break;
+    case 6: src = L.w0; rows = L.Mp; pitch = L.Np; esz = 2; break;
+    case 7: if (index < 0 || index >= n_odd) return -1;
+            src = L.wodd + index * L.wodd_stride; rows = L.Mp; pitch = L.Np; break;
+    default: return -1;
+  }
+  const uint64_t bytes = rows * pitch * esz;
+  if (bytes > capacity_bytes) return -2;
+  if (cudaMemcpyAsync(host_dst, src, bytes, cudaMemcpyDeviceToHost, g.stream) != cudaSuccess ||
+      cudaStreamSynchronize(g.stream) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  info[0] = rows; info[1] = pitch; info[2] = esz; info[3] = L.n_chunks; info[4] = L.last_seg;
+  info[5] = bytes;
+  return 0;
+}
+
+}  // extern "C"

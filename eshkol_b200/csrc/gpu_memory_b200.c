@@ -1,0 +1,473 @@
+/*
+ * Host side of the drop-in backend, in C: buffer handles, the dispatch policy and
+ * the environment switches of the reference's GPU backends, on top of the thin
+ * device-level shim (include/eshkol_b200_ext.h).
+ *
+ * What each function mirrors in the reference:
+ *   init / shutdown / queries      lib/backend/gpu/gpu_memory_cuda.cpp:839-920
+ *   alloc / free / wrap / sync     lib/backend/gpu/gpu_memory_cuda.cpp:168-285, 793-821, 924-1027
+ *   tier selection for f64 matmul  lib/backend/gpu/gpu_memory_cuda.cpp:310-326, 527-566, 577-650
+ *                                  lib/backend/gpu/gpu_memory.mm:1309-1343, 3028-3051
+ *   eshkol_matmul_dispatch         lib/backend/gpu/gpu_memory_cuda.cpp:1107-1157
+ *   eshkol_batch_matmul_dispatch   lib/backend/gpu/gpu_memory_cuda.cpp:1165-1175
+ *
+ * Differences that are deliberate:
+ *   - a wrapped host buffer is staged into device memory (one DMA in, one out)
+ *     instead of being mapped: the GEMM reads each operand many times and must
+ *     not do so across PCIe;
+ *   - there is no silent CPU result.  Below the element threshold the call is
+ *     handed to the runtime's eshkol_matmul_f64 when that symbol is linked in
+ *     (dispatch policy, unchanged); a failure of the GPU path is reported on
+ *     stderr and by the return value, and the void dispatchers then fill C with
+ *     NaN rather than a number of unknown provenance.
+ */
+#include "../../include/eshkol_gpu_memory_b200.h"
+#include "../../include/eshkol_b200_ext.h"
+
+#include <math.h>
+#include <pthread.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+size_t g_gpu_threshold = 100000; /* gpu_memory_cuda.cpp:107 */
+
+static EshkolGPUBackend g_backend = ESHKOL_GPU_NONE;
+static int g_initialized = 0;
+static pthread_mutex_t g_init_mutex = PTHREAD_MUTEX_INITIALIZER;
+
+/* bit 0 and 1 as in the reference (gpu_memory_cuda.cpp:123-124); bit 2 marks a wrapped
+ * buffer whose device copy was written by an operator and not yet copied back */
+enum { FLAG_WRAPPED = 1u << 0, FLAG_COPY_BACK = 1u << 1, FLAG_DIRTY = 1u << 2 };
+
+/* CPU entry points of the host runtime; present when this object is linked into
+ * Eshkol, absent when the library is used on its own. */
+extern void eshkol_matmul_f64(const double*, const double*, double*, uint64_t, uint64_t, uint64_t)
+    __attribute__((weak));
+extern void eshkol_batch_matmul_f64(const double*, const double*, double*, int64_t, int64_t,
+                                    int64_t, int64_t) __attribute__((weak));
+
+static int gpu_verbose(void) {
+  static int checked = 0, verbose = 0;
+  if (!checked) { verbose = getenv("ESHKOL_GPU_VERBOSE") != NULL; checked = 1; }
+  return verbose;
+}
+#define GPU_LOG(...) do { if (gpu_verbose()) { fprintf(stderr, "[GPU] " __VA_ARGS__); fputc('\n', stderr); } } while (0)
+
+/* ------------------------------------------------------------------ init ---- */
+int eshkol_gpu_init(void) {
+  if (__atomic_load_n(&g_initialized, __ATOMIC_ACQUIRE)) return g_backend != ESHKOL_GPU_NONE;
+  pthread_mutex_lock(&g_init_mutex);
+  if (!g_initialized) {
+    const char* env = getenv("ESHKOL_GPU_THRESHOLD");
+    if (env) {
+      long v = atol(env);
+      if (v > 0) g_gpu_threshold = (size_t)v;
+    }
+    int dev = 0;
+    const char* denv = getenv("ESHKOL_B200_DEVICE");
+    if (denv) dev = atoi(denv);
+    g_backend = (eshkol_b200_init(dev) == 0) ? ESHKOL_GPU_CUDA : ESHKOL_GPU_NONE;
+    __atomic_store_n(&g_initialized, 1, __ATOMIC_RELEASE);
+  }
+  pthread_mutex_unlock(&g_init_mutex);
+  return g_backend != ESHKOL_GPU_NONE;
+}
+
+void eshkol_gpu_shutdown(void) {
+  pthread_mutex_lock(&g_init_mutex);
+  if (g_backend == ESHKOL_GPU_CUDA) eshkol_b200_shutdown();
+  g_backend = ESHKOL_GPU_NONE;
+  __atomic_store_n(&g_initialized, 0, __ATOMIC_RELEASE);
+  pthread_mutex_unlock(&g_init_mutex);
+}
+
+EshkolGPUBackend eshkol_gpu_get_backend(void) { return g_backend; }
+
+const char* eshkol_gpu_backend_name(EshkolGPUBackend backend) {
+  switch (backend) {
+    case ESHKOL_GPU_NONE: return "CPU (no GPU)";
+    case ESHKOL_GPU_METAL: return "Apple Metal (not available on Linux)";
+    case ESHKOL_GPU_CUDA: return "NVIDIA CUDA";
+    case ESHKOL_GPU_VULKAN: return "Vulkan";
+  }
+  return "Unknown";
+}
+
+int eshkol_gpu_backend_available(EshkolGPUBackend backend) { return g_backend == backend; }
+int eshkol_gpu_supports_f64(void) { return g_backend == ESHKOL_GPU_CUDA; }
+int eshkol_gpu_has_fp64(void) { return eshkol_gpu_supports_f64(); }
+
+/* ---------------------------------------------------------------- memory ---- */
+int eshkol_gpu_alloc(size_t size_bytes, EshkolMemoryType mem_type, EshkolGPUBuffer* out) {
+  if (!out || size_bytes == 0) return -1;
+  memset(out, 0, sizeof(*out));
+  if (g_backend != ESHKOL_GPU_CUDA) {
+    out->host_ptr = malloc(size_bytes);
+    if (!out->host_ptr) return -1;
+    out->device_ptr = out->host_ptr;
+    out->size_bytes = size_bytes;
+    out->mem_type = ESHKOL_MEM_HOST;
+    out->backend = ESHKOL_GPU_NONE;
+    return 0;
+  }
+  void* p = NULL;
+  switch (mem_type) {
+    case ESHKOL_MEM_DEVICE:
+      if (eshkol_b200_mem_alloc(0, size_bytes, &p)) return -1;
+      out->device_ptr = p;
+      break;
+    case ESHKOL_MEM_HOST_PINNED:
+      if (eshkol_b200_mem_alloc(2, size_bytes, &p)) return -1;
+      out->host_ptr = p;
+      break;
+    default: /* unified, and anything else, as the reference does */
+      if (eshkol_b200_mem_alloc(1, size_bytes, &p)) return -1;
+      out->host_ptr = p;
+      out->device_ptr = p;
+      mem_type = (mem_type == ESHKOL_MEM_UNIFIED) ? ESHKOL_MEM_UNIFIED : mem_type;
+      break;
+  }
+  out->size_bytes = size_bytes;
+  out->mem_type = mem_type;
+  out->backend = ESHKOL_GPU_CUDA;
+  return 0;
+}
+
+int eshkol_gpu_alloc_aligned(size_t size_bytes, size_t alignment, EshkolMemoryType mem_type,
+                             EshkolGPUBuffer* out) {
+  if (alignment == 0) alignment = 1;
+  const size_t aligned = (size_bytes + alignment - 1) & ~(alignment - 1);
+  return eshkol_gpu_alloc(aligned, mem_type, out);
+}
+
+static int copy_back(EshkolGPUBuffer* b) {
+  if (!(b->flags & FLAG_COPY_BACK) || !b->backend_data || !b->device_ptr) return 0;
+  if (eshkol_b200_copy_d2h(b->backend_data, b->device_ptr, b->size_bytes)) return -1;
+  b->flags &= ~(uint32_t)FLAG_DIRTY;
+  return eshkol_b200_sync_status() == 0 ? 0 : -1;
+}
+
+void eshkol_gpu_free(EshkolGPUBuffer* b) {
+  if (!b) return;
+  if (b->backend == ESHKOL_GPU_CUDA) {
+    if (b->flags & FLAG_WRAPPED) {
+      /* the device copy is ours, the host memory is the caller's.  A caller that
+       * frees without syncing (lib/backend/vm_gpu_dispatch.h:78-83) still gets its
+       * result: an operator's output is copied back here, as cuda_free does for its
+       * staged buffers (gpu_memory_cuda.cpp:214-219). */
+      if (b->flags & FLAG_DIRTY) (void)copy_back(b);
+      if (b->device_ptr) eshkol_b200_mem_free(0, b->device_ptr);
+    } else if (b->mem_type == ESHKOL_MEM_HOST_PINNED) {
+      if (b->host_ptr) eshkol_b200_mem_free(2, b->host_ptr);
+    } else if (b->device_ptr) {
+      eshkol_b200_mem_free(0, b->device_ptr);
+    }
+  } else if (b->host_ptr && !(b->flags & FLAG_WRAPPED)) {
+    free(b->host_ptr);
+  }
+  memset(b, 0, sizeof(*b));
+}
+
+int eshkol_gpu_wrap_host(void* host_ptr, size_t size_bytes, EshkolGPUBuffer* out) {
+  if (!host_ptr || !out || size_bytes == 0) return -1;
+  memset(out, 0, sizeof(*out));
+  if (g_backend != ESHKOL_GPU_CUDA) {
+    out->host_ptr = host_ptr;
+    out->device_ptr = host_ptr;
+    out->size_bytes = size_bytes;
+    out->mem_type = ESHKOL_MEM_HOST;
+    out->backend = ESHKOL_GPU_NONE;
+    out->flags = FLAG_WRAPPED;
+    return 0;
+  }
+  void* d = NULL;
+  if (eshkol_b200_mem_alloc(0, size_bytes, &d)) return -1;
+  if (eshkol_b200_copy_h2d(d, host_ptr, size_bytes)) { eshkol_b200_mem_free(0, d); return -1; }
+  out->host_ptr = host_ptr;
+  out->device_ptr = d;
+  out->size_bytes = size_bytes;
+  out->mem_type = ESHKOL_MEM_DEVICE;
+  out->backend = ESHKOL_GPU_CUDA;
+  out->flags = FLAG_WRAPPED | FLAG_COPY_BACK;
+  out->backend_data = host_ptr;
+  return 0;
+}
+
+int eshkol_gpu_sync(EshkolGPUBuffer* b, EshkolSyncDirection direction) {
+  if (!b) return -1;
+  if (b->backend != ESHKOL_GPU_CUDA) return 0;
+  if (b->flags & FLAG_WRAPPED) {
+    if (direction == ESHKOL_SYNC_HOST_TO_DEVICE || direction == ESHKOL_SYNC_BIDIRECTIONAL)
+      if (eshkol_b200_copy_h2d(b->device_ptr, b->backend_data, b->size_bytes)) return -1;
+    if (direction == ESHKOL_SYNC_DEVICE_TO_HOST || direction == ESHKOL_SYNC_BIDIRECTIONAL)
+      return copy_back(b);
+  }
+  return eshkol_b200_sync_status() == 0 ? 0 : -1;
+}
+
+int eshkol_gpu_sync_async(EshkolGPUBuffer* b, EshkolSyncDirection direction, void* stream) {
+  (void)stream; /* one stream, as in the reference (gpu_memory_cuda.cpp:1012-1015) */
+  return eshkol_gpu_sync(b, direction);
+}
+
+void eshkol_gpu_wait(EshkolGPUBuffer* b) {
+  (void)b;
+  if (g_backend == ESHKOL_GPU_CUDA) (void)eshkol_b200_sync_status();
+}
+
+/* ------------------------------------------------------- tier selection ---- */
+typedef struct { int tier, param; const char* why; } TierChoice;
+
+/* guaranteed relative error of Ozaki-I at T = 1..8 (gpu_memory_cuda.cpp:485-487) */
+static const double OZAKI_TOL[9] = {1.0, 1e-3, 1e-5, 1e-7, 1e-9, 1e-11, 1e-13, 1e-14, 1e-14};
+
+static int env_int_clamped(const char* name, int lo, int hi, int dflt, int clamp_to_edge) {
+  const char* e = getenv(name);
+  if (!e) return dflt;
+  const int v = atoi(e);
+  if (v >= lo && v <= hi) return v;
+  const int used = clamp_to_edge ? (v < lo ? lo : hi) : dflt;
+  fprintf(stderr, "[GPU] %s=%d out of range [%d,%d]; using %d\n", name, v, lo, hi, used);
+  return used;
+}
+
+static TierChoice choose_tier(uint64_t M, uint64_t K, uint64_t N) {
+  TierChoice c = {ESHKOL_B200_TIER_OZAKI2, 16, "default: Ozaki-II exact"};
+  const char* k;
+  if ((k = getenv("ESHKOL_B200_TIER")) != NULL) {
+    if (!strncmp(k, "ozaki1", 6)) { c.tier = ESHKOL_B200_TIER_OZAKI1; c.param = k[6] == ':' ? atoi(k + 7) : 6; c.why = "ESHKOL_B200_TIER"; return c; }
+    if (!strncmp(k, "fast", 4)) { c.tier = ESHKOL_B200_TIER_OZAKI2_FAST; c.param = k[4] == ':' ? atoi(k + 5) : 11; c.why = "ESHKOL_B200_TIER"; return c; }
+    if (!strncmp(k, "exact", 5)) { c.param = k[5] == ':' ? atoi(k + 6) : 16; c.why = "ESHKOL_B200_TIER"; return c; }
+    if (!strcmp(k, "dgemm")) { c.tier = ESHKOL_B200_TIER_DGEMM; c.param = 0; c.why = "ESHKOL_B200_TIER"; return c; }
+    fprintf(stderr, "[GPU] ESHKOL_B200_TIER=%s not understood; ignoring\n", k);
+  }
+  /* CUDA backend's explicit switch: fixed T when every dimension is >= 1024 */
+  if ((k = getenv("ESHKOL_CUDA_F64_KERNEL")) != NULL && !strcmp(k, "ozaki-int8")) {
+    const int T = env_int_clamped("ESHKOL_OZAKI_CUDA_T", 1, 8, 6, 0);
+    if (M >= 1024 && K >= 1024 && N >= 1024) {
+      c.tier = ESHKOL_B200_TIER_OZAKI1; c.param = T; c.why = "ESHKOL_CUDA_F64_KERNEL override";
+      return c;
+    }
+  }
+  /* CUDA backend's accuracy budget: smallest T whose guaranteed error meets it */
+  if ((k = getenv("ESHKOL_MATMUL_ACCURACY")) != NULL && *k) {
+    double budget;
+    if (!strcmp(k, "fast")) budget = 1e-2;
+    else if (!strcmp(k, "exact") || !strcmp(k, "full")) budget = 1e-15;
+    else { budget = atof(k); if (!(budget > 0.0)) budget = 1e-15; }
+    if (K <= 133000) {
+      for (int T = 1; T <= 7; ++T)
+        if (OZAKI_TOL[T] <= budget) { c.tier = ESHKOL_B200_TIER_OZAKI1; c.param = T; c.why = "accuracy-budget selector"; return c; }
+    }
+    c.why = "accuracy budget tighter than any slice tier: Ozaki-II exact";
+    return c;
+  }
+  /* Metal backend's switches */
+  int fast = 0;
+  if ((k = getenv("ESHKOL_OZAKI_FAST")) != NULL && strcmp(k, "0") != 0) fast = 1;
+  if ((k = getenv("ESHKOL_SF64_KERNEL")) != NULL && !strcmp(k, "ozaki-fast")) fast = 1;
+  if (fast) {
+    c.tier = ESHKOL_B200_TIER_OZAKI2_FAST;
+    c.param = env_int_clamped("ESHKOL_OZAKI_FAST_MODULI", 2, 16, 11, 1);
+    c.why = "Ozaki-II fast tier";
+    return c;
+  }
+  c.param = env_int_clamped("ESHKOL_OZAKI_NUM_MODULI", 2, 16, 16, 0);
+  return c;
+}
+
+/* tests: the tier the environment selects for a shape, without touching a GPU */
+void eshkol_b200_debug_choose_tier(uint64_t M, uint64_t K, uint64_t N, int* tier, int* param) {
+  const TierChoice c = choose_tier(M, K, N);
+  if (tier) *tier = c.tier;
+  if (param) *param = c.param;
+}
+
+int eshkol_gpu_matmul_f64(EshkolGPUBuffer* A, EshkolGPUBuffer* B, EshkolGPUBuffer* C,
+                          uint64_t M, uint64_t K, uint64_t N) {
+  if (!A || !B || !C) return -1;
+  if (g_backend != ESHKOL_GPU_CUDA) {
+    fprintf(stderr, "[GPU] eshkol_gpu_matmul_f64: no B200 backend is active\n");
+    return -1;
+  }
+  if (!A->device_ptr || !B->device_ptr || !C->device_ptr) return -1;
+  TierChoice c = choose_tier(M, K, N);
+  if (c.tier != ESHKOL_B200_TIER_DGEMM && K > 131071) {
+    c.tier = ESHKOL_B200_TIER_DGEMM; c.param = 0; c.why = "K beyond the int32-exact bound";
+  }
+  GPU_LOG("matmul %llux%llu @ %llux%llu -> tier %d param %d (%s)", (unsigned long long)M,
+          (unsigned long long)K, (unsigned long long)K, (unsigned long long)N, c.tier, c.param, c.why);
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  o.tier = c.tier;
+  o.param = c.param;
+  if (eshkol_b200_gemm_f64_device((const double*)A->device_ptr, (const double*)B->device_ptr,
+                                  (double*)C->device_ptr, M, K, N, &o))
+    return -1;
+  if (C->flags & FLAG_WRAPPED) C->flags |= FLAG_DIRTY;
+  /* every operator returns only after the device finished (gpu_memory_cuda.cpp:611, 642) */
+  return eshkol_b200_sync_status() == 0 ? 0 : -1;
+}
+
+int eshkol_gpu_matmul_f32(EshkolGPUBuffer* A, EshkolGPUBuffer* B, EshkolGPUBuffer* C,
+                          uint64_t M, uint64_t K, uint64_t N) {
+  (void)A; (void)B; (void)C; (void)M; (void)K; (void)N;
+  /* f32 buffers never reach this backend from the f64 tensor runtime; not built */
+  return -1;
+}
+
+void eshkol_gpu_set_threshold(size_t threshold) { g_gpu_threshold = threshold; }
+size_t eshkol_gpu_get_threshold(void) { return g_gpu_threshold; }
+int eshkol_gpu_should_use(size_t n) { return g_backend != ESHKOL_GPU_NONE && n >= g_gpu_threshold; }
+
+/* ----------------------------------------------------------- elementwise ---- */
+int eshkol_gpu_elementwise_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* out,
+                               uint64_t n, EshkolElementwiseOp op) {
+  if (!a || !out || n == 0) return -1;
+  if (g_backend != ESHKOL_GPU_CUDA || !a->device_ptr || !out->device_ptr) return -1;
+  const double* bp = (b && b->device_ptr) ? (const double*)b->device_ptr : NULL;
+  if (eshkol_b200_elementwise_f64_device((const double*)a->device_ptr, bp, (double*)out->device_ptr,
+                                         n, (int)op))
+    return -1;
+  if (out->flags & FLAG_WRAPPED) out->flags |= FLAG_DIRTY;
+  return eshkol_b200_sync_status() == 0 ? 0 : -1;
+}
+
+/* ----------------------------------------- operators outside this path ---- */
+int eshkol_gpu_reduce_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t n, EshkolReduceOp op) {
+  (void)in; (void)out; (void)n; (void)op; return -1;
+}
+int eshkol_gpu_reduce_axis_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t rank,
+                               const uint64_t* shape, uint64_t axis, EshkolReduceOp op) {
+  (void)in; (void)out; (void)rank; (void)shape; (void)axis; (void)op; return -1;
+}
+int eshkol_gpu_transpose_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t rows, uint64_t cols) {
+  (void)in; (void)out; (void)rows; (void)cols; return -1;
+}
+int eshkol_gpu_softmax_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t num_slices,
+                           uint64_t slice_len) {
+  (void)in; (void)out; (void)num_slices; (void)slice_len; return -1;
+}
+int eshkol_gpu_normalize_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t num_slices,
+                             uint64_t slice_len, double gamma, double beta, double epsilon) {
+  (void)in; (void)out; (void)num_slices; (void)slice_len; (void)gamma; (void)beta; (void)epsilon;
+  return -1;
+}
+int eshkol_gpu_conv2d_backward_input_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
+    uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t d4, uint64_t d5, uint64_t d6,
+    uint64_t d7, uint64_t d8, uint64_t d9, uint64_t d10) {
+  (void)a; (void)b; (void)c; (void)d0; (void)d1; (void)d2; (void)d3; (void)d4; (void)d5; (void)d6;
+  (void)d7; (void)d8; (void)d9; (void)d10; return -1;
+}
+int eshkol_gpu_conv2d_backward_kernel_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
+    uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t d4, uint64_t d5, uint64_t d6,
+    uint64_t d7, uint64_t d8, uint64_t d9, uint64_t d10) {
+  (void)a; (void)b; (void)c; (void)d0; (void)d1; (void)d2; (void)d3; (void)d4; (void)d5; (void)d6;
+  (void)d7; (void)d8; (void)d9; (void)d10; return -1;
+}
+int eshkol_gpu_batchnorm_backward_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
+    EshkolGPUBuffer* d, EshkolGPUBuffer* e, EshkolGPUBuffer* f, EshkolGPUBuffer* g2,
+    EshkolGPUBuffer* h, uint64_t n0, uint64_t n1) {
+  (void)a; (void)b; (void)c; (void)d; (void)e; (void)f; (void)g2; (void)h; (void)n0; (void)n1;
+  return -1;
+}
+int eshkol_gpu_layernorm_backward_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
+    EshkolGPUBuffer* d, EshkolGPUBuffer* e, EshkolGPUBuffer* f, uint64_t n0, uint64_t n1) {
+  (void)a; (void)b; (void)c; (void)d; (void)e; (void)f; (void)n0; (void)n1; return -1;
+}
+
+/* ------------------------------------------------------------ dispatchers ---- */
+static void fill_nan(double* c, uint64_t n) {
+  for (uint64_t i = 0; i < n; ++i) c[i] = NAN;
+}
+
+/* one GEMM on host arrays through the buffer API; 0 on success */
+static int gpu_matmul_host(const double* A, const double* B, double* C, uint64_t M, uint64_t K,
+                           uint64_t N) {
+  EshkolGPUBuffer a, b, c;
+  memset(&a, 0, sizeof(a)); memset(&b, 0, sizeof(b)); memset(&c, 0, sizeof(c));
+  int rc = -1;
+  /* C is output only: give it device memory without the upload a wrap would do */
+  void* dc = NULL;
+  if (eshkol_gpu_wrap_host((void*)A, M * K * sizeof(double), &a) == 0 &&
+      eshkol_gpu_wrap_host((void*)B, K * N * sizeof(double), &b) == 0 &&
+      eshkol_b200_mem_alloc(0, M * N * sizeof(double), &dc) == 0) {
+    c.host_ptr = C; c.device_ptr = dc; c.size_bytes = M * N * sizeof(double);
+    c.mem_type = ESHKOL_MEM_DEVICE; c.backend = ESHKOL_GPU_CUDA;
+    c.flags = FLAG_WRAPPED | FLAG_COPY_BACK; c.backend_data = C;
+    if (eshkol_gpu_matmul_f64(&a, &b, &c, M, K, N) == 0 &&
+        eshkol_gpu_sync(&c, ESHKOL_SYNC_DEVICE_TO_HOST) == 0)
+      rc = 0;
+  }
+  a.flags &= ~FLAG_COPY_BACK; b.flags &= ~FLAG_COPY_BACK;
+  if (a.device_ptr) eshkol_gpu_free(&a);
+  if (b.device_ptr) eshkol_gpu_free(&b);
+  if (c.device_ptr) eshkol_gpu_free(&c);
+  else if (dc) eshkol_b200_mem_free(0, dc);
+  return rc;
+}
+
+void eshkol_matmul_dispatch(const double* A, const double* B, double* C, uint64_t M, uint64_t K,
+                            uint64_t N, int32_t dtype) {
+  (void)dtype; /* f16 / bf16 tags keep f64 storage; the environment picks the tier */
+  if (!A || !B || !C || M == 0 || K == 0 || N == 0) return;
+  if (g_backend == ESHKOL_GPU_NONE) eshkol_gpu_init(); /* gpu_memory_cuda.cpp:1117-1119 */
+  const size_t n_out = (size_t)(M * N);
+  if (!eshkol_gpu_should_use(n_out) && eshkol_matmul_f64) {
+    eshkol_matmul_f64(A, B, C, M, K, N); /* small shapes stay on the CPU: policy, not a fallback */
+    return;
+  }
+  if (g_backend == ESHKOL_GPU_CUDA && gpu_matmul_host(A, B, C, M, K, N) == 0) return;
+  fprintf(stderr, "[GPU] eshkol_matmul_dispatch: the B200 path FAILED for %llux%llux%llu; "
+                  "C is filled with NaN\n", (unsigned long long)M, (unsigned long long)K,
+          (unsigned long long)N);
+  fill_nan(C, M * N);
+}
+
+void eshkol_batch_matmul_dispatch(const double* a, const double* b, double* c, int64_t batch,
+                                  int64_t M, int64_t K, int64_t N, int32_t dtype) {
+  if (!a || !b || !c || batch <= 0 || M <= 0 || K <= 0 || N <= 0) return;
+  if (g_backend == ESHKOL_GPU_NONE) eshkol_gpu_init();
+  if (!eshkol_gpu_should_use((size_t)(M * N)) && eshkol_batch_matmul_f64) {
+    eshkol_batch_matmul_f64(a, b, c, batch, M, K, N);
+    return;
+  }
+  for (int64_t i = 0; i < batch; ++i)
+    eshkol_matmul_dispatch(a + i * M * K, b + i * K * N, c + i * M * N, (uint64_t)M, (uint64_t)K,
+                           (uint64_t)N, dtype);
+}
+
+int eshkol_gpu_conv2d_f64(const double* in, int64_t batch, int64_t in_c, int64_t H, int64_t W,
+                          const double* ker, int64_t out_c, int64_t kH, int64_t kW,
+                          int64_t stride, int64_t pad, double* out, int32_t activation) {
+  if (!in || !ker || !out) return -1;
+  if (g_backend == ESHKOL_GPU_NONE) eshkol_gpu_init();
+  if (g_backend != ESHKOL_GPU_CUDA) return -1;
+  if (stride <= 0) stride = 1;
+  if (pad < 0) pad = 0;
+  const int64_t spanH = H + 2 * pad - kH, spanW = W + 2 * pad - kW;
+  if (spanH < 0 || spanW < 0) return 0;
+  const int64_t oH = spanH / stride + 1, oW = spanW / stride + 1;
+  const size_t in_b = (size_t)(batch * in_c * H * W) * 8, k_b = (size_t)(out_c * in_c * kH * kW) * 8,
+               o_b = (size_t)(batch * out_c * oH * oW) * 8;
+  void *d_in = NULL, *d_k = NULL, *d_o = NULL;
+  int rc = -1;
+  if (eshkol_b200_mem_alloc(0, in_b, &d_in) == 0 && eshkol_b200_mem_alloc(0, k_b, &d_k) == 0 &&
+      eshkol_b200_mem_alloc(0, o_b, &d_o) == 0 && eshkol_b200_copy_h2d(d_in, in, in_b) == 0 &&
+      eshkol_b200_copy_h2d(d_k, ker, k_b) == 0) {
+    TierChoice c = choose_tier((uint64_t)out_c, (uint64_t)(in_c * kH * kW), (uint64_t)(batch * oH * oW));
+    EshkolB200GemmOpts o;
+    memset(&o, 0, sizeof(o));
+    o.tier = c.tier; o.param = c.param; o.activation = activation;
+    if (eshkol_b200_conv2d_f64_device((const double*)d_in, batch, in_c, H, W, (const double*)d_k,
+                                      out_c, kH, kW, stride, pad, (double*)d_o, &o) == 0 &&
+        eshkol_b200_copy_d2h(out, d_o, o_b) == 0 && eshkol_b200_sync_status() == 0)
+      rc = 0;
+  }
+  if (d_in) eshkol_b200_mem_free(0, d_in);
+  if (d_k) eshkol_b200_mem_free(0, d_k);
+  if (d_o) eshkol_b200_mem_free(0, d_o);
+  if (rc) fprintf(stderr, "[GPU] eshkol_gpu_conv2d_f64: the B200 path FAILED\n");
+  return rc;
+}

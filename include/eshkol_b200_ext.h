@@ -1,0 +1,121 @@
+/*
+ * B200 extension entry points of libeshkol_gpu_b200.so.
+ *
+ * The drop-in boundary is include/eshkol_gpu_memory_b200.h (the reference's own
+ * ABI).  The functions here sit one level below it: they take DEVICE pointers and
+ * an explicit tier, so a host runtime that keeps tensors resident (and the tests
+ * and the benchmark) can call the GEMM without the wrap/sync round trip that
+ * eshkol_matmul_dispatch performs on every call
+ * (reference: lib/backend/gpu/gpu_memory_cuda.cpp:1134-1147).
+ *
+ * All functions use plain C types.  Unless stated otherwise they return 0 on
+ * success and a negative value on failure, and they enqueue work on the
+ * library's stream without waiting for it.
+ */
+#ifndef ESHKOL_B200_EXT_H
+#define ESHKOL_B200_EXT_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Precision tiers of the f64 GEMM. */
+typedef enum {
+  /* Ozaki-II, CRT over the first `param` moduli (2..16; 0 means 16), residues of
+   * the products combined exactly as the reference's exact tier does.
+   * Reference: ozaki_ii_dispatch, lib/backend/gpu/gpu_memory.mm:2474-2771. */
+  ESHKOL_B200_TIER_OZAKI2 = 0,
+  /* Ozaki-I, int8 slices, slice pairs with p+q <= T kept, T = `param` (1..8; 0
+   * means 6).  Reference: cuda_matmul_ozaki_int8_f64,
+   * lib/backend/gpu/gpu_memory_cuda.cpp:339-452. */
+  ESHKOL_B200_TIER_OZAKI1 = 1,
+  /* Ozaki-II "fast" tier: frexp exponents, round-half-up significand shift,
+   * fractional CRT in f64, `param` moduli (2..16; 0 means 11).
+   * Reference: ozaki_ii_fast_dispatch, lib/backend/gpu/gpu_memory.mm:2816-3012. */
+  ESHKOL_B200_TIER_OZAKI2_FAST = 2,
+  /* Native f64 FMA GEMM on the CUDA cores (the stand-in for cublasDgemm,
+   * lib/backend/gpu/gpu_memory_cuda.cpp:633-640). */
+  ESHKOL_B200_TIER_DGEMM = 3
+} EshkolB200Tier;
+
+typedef struct EshkolB200GemmOpts {
+  int32_t tier;             /* EshkolB200Tier */
+  int32_t param;            /* tier parameter, 0 = tier default */
+  int32_t activation;       /* 0 none, 1 ReLU (x > 0 ? x : 0) fused into the last pass */
+  int32_t bias_mode;        /* 0 none, 1 bias[row], 2 bias[column], added before the activation */
+  const double* bias;       /* device pointer, M or N doubles */
+  int64_t pixels_per_image; /* > 0: C is written as [N/pixels][M][pixels] (conv2d NCHW) */
+  int32_t use_simt_products;/* tests only: integer products on CUDA cores instead of tcgen05 */
+  int32_t gemm_tile_n;      /* 0 = default (256), or 128 */
+} EshkolB200GemmOpts;
+
+/* Selects `device`, creates the stream and queries the SM count.  Idempotent.
+ * Returns 0, or -1 when no sm_100 device is usable. */
+int eshkol_b200_init(int device);
+void eshkol_b200_shutdown(void);
+
+/* The CUDA stream (cudaStream_t) every call of this library enqueues on. */
+void* eshkol_b200_stream(void);
+
+/* C[M x N] = A[M x K] * B[K x N], row-major f64, all three in device memory.
+ * Asynchronous.  opts may be NULL (exact tier, no epilogue). */
+int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC,
+                                uint64_t M, uint64_t K, uint64_t N,
+                                const EshkolB200GemmOpts* opts);
+
+/* conv2d forward, NCHW cross-correlation with zero padding, lowered to the same
+ * GEMM: out[b][oc][oh][ow] = sum_{ic,kh,kw} in[b][ic][oh*s+kh-p][ow*s+kw-p] * ker[oc][ic][kh][kw].
+ * Device pointers; out is [batch][out_c][oH][oW].  Asynchronous.
+ * Reference semantics: eshkol_conv2d_kernel, lib/backend/tensor_conv_kernel.h:66-105. */
+int eshkol_b200_conv2d_f64_device(const double* d_in, int64_t batch, int64_t in_c, int64_t H,
+                                  int64_t W, const double* d_ker, int64_t out_c, int64_t kH,
+                                  int64_t kW, int64_t stride, int64_t pad, double* d_out,
+                                  const EshkolB200GemmOpts* opts);
+
+/* Memory services for the C host layer.  kind: 0 device (cudaMalloc), 1 managed,
+ * 2 pinned host.  Copies are asynchronous on the library stream; a pageable host
+ * range is staged by the CUDA runtime, a pinned one is read by DMA directly. */
+int eshkol_b200_mem_alloc(int kind, size_t bytes, void** out_ptr);
+void eshkol_b200_mem_free(int kind, void* ptr);
+int eshkol_b200_copy_h2d(void* device_dst, const void* host_src, size_t bytes);
+int eshkol_b200_copy_d2h(void* host_dst, const void* device_src, size_t bytes);
+
+/* out[i] = op(a[i], b[i]) over n device-resident doubles; op numbering and the
+ * meaning of a missing b follow elementwise_f64_kernel,
+ * lib/backend/gpu/gpu_cuda_kernels.cu:21-43 (ReLU is x > 0 ? x : 0).  Asynchronous. */
+int eshkol_b200_elementwise_f64_device(const double* a, const double* b, double* out,
+                                       uint64_t n, int op);
+
+/* Waits for the stream, then returns 0 if every kernel since the previous call
+ * completed normally, a positive kernel status code if a bounded wait inside a
+ * kernel ran out, or -1 on a CUDA error. */
+int eshkol_b200_sync_status(void);
+
+/* Number of kernels this library has launched since init (monotonic). */
+uint64_t eshkol_b200_launch_count(void);
+
+/* Bytes of device scratch currently held by the library's workspace. */
+uint64_t eshkol_b200_workspace_bytes(void);
+
+/* Tests only: copy one intermediate of the LAST Ozaki-II GEMM to host memory.
+ * what: 0 mu (int32[M])          1 nu (int32[N])
+ *       2 A residues, modulus 256 plane   3 A residues, odd plane `index` (0-based)
+ *       4 B residues, modulus 256 plane   5 B residues, odd plane `index`
+ *       6 product residues mod 256 (int16)  7 product residues, odd plane `index` (int8)
+ * info[0..5] receive rows, row pitch (elements), element size, n_chunks, last
+ * segment length, bytes copied.  Synchronises the stream. */
+int eshkol_b200_debug_fetch(int what, int index, void* host_dst, uint64_t capacity_bytes,
+                            uint64_t info[6]);
+
+/* Tests only: the tier and parameter eshkol_gpu_matmul_f64 would select for this
+ * shape from the current environment.  Touches no GPU. */
+void eshkol_b200_debug_choose_tier(uint64_t M, uint64_t K, uint64_t N, int* tier, int* param);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ESHKOL_B200_EXT_H */

@@ -1,0 +1,120 @@
+"""ctypes access to the CPU oracle (oracle/liboracle.so) and to the reference's own
+CPU code compiled into oracle/_ref/.  Test infrastructure only."""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+ORACLE_DIR = os.path.join(ROOT, "oracle")
+UNFUSED, EXPFIELD = 1, 2
+
+_dp = ctypes.POINTER(ctypes.c_double)
+_ip = ctypes.POINTER(ctypes.c_int)
+_fp = ctypes.POINTER(ctypes.c_float)
+_lib = None
+
+
+def build() -> None:
+    subprocess.run(["make", "-C", ORACLE_DIR, "-s"], check=True, capture_output=True)
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        path = os.path.join(ORACLE_DIR, "liboracle.so")
+        if not os.path.exists(path) or os.path.getmtime(path) < max(
+                os.path.getmtime(os.path.join(ORACLE_DIR, f)) for f in ("ozaki2_ref.cpp", "reduced_ref.cpp")):
+            build()
+        L = ctypes.CDLL(path)
+        i64, ci = ctypes.c_int64, ctypes.c_int
+        L.oracle_oz2_constants.argtypes = [ci, _dp, _dp, _dp, _dp, _dp, _dp, _ip]
+        L.oracle_oz2_E.argtypes = [_dp, _dp, i64, i64, i64, ci, _dp, _dp]
+        L.oracle_oz2_exact_sub.argtypes = [_dp, _dp, _dp, i64, i64, i64, ci, ci, ci, _ip, _ip, _fp, _fp, _fp]
+        L.oz2_floor_log2_model.argtypes = [ctypes.c_double]
+        L.oz2_floor_log2_model.restype = ci
+        _lib = L
+    return _lib
+
+
+def _p(a, t=_dp):
+    return a.ctypes.data_as(t)
+
+
+def oz2_E(A, B, n_mod=16) -> int:
+    A = np.ascontiguousarray(A, dtype=np.float64)
+    B = np.ascontiguousarray(B, dtype=np.float64)
+    return lib().oracle_oz2_E(_p(A), _p(B), A.shape[0], A.shape[1], B.shape[1], n_mod, None, None)
+
+
+def oz2_exact(A, B, E=None, n_mod=16, flags=EXPFIELD, debug=False):
+    """Exact-tier product of the given rows of A and columns of B (both already
+    sliced).  E defaults to the value for these operands taken as the whole problem."""
+    A = np.ascontiguousarray(A, dtype=np.float64)
+    B = np.ascontiguousarray(B, dtype=np.float64)
+    m, K = A.shape
+    n = B.shape[1]
+    if E is None:
+        E = oz2_E(A, B, n_mod)
+    C = np.empty((m, n), dtype=np.float64)
+    if not debug:
+        rc = lib().oracle_oz2_exact_sub(_p(A), _p(B), _p(C), m, K, n, E, n_mod, flags, None, None, None, None, None)
+        assert rc == 0
+        return C
+    mu = np.empty(m, dtype=np.int32)
+    nu = np.empty(n, dtype=np.int32)
+    W = np.empty((n_mod, m, n), dtype=np.float32)
+    Ar = np.empty((n_mod, m, K), dtype=np.float32)
+    Br = np.empty((n_mod, K, n), dtype=np.float32)
+    rc = lib().oracle_oz2_exact_sub(_p(A), _p(B), _p(C), m, K, n, E, n_mod, flags, _p(mu, _ip), _p(nu, _ip),
+                                    _p(W, _fp), _p(Ar, _fp), _p(Br, _fp))
+    assert rc == 0
+    return C, {"mu": mu, "nu": nu, "W": W, "Ares": Ar, "Bres": Br, "E": E}
+
+
+def floor_log2_model(x: float) -> int:
+    return lib().oz2_floor_log2_model(float(x))
+
+
+def ref_lib(name: str):
+    """One of the reference-compiled libraries under oracle/_ref, or None if absent."""
+    path = os.path.join(ORACLE_DIR, "_ref", name)
+    if not os.path.exists(path):
+        return None
+    return ctypes.CDLL(path)
+
+
+def ref_matmul(A, B, blas: bool = False):
+    L = ref_lib("libref_matmul_blas.so" if blas else "libref_matmul_simd.so")
+    if L is None:
+        return None
+    A = np.ascontiguousarray(A, dtype=np.float64)
+    B = np.ascontiguousarray(B, dtype=np.float64)
+    C = np.zeros((A.shape[0], B.shape[1]), dtype=np.float64)
+    u64 = ctypes.c_uint64
+    L.eshkol_matmul_f64.argtypes = [_dp, _dp, _dp, u64, u64, u64]
+    L.eshkol_matmul_f64.restype = None
+    L.eshkol_matmul_f64(_p(A), _p(B), _p(C), A.shape[0], A.shape[1], B.shape[1])
+    return C
+
+
+def ref_conv2d(inp, ker, stride=1, pad=0):
+    L = ref_lib("libref_conv.so")
+    if L is None:
+        return None
+    inp = np.ascontiguousarray(inp, dtype=np.float64)
+    ker = np.ascontiguousarray(ker, dtype=np.float64)
+    b, ic, H, W = inp.shape
+    oc, _, kH, kW = ker.shape
+    i64 = ctypes.c_int64
+    L.ref_conv_out_dim.argtypes = [i64] * 4
+    L.ref_conv_out_dim.restype = i64
+    oH, oW = L.ref_conv_out_dim(H, kH, stride, pad), L.ref_conv_out_dim(W, kW, stride, pad)
+    out = np.zeros((b, oc, oH, oW), dtype=np.float64)
+    L.ref_conv2d.argtypes = [_dp, i64, i64, i64, i64, _dp, i64, i64, i64, i64, i64, _dp]
+    L.ref_conv2d.restype = None
+    L.ref_conv2d(_p(inp), b, ic, H, W, _p(ker), oc, kH, kW, stride, pad, _p(out))
+    return out

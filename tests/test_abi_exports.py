@@ -1,0 +1,131 @@
+"""The shared library loads without a GPU and exports every symbol include/*.h declares."""
+import ctypes
+import glob
+import os
+import re
+
+import numpy as np
+import pytest
+
+import eshkol_b200 as eb
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    names = set()
+    for path in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        text = open(path).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        for m in re.finditer(r"\b(eshkol_[a-z0-9_]+)\s*\(", text):
+            names.add(m.group(1))
+        for m in re.finditer(r"extern\s+size_t\s+(\w+)\s*;", text):
+            names.add(m.group(1))
+    return sorted(names)
+
+
+def test_headers_declare_the_reference_abi():
+    names = declared_symbols()
+    # the 32 functions + one global of inc/eshkol/backend/gpu/gpu_memory.h:90-474
+    for required in ["eshkol_gpu_init", "eshkol_gpu_shutdown", "eshkol_gpu_get_backend",
+                     "eshkol_gpu_backend_name", "eshkol_gpu_backend_available", "eshkol_gpu_supports_f64",
+                     "eshkol_gpu_has_fp64", "eshkol_gpu_alloc", "eshkol_gpu_alloc_aligned", "eshkol_gpu_free",
+                     "eshkol_gpu_wrap_host", "eshkol_gpu_sync", "eshkol_gpu_sync_async", "eshkol_gpu_wait",
+                     "eshkol_gpu_matmul_f64", "eshkol_gpu_matmul_f32", "g_gpu_threshold",
+                     "eshkol_gpu_set_threshold", "eshkol_gpu_get_threshold", "eshkol_gpu_should_use",
+                     "eshkol_gpu_elementwise_f64", "eshkol_gpu_reduce_f64", "eshkol_gpu_reduce_axis_f64",
+                     "eshkol_gpu_transpose_f64", "eshkol_gpu_softmax_f64", "eshkol_gpu_normalize_f64",
+                     "eshkol_gpu_conv2d_backward_input_f64", "eshkol_gpu_conv2d_backward_kernel_f64",
+                     "eshkol_gpu_batchnorm_backward_f64", "eshkol_gpu_layernorm_backward_f64",
+                     "eshkol_matmul_dispatch", "eshkol_batch_matmul_dispatch"]:
+        assert required in names, required
+
+
+def test_every_declared_symbol_is_exported():
+    lib = ctypes.CDLL(eb.library_path())
+    missing = [n for n in declared_symbols() if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+def test_buffer_struct_layout_is_the_references():
+    # inc/eshkol/backend/gpu/gpu_memory.h:60-68; mirrored by hand in lib/backend/vm_gpu_dispatch.h:60
+    assert ctypes.sizeof(eb.EshkolGPUBuffer) == 48
+    off = {f[0]: getattr(eb.EshkolGPUBuffer, f[0]).offset for f in eb.EshkolGPUBuffer._fields_}
+    assert off == {"host_ptr": 0, "device_ptr": 8, "size_bytes": 16, "mem_type": 24, "backend": 28,
+                   "flags": 32, "backend_data": 40}
+
+
+def test_threshold_and_names_without_gpu():
+    lib = eb.load_library()
+    assert lib.eshkol_gpu_get_threshold() == 100000 or lib.eshkol_gpu_get_threshold() > 0
+    old = lib.eshkol_gpu_get_threshold()
+    lib.eshkol_gpu_set_threshold(12345)
+    assert lib.eshkol_gpu_get_threshold() == 12345
+    assert ctypes.c_size_t.in_dll(lib, "g_gpu_threshold").value == 12345
+    lib.eshkol_gpu_set_threshold(old)
+    assert lib.eshkol_gpu_backend_name(2) == b"NVIDIA CUDA"
+    assert lib.eshkol_gpu_backend_name(0) == b"CPU (no GPU)"
+
+
+def _choose(monkeypatch, env, shape=(2048, 2048, 2048)):
+    for k in ["ESHKOL_B200_TIER", "ESHKOL_CUDA_F64_KERNEL", "ESHKOL_OZAKI_CUDA_T", "ESHKOL_MATMUL_ACCURACY",
+              "ESHKOL_OZAKI_FAST", "ESHKOL_SF64_KERNEL", "ESHKOL_OZAKI_FAST_MODULI", "ESHKOL_OZAKI_NUM_MODULI"]:
+        monkeypatch.delenv(k, raising=False)
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    t, p = ctypes.c_int(), ctypes.c_int()
+    eb.load_library().eshkol_b200_debug_choose_tier(*shape, ctypes.byref(t), ctypes.byref(p))
+    return t.value, p.value
+
+
+def test_tier_selection_follows_the_reference_switches(monkeypatch):
+    assert _choose(monkeypatch, {}) == (eb.TIER_OZAKI2, 16)
+    assert _choose(monkeypatch, {"ESHKOL_SF64_KERNEL": "ozaki", "ESHKOL_OZAKI_NUM_MODULI": "12"}) == (eb.TIER_OZAKI2, 12)
+    # out of range moduli count: loud, default kept (lib/backend/gpu/gpu_memory.mm:1309-1314)
+    assert _choose(monkeypatch, {"ESHKOL_OZAKI_NUM_MODULI": "17"}) == (eb.TIER_OZAKI2, 16)
+    # lib/backend/gpu/gpu_memory_cuda.cpp:310-326, 462-464
+    assert _choose(monkeypatch, {"ESHKOL_CUDA_F64_KERNEL": "ozaki-int8"}) == (eb.TIER_OZAKI1, 6)
+    assert _choose(monkeypatch, {"ESHKOL_CUDA_F64_KERNEL": "ozaki-int8", "ESHKOL_OZAKI_CUDA_T": "4"}) == (eb.TIER_OZAKI1, 4)
+    assert _choose(monkeypatch, {"ESHKOL_CUDA_F64_KERNEL": "ozaki-int8", "ESHKOL_OZAKI_CUDA_T": "99"}) == (eb.TIER_OZAKI1, 6)
+    assert _choose(monkeypatch, {"ESHKOL_CUDA_F64_KERNEL": "ozaki-int8"}, (512, 512, 512)) == (eb.TIER_OZAKI2, 16)
+    # accuracy budget: smallest T whose guaranteed error meets it (gpu_memory_cuda.cpp:485-487, 552-566)
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "fast"}) == (eb.TIER_OZAKI1, 1)
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "1e-9"}) == (eb.TIER_OZAKI1, 4)
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "exact"}) == (eb.TIER_OZAKI2, 16)
+    # fast tier (gpu_memory.mm:1320-1337)
+    assert _choose(monkeypatch, {"ESHKOL_OZAKI_FAST": "1"}) == (eb.TIER_OZAKI2_FAST, 11)
+    assert _choose(monkeypatch, {"ESHKOL_SF64_KERNEL": "ozaki-fast", "ESHKOL_OZAKI_FAST_MODULI": "14"}) == (eb.TIER_OZAKI2_FAST, 14)
+    assert _choose(monkeypatch, {"ESHKOL_OZAKI_FAST": "1", "ESHKOL_OZAKI_FAST_MODULI": "40"}) == (eb.TIER_OZAKI2_FAST, 16)
+    assert _choose(monkeypatch, {"ESHKOL_B200_TIER": "dgemm"}) == (eb.TIER_DGEMM, 0)
+
+
+def test_inputs_stream_is_drand48():
+    from eshkol_b200 import inputs
+    libc = ctypes.CDLL(None)
+    libc.drand48.restype = ctypes.c_double
+    libc.srand48(12345)
+    want = np.array([libc.drand48() for _ in range(4097)])
+    got = inputs.lcg_states(12345, 4097).astype(np.float64) / float(1 << 48)
+    assert np.array_equal(got, want)
+    import torch
+    st = inputs.lcg_states(12345, 4097, device="cpu").numpy().astype(np.uint64)
+    assert np.array_equal(st, inputs.lcg_states(12345, 4097))
+    u = inputs.uniform(1, (8, 8))
+    assert u.min() >= -1.0 and u.max() < 1.0
+    w = inputs.wide(2, (64, 64))
+    assert np.abs(w).max() < 2.0 ** 20 and np.abs(w[w != 0]).min() < 2.0 ** -12
+    f = inputs.full53(3, (4096,))
+    assert (np.frombuffer(((f + 1.0) / 2.0 * 2.0 ** 53).astype(np.uint64).tobytes(), dtype=np.uint64) & np.uint64(15)).any()
+
+
+def test_calls_fail_loudly_without_a_device():
+    lib = eb.load_library()
+    if lib.eshkol_gpu_init() == 1:
+        pytest.skip("a GPU is present")
+    a = np.ones((4, 4))
+    buf = eb.EshkolGPUBuffer()
+    assert lib.eshkol_gpu_matmul_f64(ctypes.byref(buf), ctypes.byref(buf), ctypes.byref(buf), 4, 4, 4) == -1
+    assert lib.eshkol_b200_gemm_f64_device(a.ctypes.data, a.ctypes.data, a.ctypes.data, 4, 4, 4, None) == -1
+    # the void dispatcher must not leave a plausible number behind
+    c = eb.matmul_dispatch(a, a)
+    assert np.isnan(c).all()

@@ -1,0 +1,168 @@
+"""Exact tier on the GPU against the CPU oracle, stage by stage and end to end (bit-exact)."""
+import numpy as np
+import pytest
+
+import eshkol_b200 as eb
+from eshkol_b200 import api, inputs
+import fixtures as fx
+import gpu_util as gu
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+
+MODULI = (256, 255, 253, 251, 247, 241, 239, 233, 229, 227, 223, 217, 211, 199, 197, 193)
+
+
+def check_stages(A, B, simt):
+    """scales, residue planes, product residues and C of one GEMM, each against the oracle"""
+    M, K = A.shape
+    N = B.shape[1]
+    C = gu.gemm(A, B, simt=simt)
+    Cref, d = ol.oz2_exact(A, B, 52, debug=True)
+    mu, _ = api.debug_fetch(0)
+    nu, _ = api.debug_fetch(1)
+    assert np.array_equal(mu[0, :M], d["mu"])
+    assert np.array_equal(nu[0, :N], d["nu"])
+    # modulus 256: representative in [-128, 128] with the reference's tie rule
+    a0, meta = api.debug_fetch(2)
+    lo, hi, odd = gu.decode_plane0(a0, K, meta, "A")
+    ra = d["Ares"][0].astype(np.int32)
+    assert np.array_equal(lo.astype(np.int32), ((ra + 128) % 256) - 128)
+    assert np.array_equal(hi, np.where(ra == 128, 16, 0))
+    assert np.array_equal(odd, (ra & 1) * 16)
+    b0, meta = api.debug_fetch(4)
+    lo, hi, odd = gu.decode_plane0(b0, K, meta, "B")
+    rb = d["Bres"][0].astype(np.int32).T
+    assert np.array_equal(lo.astype(np.int32), ((rb + 128) % 256) - 128)
+    assert np.array_equal(hi, np.where(rb == 128, 16, 0))
+    assert np.array_equal(odd, (rb & 1) * 16)
+    # odd moduli: canonical centred residue, same class as the reference's value
+    for l in (1, 2, 8, 15):
+        p = MODULI[l]
+        ap, _ = api.debug_fetch(3, l - 1)
+        got = ap[:, :K].astype(np.int32)
+        assert np.abs(got).max() <= (p - 1) // 2
+        assert not ((got - d["Ares"][l].astype(np.int32)) % p).any()
+        assert not ap[:, K:].any()
+        bp, _ = api.debug_fetch(5, l - 1)
+        got = bp[:, :K].astype(np.int32)
+        assert np.abs(got).max() <= (p - 1) // 2
+        assert not ((got - d["Bres"][l].astype(np.int32).T) % p).any()
+    # residues of the products
+    w0, _ = api.debug_fetch(6)
+    assert np.array_equal(w0[:M, :N].astype(np.int32), d["W"][0].astype(np.int32))
+    for l in range(1, 16):
+        wl, _ = api.debug_fetch(7, l - 1)
+        assert np.array_equal(wl[:M, :N].astype(np.int32), d["W"][l].astype(np.int32)), l
+    assert gu.same_bits(C, Cref)
+
+
+@pytest.mark.parametrize("simt", [True, False], ids=["cuda-core-products", "tcgen05-products"])
+def test_stages_small_ragged(gpu_lib, simt):
+    A = inputs.uniform(1, (200, 1100))
+    B = inputs.uniform(2, (1100, 300))
+    check_stages(A, B, simt)
+
+
+@pytest.mark.parametrize("simt", [True, False], ids=["cuda-core-products", "tcgen05-products"])
+def test_stages_full53_hits_the_mod256_tie_path(gpu_lib, simt):
+    A = inputs.full53(1, (256, 2100))
+    B = inputs.full53(2, (2100, 256))
+    d = ol.oz2_exact(A, B, 52, debug=True)[1]
+    assert (np.abs(d["Ares"][0]) == 128).any() and (np.abs(d["W"][0]) == 128).any()
+    check_stages(A, B, simt)
+
+
+@pytest.mark.parametrize("shape", [(1, 1, 1), (1, 7, 1), (3, 1008, 5), (129, 1009, 257), (128, 2016, 256),
+                                   (130, 127, 513), (257, 4000, 100)])
+def test_bit_exact_odd_shapes(gpu_lib, shape):
+    M, K, N = shape
+    A = inputs.full53(11, (M, K))
+    B = inputs.wide(12, (K, N), span=9, lo=-4)
+    assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, 52))
+
+
+def test_c1_512_cubed_bit_exact(gpu_lib):
+    A = inputs.uniform(1, (512, 512))
+    B = inputs.uniform(2, (512, 512))
+    assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, 52))
+
+
+def test_tile_n_128_variant_bit_exact(gpu_lib):
+    A = inputs.full53(5, (300, 1500))
+    B = inputs.full53(6, (1500, 400))
+    assert gu.same_bits(gu.gemm(A, B, tile_n=128), ol.oz2_exact(A, B, 52))
+
+
+def test_certificate_all_cells_match_oracle_and_25_match_exact_ints(gpu_lib):
+    a, b = fx.certificate_operands()
+    A, B = a.astype(np.float64), b.astype(np.float64)
+    C = gu.gemm(A, B)
+    for i in fx.CERT_POINTS:
+        for j in fx.CERT_POINTS:
+            assert C[i, j] == float(fx.exact_dot(a, b, i, j))
+    assert gu.same_bits(C, ol.oz2_exact(A, B, 52))
+
+
+@pytest.mark.parametrize("regime", [0, 1, 2, 3])
+def test_regimes_gate_and_bits(gpu_lib, regime):
+    n = 512
+    A, B = fx.regime_operands(regime, n)
+    C = gu.gemm(A, B)
+    rows = fx.probe_grid(n)
+    worst = max(fx.rel_err(C[i, j], fx.naive_dot(A, B, i, j)) for i in rows for j in rows)
+    assert worst < 1e-9
+    assert gu.same_bits(C, ol.oz2_exact(A, B, 52))
+
+
+def test_zero_rows_columns_and_signed_zero(gpu_lib):
+    A = inputs.uniform(3, (140, 300))
+    B = inputs.uniform(4, (300, 270))
+    A[5, :] = 0.0
+    A[130, :] = -0.0
+    B[:, 0] = 0.0
+    B[:, 269] = 0.0
+    C = gu.gemm(A, B)
+    assert gu.same_bits(C, ol.oz2_exact(A, B, 52))
+    assert not C[5].any() and not C[:, 0].any()
+
+
+def test_fewer_moduli_follow_the_reference_exponent_rule(gpu_lib):
+    A = inputs.uniform(7, (150, 700))
+    B = inputs.uniform(8, (700, 260))
+    for n_mod in (8, 12, 15):
+        E = ol.oz2_E(A, B, n_mod)
+        assert E < 52 or n_mod == 15
+        assert gu.same_bits(gu.gemm(A, B, param=n_mod), ol.oz2_exact(A, B, E, n_mod=n_mod))
+
+
+def test_ones_and_identity(gpu_lib):
+    # tests/gpu/gpu_scale_correctness_test.esk, tests/gpu/cuda_host_sync_regression_test.esk
+    n = 1024
+    assert np.all(gu.gemm(np.ones((n, n)), np.ones((n, n))) == float(n))
+    A = inputs.uniform(9, (50, 50))
+    assert gu.same_bits(gu.gemm(A, np.eye(50)), ol.oz2_exact(A, np.eye(50), 52))
+
+
+def test_fused_relu_and_bias(gpu_lib):
+    A = inputs.uniform(1, (130, 400))
+    B = inputs.uniform(2, (400, 300))
+    ref = ol.oz2_exact(A, B, 52)
+    got = gu.gemm(A, B, activation=1)
+    assert gu.same_bits(got, np.where(ref > 0.0, ref, 0.0))
+    bias = inputs.uniform(3, (130,))
+    got = gu.gemm(A, B, activation=1, bias=bias, bias_mode=1)
+    want = ref + bias[:, None]
+    assert gu.same_bits(got, np.where(want > 0.0, want, 0.0))
+
+
+def test_c2_4096_wide_exponent_sampled_rows_and_columns(gpu_lib):
+    n = 4096
+    A = inputs.wide(1, (n, n))
+    B = inputs.wide(2, (n, n))
+    C = gu.gemm(A, B)
+    rng = np.random.default_rng(0)
+    rows = np.sort(rng.choice(n, 24, replace=False))
+    cols = np.sort(rng.choice(n, 24, replace=False))
+    assert gu.same_bits(C[rows], ol.oz2_exact(A[rows], B, 52))
+    assert gu.same_bits(C[:, cols], ol.oz2_exact(A, np.ascontiguousarray(B[:, cols]), 52))
