@@ -106,6 +106,8 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_copy_d2h", ctypes.c_int, [vp, vp, ctypes.c_size_t])
     sig("eshkol_b200_elementwise_f64_device", ctypes.c_int, [vp, vp, vp, u64, ctypes.c_int])
     sig("eshkol_b200_sync_status", ctypes.c_int, [])
+    sig("eshkol_b200_set_phase_timing", None, [ctypes.c_int])
+    sig("eshkol_b200_get_phase_times", ctypes.c_int, [ctypes.POINTER(ctypes.c_float), ctypes.c_int])
     sig("eshkol_b200_launch_count", u64, [])
     sig("eshkol_b200_workspace_bytes", u64, [])
     sig("eshkol_b200_debug_fetch", ctypes.c_int, [ctypes.c_int, ctypes.c_int, vp, u64, ctypes.POINTER(u64)])

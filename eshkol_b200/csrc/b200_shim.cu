@@ -33,6 +33,10 @@ struct State {
   uint8_t* aux = nullptr;  // second scratch block (conv2d im2col operand)
   size_t aux_bytes = 0;
   PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
+  // optional per-stage timing of the Ozaki-II driver (CUDA events on the stream)
+  bool timing = false;
+  cudaEvent_t ev[8] = {};
+  bool ev_made = false, ev_valid = false;
   // layout of the last Ozaki-II GEMM, for eshkol_b200_debug_fetch
   struct Last {
     bool valid = false;
@@ -277,9 +281,14 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
   Oz2DeviceConsts hc;
   oz2_host_consts(n_mod, &hc, &log2P);
 
+  const bool timed = g.timing && g.ev_made;
+  g.ev_valid = false;
+#define B200_MARK(i) do { if (timed) B200_CHECK(cudaEventRecord(g.ev[i], st)); } while (0)
+  B200_MARK(0);
   B200_CHECK(launch_scan_rows(dA, M, K, amax, st));
   B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(bmax), st));
   g.launches += 2;
+  B200_MARK(1);
 
   // With all 16 moduli, log2 P - 1 - log2 K - 2 > 104 for every admissible K, so E
   // clamps to 52 whatever the data; fewer moduli need the data-dependent bound.
@@ -294,12 +303,15 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
   B200_CHECK(launch_scales(amax, M, E, mu, sa, sai, st));
   B200_CHECK(launch_scales(bmax, N, E, nu, sb, sbi, st));
   g.launches += 2;
+  B200_MARK(2);
 
   SplitPlanes pa{M, K, Kp, K0, n_chunks, last_seg, n_odd, a0, aodd, static_cast<long long>(a_stride)};
   SplitPlanes pb{N, K, Kp, K0, n_chunks, last_seg, n_odd, b0, bodd, static_cast<long long>(b_stride)};
   B200_CHECK(launch_split_a(dA, sa, pa, hc, st));
+  B200_MARK(3);
   B200_CHECK(launch_split_b(dB, sb, N, pb, hc, st));
   g.launches += 2;
+  B200_MARK(4);
 
   GemmJob jobs[16];
   fill_mod_job(&jobs[0], 0, 0, 0, 0);
@@ -329,6 +341,7 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
     SimtPlanes s1{aodd, static_cast<long long>(a_stride), static_cast<int>(Kp), bodd,
                   static_cast<long long>(b_stride), static_cast<int>(Kp), static_cast<int>(M), static_cast<int>(N)};
     B200_CHECK(launch_modgemm_simt(kEpiMod256, s0, p0, st));
+    B200_MARK(5);
     B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
   } else {
     CUtensorMap mA0, mB0, mA1, mB1;
@@ -337,9 +350,11 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
     if (make_plane_map(&mA1, aodd, Kp, M, n_odd, static_cast<long long>(a_stride), kBM)) return -1;
     if (make_plane_map(&mB1, bodd, Kp, N, n_odd, static_cast<long long>(b_stride), bn)) return -1;
     B200_CHECK(launch_modgemm(bn, kEpiMod256, mA0, mB0, p0, tiles_m * tiles_n, g.num_sms, st));
+    B200_MARK(5);
     B200_CHECK(launch_modgemm(bn, kEpiModI8, mA1, mB1, p1, tiles_m * tiles_n * n_odd, g.num_sms, st));
   }
   g.launches += 2;
+  B200_MARK(6);
 
   CrtArgs ca;
   ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = Np;
@@ -351,6 +366,9 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
   ca.pixels_per_image = o.pixels_per_image;
   B200_CHECK(launch_crt(ca, hc, st));
   g.launches += 1;
+  B200_MARK(7);
+#undef B200_MARK
+  g.ev_valid = timed;
 
   State::Last& L = g.last;
   L.valid = true; L.M = M; L.K = K; L.N = N; L.Kp = Kp; L.K0 = K0; L.Mp = Mp; L.Np = Np;
@@ -408,6 +426,7 @@ void eshkol_b200_shutdown(void) {
   if (g.ws) cudaFree(g.ws);
   if (g.aux) cudaFree(g.aux);
   if (g.d_status) cudaFree(g.d_status);
+  if (g.ev_made) for (int i = 0; i < 8; ++i) cudaEventDestroy(g.ev[i]);
   cudaStreamDestroy(g.stream);
   g = State();
 }
@@ -507,6 +526,25 @@ int eshkol_b200_sync_status(void) {
     cudaStreamSynchronize(g.stream);
   }
   return h;
+}
+
+void eshkol_b200_set_phase_timing(int on) {
+  if (!g.ready) return;
+  if (on && !g.ev_made) {
+    for (int i = 0; i < 8; ++i)
+      if (cudaEventCreate(&g.ev[i]) != cudaSuccess) { cudaGetLastError(); return; }
+    g.ev_made = true;
+  }
+  g.timing = on != 0;
+  g.ev_valid = false;
+}
+
+int eshkol_b200_get_phase_times(float* ms, int capacity) {
+  if (!g.ready || !ms || capacity < 7 || !g.ev_valid) return -1;
+  if (cudaStreamSynchronize(g.stream) != cudaSuccess) { cudaGetLastError(); return -1; }
+  for (int i = 0; i < 7; ++i)
+    if (cudaEventElapsedTime(&ms[i], g.ev[i], g.ev[i + 1]) != cudaSuccess) { cudaGetLastError(); return -1; }
+  return 7;
 }
 
 uint64_t eshkol_b200_launch_count(void) { return g.launches; }

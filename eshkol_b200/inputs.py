@@ -9,7 +9,7 @@ project's own definitions of the benchmark configurations:
   uniform       2u - 1                                   (one draw per element)
   wide          (2u - 1) * 2^k, k = floor(41 u') - 20    (two draws per element)
   normal        Box-Muller on consecutive draws, scaled  (two draws per pair)
-  full53        53-bit mantissas from two draws, 2u - 1  (parity only)
+  full53        +-m/2^53, m a 53-bit integer from two draws  (parity only)
 """
 from __future__ import annotations
 
@@ -66,9 +66,23 @@ def xp_device(xp):
     return xp.device
 
 
-def lcg_states(seed: int, n: int, device=None):
-    """states 1..n of the stream seeded with `seed` (numpy uint64, or torch int64 on `device`)."""
-    s0 = seed_state(seed)
+def _advance(state: int, steps: int) -> int:
+    """state after `steps` LCG steps, by square-and-multiply on the affine map"""
+    am, cm = _A, _C
+    acc_a, acc_c = 1, 0
+    while steps:
+        if steps & 1:
+            acc_a, acc_c = (acc_a * am) & _MASK, (acc_c * am + cm) & _MASK
+        cm = (am * cm + cm) & _MASK
+        am = (am * am) & _MASK
+        steps >>= 1
+    return (acc_a * state + acc_c) & _MASK
+
+
+def lcg_states(seed: int, n: int, device=None, start: int = 0):
+    """states start+1..start+n of the stream seeded with `seed` (numpy uint64, or torch
+    int64 on `device`)."""
+    s0 = _advance(seed_state(seed), start)
     if device is None:
         A, Cc = _skip_tables(n, np)
         with np.errstate(over="ignore"):
@@ -85,10 +99,11 @@ def _to_unit(states, device):
     return states.to(torch.float64) * (1.0 / float(1 << 48))
 
 
-def uniform(seed: int, shape, device=None):
-    """entries 2u - 1 in [-1, 1), row-major fill order"""
+def uniform(seed: int, shape, device=None, start: int = 0):
+    """entries 2u - 1 in [-1, 1), row-major fill order; `start` skips that many elements
+    of the stream (a row shard of a larger matrix)"""
     n = int(np.prod(shape))
-    u = _to_unit(lcg_states(seed, n, device), device)
+    u = _to_unit(lcg_states(seed, n, device, start), device)
     return (2.0 * u - 1.0).reshape(*shape)
 
 
@@ -129,12 +144,17 @@ def normal(seed: int, shape, device=None, scale: float = 1.0):
 
 
 def full53(seed: int, shape, device=None):
-    """2u - 1 with u carrying 53 random mantissa bits (48 from one draw, 5 from the next)"""
+    """+-m / 2^53 with m a 53-bit integer built from the high bits of two draws (32 of
+    the first, 21 of the second; the sign is bit 20 of the second).  The low bits of
+    the LCG states have short periods and are not used.  Every mantissa bit down to
+    2^-53 varies, so the scaled operands take odd as well as even integer values."""
     n = int(np.prod(shape))
     st = lcg_states(seed, 2 * n, device)
     if device is None:
-        hi = st[0::2].astype(np.float64) * 32.0 + (st[1::2] >> np.uint64(43)).astype(np.float64)
-        return (2.0 * (hi * (1.0 / float(1 << 53))) - 1.0).reshape(*shape)
+        m = ((st[0::2] >> np.uint64(16)) << np.uint64(21)) | (st[1::2] >> np.uint64(27))
+        sign = 1.0 - 2.0 * ((st[1::2] >> np.uint64(20)) & np.uint64(1)).astype(np.float64)
+        return (sign * (m.astype(np.float64) * (1.0 / float(1 << 53)))).reshape(*shape)
     import torch
-    hi = st[0::2].to(torch.float64) * 32.0 + (st[1::2] >> 43).to(torch.float64)
-    return (2.0 * (hi * (1.0 / float(1 << 53))) - 1.0).reshape(*shape)
+    m = ((st[0::2] >> 16) << 21) | (st[1::2] >> 27)
+    sign = 1.0 - 2.0 * ((st[1::2] >> 20) & 1).to(torch.float64)
+    return (sign * (m.to(torch.float64) * (1.0 / float(1 << 53)))).reshape(*shape)

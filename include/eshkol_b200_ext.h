@@ -94,6 +94,16 @@ int eshkol_b200_elementwise_f64_device(const double* a, const double* b, double*
  * kernel ran out, or -1 on a CUDA error. */
 int eshkol_b200_sync_status(void);
 
+/* Per-stage timing of the Ozaki-II driver, the counterpart of the reference's
+ * ESHKOL_OZAKI_PROFILE line (lib/backend/gpu/gpu_memory.mm:2479, 2658-2664).  When
+ * switched on, CUDA events on the library stream bracket each stage of every
+ * Ozaki-II GEMM.  get_phase_times waits for the stream and writes the durations
+ * of the LAST such GEMM in milliseconds: [0] row/column scan, [1] scales,
+ * [2] split A, [3] split B, [4] products modulo 256, [5] products modulo the odd
+ * moduli, [6] reconstruction.  Returns 7, or -1 when nothing was timed. */
+void eshkol_b200_set_phase_timing(int on);
+int eshkol_b200_get_phase_times(float* ms, int capacity);
+
 /* Number of kernels this library has launched since init (monotonic). */
 uint64_t eshkol_b200_launch_count(void);
 

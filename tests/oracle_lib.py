@@ -34,6 +34,9 @@ def lib() -> ctypes.CDLL:
         L.oracle_oz2_constants.argtypes = [ci, _dp, _dp, _dp, _dp, _dp, _dp, _ip]
         L.oracle_oz2_E.argtypes = [_dp, _dp, i64, i64, i64, ci, _dp, _dp]
         L.oracle_oz2_exact_sub.argtypes = [_dp, _dp, _dp, i64, i64, i64, ci, ci, ci, _ip, _ip, _fp, _fp, _fp]
+        L.oracle_oz1.argtypes = [_dp, _dp, _dp, i64, i64, i64, ci, ci]
+        L.oracle_fast_integerise.argtypes = [_dp, _dp, i64, i64, i64, ctypes.c_double, _ip, _ip,
+                                             ctypes.POINTER(ctypes.c_int64), ctypes.POINTER(ctypes.c_int64)]
         L.oz2_floor_log2_model.argtypes = [ctypes.c_double]
         L.oz2_floor_log2_model.restype = ci
         _lib = L
@@ -73,6 +76,49 @@ def oz2_exact(A, B, E=None, n_mod=16, flags=EXPFIELD, debug=False):
                                     _p(W, _fp), _p(Ar, _fp), _p(Br, _fp))
     assert rc == 0
     return C, {"mu": mu, "nu": nu, "W": W, "Ares": Ar, "Bres": Br, "E": E}
+
+
+def oz1(A, B, T=6, max_pairs=8):
+    """Ozaki-I restatement; max_pairs models the library's per-accumulator pair limit."""
+    A = np.ascontiguousarray(A, dtype=np.float64)
+    B = np.ascontiguousarray(B, dtype=np.float64)
+    C = np.empty((A.shape[0], B.shape[1]), dtype=np.float64)
+    rc = lib().oracle_oz1(_p(A), _p(B), _p(C), A.shape[0], A.shape[1], B.shape[1], T, max_pairs)
+    assert rc == 0
+    return C
+
+
+MODULI = (256, 255, 253, 251, 247, 241, 239, 233, 229, 227, 223, 217, 211, 199, 197, 193)
+
+
+def fast_exact_reference(A, B, n_mod=11):
+    """What an error-free fast tier returns: the exact integer product of the
+    round-half-up integerised operands, reduced to the centred residue modulo P and
+    scaled back (python integers; small shapes only)."""
+    import math
+    A = np.ascontiguousarray(A, dtype=np.float64)
+    B = np.ascontiguousarray(B, dtype=np.float64)
+    M, K = A.shape
+    N = B.shape[1]
+    P = 1
+    for p in MODULI[:n_mod]:
+        P *= p
+    log2P = math.log2(float(P))
+    er = np.empty(M, dtype=np.int32)
+    ec = np.empty(N, dtype=np.int32)
+    Ai = np.empty((M, K), dtype=np.int64)
+    Bi = np.empty((K, N), dtype=np.int64)
+    i64p = ctypes.POINTER(ctypes.c_int64)
+    E = lib().oracle_fast_integerise(_p(A), _p(B), M, K, N, log2P, _p(er, _ip), _p(ec, _ip), _p(Ai, i64p), _p(Bi, i64p))
+    X = Ai.astype(object) @ Bi.astype(object)
+    C = np.empty((M, N), dtype=np.float64)
+    for i in range(M):
+        for j in range(N):
+            x = int(X[i, j]) % P
+            if 2 * x >= P:
+                x -= P
+            C[i, j] = math.ldexp(float(x), int(er[i]) + int(ec[j]) - 2 * E)
+    return C, E
 
 
 def floor_log2_model(x: float) -> int:

@@ -1,0 +1,194 @@
+"""Reduced-precision tiers, conv2d and the host-pointer dispatchers on the GPU."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import eshkol_b200 as eb
+from eshkol_b200 import api, inputs
+import fixtures as fx
+import gpu_util as gu
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+
+# guaranteed relative error of the slice tiers (lib/backend/gpu/gpu_memory_cuda.cpp:485-487)
+OZAKI_TOL = {1: 1e-3, 2: 1e-5, 3: 1e-7, 4: 1e-9, 5: 1e-11, 6: 1e-13, 7: 1e-14}
+# published worst-case errors of the fast tier (docs/breakdown/GPU_ACCELERATION.md:173-179)
+FAST_TOL = {10: 2.2e-7, 11: 2.4e-8, 12: 4.0e-8, 14: 6e-11}
+
+
+def normwise(got, ref):
+    return float(np.linalg.norm((got - ref).astype(np.float64)) / np.linalg.norm(ref.astype(np.float64)))
+
+
+def true_product(A, B):
+    """the product in 80-bit arithmetic: the 'exact f64 reference' the tier bounds are stated against"""
+    return (A.astype(np.longdouble) @ B.astype(np.longdouble))
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 4, 5, 6, 7])
+def test_ozaki1_bits_match_restatement_and_meet_the_tier_bound(gpu_lib, T):
+    A = inputs.normal(1, (200, 900))
+    B = inputs.normal(2, (900, 300))
+    got = gu.gemm(A, B, tier=eb.TIER_OZAKI1, param=T)
+    assert gu.same_bits(got, ol.oz1(A, B, T))
+    assert normwise(got, true_product(A, B)) < OZAKI_TOL[T]
+
+
+def test_ozaki1_cuda_core_and_tensor_core_products_agree(gpu_lib):
+    A = inputs.wide(3, (130, 1300), span=9, lo=-4)
+    B = inputs.wide(4, (1300, 270), span=9, lo=-4)
+    a = gu.gemm(A, B, tier=eb.TIER_OZAKI1, param=6, simt=True)
+    b = gu.gemm(A, B, tier=eb.TIER_OZAKI1, param=6)
+    assert gu.same_bits(a, b)
+
+
+@pytest.mark.parametrize("regime", [0, 1, 2, 3])
+def test_ozaki1_reference_gate(gpu_lib, regime):
+    # tests/gpu/cuda_ozaki_correctness_gate.sh:99-118: T=6 normwise < 1e-9, T=4 < 1e-6 over the probe grid
+    n = 1024
+    A, B = fx.regime_operands(regime, n)
+    rows = fx.probe_grid(n)
+    ref = np.array([[fx.naive_dot(A, B, i, j) for j in rows] for i in rows])
+    for T, tol in ((6, 1e-9), (4, 1e-6)):
+        C = gu.gemm(A, B, tier=eb.TIER_OZAKI1, param=T)
+        assert normwise(C[np.ix_(rows, rows)], ref) < tol
+
+
+@pytest.mark.parametrize("n_mod", [10, 11, 12, 14, 16])
+def test_fast_tier_within_published_bounds(gpu_lib, n_mod):
+    A = inputs.normal(5, (96, 700))
+    B = inputs.normal(6, (700, 80))
+    got = gu.gemm(A, B, tier=eb.TIER_OZAKI2_FAST, param=n_mod)
+    # against an error-free evaluation of the same scheme: only the f64 fractional CRT differs
+    ideal, E = ol.fast_exact_reference(A, B, n_mod)
+    assert normwise(got, ideal) < 1e-10
+    # against the true product: the tier's documented accuracy (normwise; cells that
+    # cancel to almost nothing have no meaningful element-wise relative error)
+    assert normwise(got, true_product(A, B)) < FAST_TOL.get(n_mod, 1e-10), (n_mod, E)
+
+
+@pytest.mark.parametrize("regime", [0, 1, 2, 3])
+def test_fast_tier_reference_gate(gpu_lib, regime):
+    # tests/gpu/ozaki_fast_test.esk:13: max rel err < 1e-7 at the default 11 moduli
+    n = 512
+    A, B = fx.regime_operands(regime, n)
+    C = gu.gemm(A, B, tier=eb.TIER_OZAKI2_FAST, param=11)
+    rows = fx.probe_grid(n)
+    assert max(fx.rel_err(C[i, j], fx.naive_dot(A, B, i, j)) for i in rows for j in rows) < 1e-7
+
+
+def test_native_dgemm_tier(gpu_lib):
+    A = inputs.uniform(7, (150, 333))
+    B = inputs.uniform(8, (333, 97))
+    got = gu.gemm(A, B, tier=eb.TIER_DGEMM)
+    assert np.max(np.abs(got - A @ B)) < 1e-12
+
+
+def _conv_gpu(inp, ker, stride, pad, activation=0):
+    return api.conv2d(inp, ker, stride, pad, activation)
+
+
+@pytest.mark.parametrize("case", range(len(fx.CONV_CASES)))
+def test_conv_known_answers(gpu_lib, case):
+    ishape, ival, kshape, kval, stride, pad, oshape, oval = fx.CONV_CASES[case]
+    inp = np.array(ival, dtype=np.float64).reshape(ishape)
+    ker = np.array(kval, dtype=np.float64).reshape(kshape)
+    got = _conv_gpu(inp, ker, stride, pad)
+    assert got.shape == tuple(oshape)
+    assert np.allclose(got, np.array(oval, dtype=np.float64).reshape(oshape), rtol=0, atol=1e-9)
+
+
+@pytest.mark.parametrize("cfg", [(2, 5, 13, 11, 7, 3, 3, 1, 1), (3, 4, 9, 9, 6, 2, 3, 2, 0), (1, 3, 8, 8, 130, 3, 3, 1, 1)])
+def test_conv_bits_match_oracle_on_the_lowered_operands(gpu_lib, cfg):
+    b, ic, H, W, oc, kH, kW, stride, pad = cfg
+    inp = inputs.normal(1, (b, ic, H, W), scale=0.1)
+    ker = inputs.normal(2, (oc, ic, kH, kW), scale=0.1)
+    got = _conv_gpu(inp, ker, stride, pad, activation=1)
+    col, oH, oW = fx.im2col(inp, kH, kW, stride, pad)
+    low = ol.oz2_exact(ker.reshape(oc, -1), col, 52).reshape(oc, b, oH, oW).transpose(1, 0, 2, 3)
+    assert gu.same_bits(got, np.where(low > 0.0, low, 0.0))
+    # against the direct loop: every cell to rounding except the few that carry the
+    # exact tier's own 2^-25-relative CRT rounding (parity status)
+    direct = fx.conv2d_numpy(inp, ker, stride, pad)
+    direct = np.where(direct > 0.0, direct, 0.0)
+    err = np.abs(got - direct)
+    assert np.median(err) < 1e-15 and np.mean(err < 1e-12) > 0.95 and err.max() < 1e-7
+
+
+def test_conv_c4_shape_sampled(gpu_lib):
+    # batch 32, 64 -> 128 channels, 56x56, 3x3, stride 1, pad 1, fused ReLU
+    inp = inputs.normal(1, (32, 64, 56, 56), scale=0.1)
+    ker = inputs.normal(2, (128, 64, 3, 3), scale=0.1)
+    got = _conv_gpu(inp, ker, 1, 1, activation=1)
+    assert got.shape == (32, 128, 56, 56)
+    # bits on sampled output pixels: oracle on the matching im2col columns
+    col, oH, oW = fx.im2col(inp[[0, 31]], 3, 3, 1, 1)
+    cols = np.array([0, 57, 3135, 3136 + 1000, 2 * 3136 - 1])
+    low = ol.oz2_exact(ker.reshape(128, -1), np.ascontiguousarray(col[:, cols]), 52)
+    low = np.where(low > 0.0, low, 0.0)
+    flat = got[[0, 31]].transpose(1, 0, 2, 3).reshape(128, -1)
+    assert gu.same_bits(np.ascontiguousarray(flat[:, cols]), low)
+    ref = ol.ref_conv2d(inp[:1], ker, 1, 1)
+    if ref is not None:
+        err = np.abs(got[0] - np.where(ref[0] > 0.0, ref[0], 0.0))
+        assert np.mean(err < 1e-12) > 0.95 and err.max() < 1e-6
+
+
+def test_dispatch_on_host_pointers(gpu_lib):
+    gpu_lib.eshkol_gpu_set_threshold(1)  # as the reference's GPU gates do with ESHKOL_GPU_THRESHOLD=1
+    try:
+        assert np.array_equal(eb.matmul_dispatch([[1, 2], [3, 4]], [[5, 6], [7, 8]]), [[19, 22], [43, 50]])
+        assert np.array_equal(eb.matmul_dispatch([[1, 2, 3], [4, 5, 6]], [[7, 8], [9, 10], [11, 12]]),
+                              [[58, 64], [139, 154]])
+        A = inputs.uniform(1, (50, 50))
+        assert gu.same_bits(eb.matmul_dispatch(A, np.eye(50)), ol.oz2_exact(A, np.eye(50), 52))
+        assert np.array_equal(eb.matmul_dispatch(np.arange(64.0).reshape(8, 8) - 17.0, np.eye(8)),
+                              np.arange(64.0).reshape(8, 8) - 17.0)
+        A = inputs.full53(3, (333, 777))[:, 1:]          # unaligned, non-contiguous source made contiguous
+        B = inputs.full53(4, (776, 201))
+        assert gu.same_bits(eb.matmul_dispatch(A, B), ol.oz2_exact(np.ascontiguousarray(A), B, 52))
+        a = inputs.uniform(5, (3, 40, 64))
+        b = inputs.uniform(6, (3, 64, 24))
+        c = eb.batch_matmul_dispatch(a, b)
+        for i in range(3):
+            assert gu.same_bits(c[i], ol.oz2_exact(a[i], b[i], 52))
+    finally:
+        gpu_lib.eshkol_gpu_set_threshold(100000)
+
+
+def test_buffer_api_round_trip_like_the_vm(gpu_lib):
+    # lib/backend/vm_gpu_dispatch.h:62-86: wrap three host arrays, multiply, free (no explicit sync)
+    A = inputs.uniform(1, (120, 256))
+    B = inputs.uniform(2, (256, 140))
+    C = np.zeros((120, 140))
+    ba, bb, bc = eb.EshkolGPUBuffer(), eb.EshkolGPUBuffer(), eb.EshkolGPUBuffer()
+    assert gpu_lib.eshkol_gpu_wrap_host(A.ctypes.data, A.nbytes, ctypes.byref(ba)) == 0
+    assert gpu_lib.eshkol_gpu_wrap_host(B.ctypes.data, B.nbytes, ctypes.byref(bb)) == 0
+    assert gpu_lib.eshkol_gpu_wrap_host(C.ctypes.data, C.nbytes, ctypes.byref(bc)) == 0
+    assert gpu_lib.eshkol_gpu_matmul_f64(ctypes.byref(ba), ctypes.byref(bb), ctypes.byref(bc), 120, 256, 140) == 0
+    for b in (ba, bb, bc):
+        gpu_lib.eshkol_gpu_free(ctypes.byref(b))
+    assert bc.device_ptr is None and bc.size_bytes == 0
+    assert gu.same_bits(C, ol.oz2_exact(A, B, 52))
+    # device buffers + elementwise ReLU (lib/backend/gpu/gpu_cuda_kernels.cu:37)
+    x = eb.EshkolGPUBuffer()
+    assert gpu_lib.eshkol_gpu_alloc(C.nbytes, 3, ctypes.byref(x)) == 0  # unified: host_ptr == device_ptr
+    assert x.host_ptr == x.device_ptr
+    v = np.ctypeslib.as_array(ctypes.cast(x.host_ptr, ctypes.POINTER(ctypes.c_double)), shape=(C.size,))
+    v[:] = np.linspace(-1, 1, C.size)
+    v[0] = float("nan")
+    assert gpu_lib.eshkol_gpu_elementwise_f64(ctypes.byref(x), None, ctypes.byref(x), C.size, 11) == 0
+    assert v[0] == 0.0 and v.min() == 0.0 and v[-1] == 1.0
+    gpu_lib.eshkol_gpu_free(ctypes.byref(x))
+
+
+def test_k_beyond_int32_bound_is_refused_loudly(gpu_lib):
+    import torch
+    a = torch.zeros((1, 131072), dtype=torch.float64, device="cuda")
+    b = torch.zeros((131072, 1), dtype=torch.float64, device="cuda")
+    c = torch.zeros((1, 1), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    rc = gpu_lib.eshkol_b200_gemm_f64_device(a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, 131072, 1, None)
+    assert rc == -1
