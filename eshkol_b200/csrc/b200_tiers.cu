@@ -7,9 +7,9 @@
 //    per pair.
 //  * Ozaki-II fast: restates ozaki_ii_fast_dispatch and its three shaders,
 //    lib/backend/gpu/gpu_memory.mm:2816-3012 and
-//    lib/backend/gpu/metal_softfloat.h:4150-4246, with the fractional CRT carried in
-//    f64 and the exact tier's moduli (int32 accumulation lifts the cap the f32 GEMM
-//    imposed on them).
+//    lib/backend/gpu/metal_softfloat.h:4150-4246, with the CRT carried in exact 128-bit
+//    integers instead of double-float and the exact tier's moduli (int32 accumulation
+//    lifts the cap the f32 GEMM imposed on them).
 //  * native f64 GEMM on CUDA cores: the stand-in for the reference's cublasDgemm call.
 //  * conv2d: explicit im2col of the input, then the chosen GEMM tier with the NCHW
 //    scatter and optional bias / ReLU fused into its last pass.
@@ -293,29 +293,53 @@ __global__ void __launch_bounds__(256) fast_split_b_kernel(const double* __restr
   }
 }
 
-// metal_softfloat.h:4192-4245 in f64: S = sum_l ((G_l mod p)*q_l mod p)/p kept
-// modulo 1, centred to [-1/2, 1/2), times P * 2^(e_i + f_j - 2E).
+// The fractional CRT of metal_softfloat.h:4192-4245, carried out in exact 128-bit
+// integer arithmetic instead of double-float: x = sum_l u_l * (P/p_l) mod P with
+// u_l = (G_l mod p_l) * q_l mod p_l, centred to [-P/2, P/2), converted to f64 with one
+// round-to-nearest-even, then scaled by 2^(e_i + f_j - 2E).  No rounding happens before
+// the final conversion, so the tier's only error is the integerisation of the inputs.
+struct FastCrtConsts {
+  unsigned long long P_hi, P_lo;
+  unsigned long long Pp_hi[16], Pp_lo[16];  // P / p_l
+  int p[16], q[16];
+  int n_mod;
+};
+
+__device__ __forceinline__ double u128_to_double_rne(unsigned __int128 v) {
+  const unsigned long long hi = static_cast<unsigned long long>(v >> 64);
+  const unsigned long long lo = static_cast<unsigned long long>(v);
+  if (hi == 0) return __ull2double_rn(lo);
+  const int lz = __clzll(static_cast<long long>(hi));
+  const unsigned __int128 n = v << lz;                       // leading one at bit 127
+  unsigned long long mant = static_cast<unsigned long long>(n >> 75);  // top 53 bits
+  const unsigned __int128 rest = n & ((static_cast<unsigned __int128>(1) << 75) - 1);
+  const unsigned __int128 half = static_cast<unsigned __int128>(1) << 74;
+  if (rest > half || (rest == half && (mant & 1ull))) ++mant;
+  return ldexp(static_cast<double>(mant), 75 - lz);
+}
+
 __global__ void __launch_bounds__(256) fast_crt_kernel(const int8_t* __restrict__ W,
                                                        long long w_stride, long long ldw,
                                                        const int* __restrict__ erow,
                                                        const int* __restrict__ ecol, int E,
                                                        const Epilogue ep,
-                                                       const __grid_constant__ Oz2DeviceConsts c) {
+                                                       const __grid_constant__ FastCrtConsts c) {
   const long long i = blockIdx.x;
   const long long j4 = (static_cast<long long>(blockIdx.y) * 256 + threadIdx.x) * 4;
   if (j4 >= ep.N) return;
-  double S[4] = {0.0, 0.0, 0.0, 0.0};
+  const unsigned __int128 P = (static_cast<unsigned __int128>(c.P_hi) << 64) | c.P_lo;
+  unsigned __int128 S[4] = {0, 0, 0, 0};
   for (int l = 0; l < c.n_mod; ++l) {
     const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(W + l * w_stride + i * ldw + j4));
-    const int p = c.p_i[l], q = c.q_i[l];
-    const double pd = c.p_d[l];
+    const int p = c.p[l], q = c.q[l];
+    const unsigned __int128 Pp = (static_cast<unsigned __int128>(c.Pp_hi[l]) << 64) | c.Pp_lo[l];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       int gg = static_cast<int8_t>((w >> (8 * e)) & 0xffu);
       gg = (gg < 0) ? gg + p : gg;
-      const int u = (gg * q) % p;
-      double t = S[e] + static_cast<double>(u) / pd;
-      S[e] = t - floor(t);
+      const unsigned u = static_cast<unsigned>(gg * q) % static_cast<unsigned>(p);
+      unsigned __int128 t = S[e] + Pp * u;   // both < P < 2^126: no overflow
+      S[e] = (t >= P) ? t - P : t;
     }
   }
   const int ei = erow[i];
@@ -323,9 +347,11 @@ __global__ void __launch_bounds__(256) fast_crt_kernel(const int8_t* __restrict_
   for (int e = 0; e < 4; ++e) {
     const long long j = j4 + e;
     if (j >= ep.N) break;
-    double f = S[e] - floor(S[e]);
-    if (f >= 0.5) f -= 1.0;
-    store_out(ep, i, j, ldexp(f * c.P1, ei + ecol[j] - 2 * E));
+    const unsigned __int128 rem = P - S[e];
+    const bool neg = S[e] >= rem;            // 2S >= P: the centred value is S - P
+    double x = u128_to_double_rne(neg ? rem : S[e]);
+    x = neg ? -x : x;
+    store_out(ep, i, j, ldexp(x, ei + ecol[j] - 2 * E));
   }
 }
 
@@ -647,8 +673,22 @@ int ozaki2_fast_gemm(const double* dA, const double* dB, double* dC, long long M
   }
   {
     const dim3 grid(static_cast<unsigned>(M), static_cast<unsigned>((N + 1023) / 1024));
+    FastCrtConsts fc;
+    memset(&fc, 0, sizeof(fc));
+    unsigned __int128 P = 1;
+    for (int l = 0; l < n_mod; ++l) P *= static_cast<unsigned>(hc.p_i[l]);
+    fc.P_hi = static_cast<unsigned long long>(P >> 64);
+    fc.P_lo = static_cast<unsigned long long>(P);
+    for (int l = 0; l < n_mod; ++l) {
+      const unsigned __int128 Pp = P / static_cast<unsigned>(hc.p_i[l]);
+      fc.Pp_hi[l] = static_cast<unsigned long long>(Pp >> 64);
+      fc.Pp_lo[l] = static_cast<unsigned long long>(Pp);
+      fc.p[l] = hc.p_i[l];
+      fc.q[l] = hc.q_i[l];
+    }
+    fc.n_mod = n_mod;
     fast_crt_kernel<<<grid, 256, 0, st>>>(wp, static_cast<long long>(w_stride), Np, er, ec, E,
-                                          make_epilogue(dC, M, N, o), hc);
+                                          make_epilogue(dC, M, N, o), fc);
     TIER_CHECK(cudaGetLastError());
   }
   count_launches(8);

@@ -32,8 +32,8 @@ typedef enum {
    * means 6).  Reference: cuda_matmul_ozaki_int8_f64,
    * lib/backend/gpu/gpu_memory_cuda.cpp:339-452. */
   ESHKOL_B200_TIER_OZAKI1 = 1,
-  /* Ozaki-II "fast" tier: frexp exponents, round-half-up significand shift,
-   * fractional CRT in f64, `param` moduli (2..16; 0 means 11).
+  /* Ozaki-II "fast" tier: frexp exponents, round-half-up significand shift, CRT in
+   * exact 128-bit integers, `param` moduli (2..16; 0 means 11).
    * Reference: ozaki_ii_fast_dispatch, lib/backend/gpu/gpu_memory.mm:2816-3012. */
   ESHKOL_B200_TIER_OZAKI2_FAST = 2,
   /* Native f64 FMA GEMM on the CUDA cores (the stand-in for cublasDgemm,
