@@ -66,6 +66,22 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC,
                                 uint64_t M, uint64_t K, uint64_t N,
                                 const EshkolB200GemmOpts* opts);
 
+/* The same exact-tier product (16 moduli, identical bits) for callers that must not
+ * allocate: a host whose own arena already owns all device memory, so that
+ * cudaMalloc would fail, or one that cannot take the device-wide synchronisation
+ * and possible out-of-memory failure of cudaMalloc / cudaFree next to its other
+ * streams.  Every intermediate lives in a fixed 24 MiB array inside the library
+ * (held by each GPU that loads it, until exit); no allocating routine is called.
+ * A, B and C are device pointers owned by the caller.  Shapes whose scratch need
+ * exceeds the array (roughly 18*(M+N)*K + 17*M*N bytes after padding; 512x512x512
+ * and 256x2048x256 fit) are refused with a message and -1.  Calls share the array:
+ * they are ordered on the library stream and must not be made to overlap on the GPU.
+ * The first call on a device resolves the array's address and should come before
+ * any stream capture.  Asynchronous.  This entry point has no counterpart in the
+ * reference. */
+int eshkol_b200_gemm_f64_static_scratch(const double* dA, const double* dB, double* dC,
+                                        uint64_t M, uint64_t K, uint64_t N);
+
 /* conv2d forward, NCHW cross-correlation with zero padding, lowered to the same
  * GEMM: out[b][oc][oh][ow] = sum_{ic,kh,kw} in[b][ic][oh*s+kh-p][ow*s+kw-p] * ker[oc][ic][kh][kw].
  * Device pointers; out is [batch][out_c][oH][oW].  Asynchronous.
