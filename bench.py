@@ -179,29 +179,27 @@ def run_b200(args):
     lib_stream = torch.cuda.ExternalStream(api.stream_handle(), device=dev)
 
     n = 8192 if world == 1 else 32768
-    rows = n // world
-    gen = inputs.normal if world == 1 else inputs.uniform
-    if world == 1:
-        A = gen(1, (n, n), device=dev)
-        B = gen(2, (n, n), device=dev)
-    else:
-        A = inputs.uniform(1, (rows, n), device=dev, start=rank * rows * n)
-        B = inputs.uniform(2, (n, n), device=dev) if rank == 0 else torch.empty((n, n), dtype=torch.float64, device=dev)
-    C_local = torch.empty((rows, n), dtype=torch.float64, device=dev)
-    C_full = torch.empty((n, n), dtype=torch.float64, device=dev) if world > 1 else C_local
-    torch.cuda.synchronize()
     opts = api.make_opts(eb.TIER_OZAKI2, 16)
+    if world == 1:
+        rows = n
+        A = inputs.normal(1, (n, n), device=dev)
+        B = inputs.normal(2, (n, n), device=dev)
+        C_local = torch.empty((n, n), dtype=torch.float64, device=dev)
+        sg = None
+    else:
+        from eshkol_b200.sharded import ShardedGemm
+        sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16)
+        rows = sg.rows
+        A = inputs.uniform(1, (rows, n), device=dev, start=sg.row0 * n)
+        B = inputs.uniform(2, (n, n), device=dev) if rank == 0 else None
+        C_local = sg.C_blocks[rank, :rows]
+    torch.cuda.synchronize()
 
     def step():
-        if world > 1:
-            dist.broadcast(B, src=0)
-            torch.cuda.current_stream().synchronize()
-        api.gemm_device(A.data_ptr(), B.data_ptr(), C_local.data_ptr(), rows, n, n, opts)
-        if world > 1:
-            st = api.sync_status()
-            if st != 0:
-                raise RuntimeError(f"kernel status {st}")
-            dist.all_gather_into_tensor(C_full, C_local)
+        if sg is None:
+            api.gemm_device(A.data_ptr(), B.data_ptr(), C_local.data_ptr(), n, n, n, opts)
+        else:
+            sg.step(A, B)
 
     def barrier():
         if world > 1:
@@ -210,12 +208,12 @@ def run_b200(args):
         if api.sync_status() != 0:
             raise RuntimeError("kernel status non-zero")
 
-    for _ in range(max(3, args.warmup)):
-        step()
-    barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
     lib.eshkol_b200_set_phase_timing(1)
     launches0 = api.launch_count()
     ev0 = torch.cuda.Event(enable_timing=True)
@@ -223,17 +221,18 @@ def run_b200(args):
     barrier()
     if world == 1:
         ev0.record(lib_stream)
-        phase_acc = np.zeros(7)
         for _ in range(args.steps):
             step()
         ev1.record(lib_stream)
         barrier()
         ms_total = ev0.elapsed_time(ev1)
     else:
-        t0 = time.perf_counter()
+        # the step mixes the library stream and torch's (NCCL) stream with host waits in
+        # between: bracket it with events on torch's stream after a full device sync
         ev0.record(torch.cuda.current_stream())
         for _ in range(args.steps):
             step()
+        torch.cuda.current_stream().synchronize()
         ev1.record(torch.cuda.current_stream())
         barrier()
         ms_total = ev0.elapsed_time(ev1)
@@ -247,7 +246,8 @@ def run_b200(args):
 
     # per-stage times of one more (untimed) GEMM, for the roofline of the dominant kernel
     ph = (ctypes.c_float * 8)()
-    api.gemm_device(A.data_ptr(), B.data_ptr(), C_local.data_ptr(), rows, n, n, opts)
+    Bdev = B if sg is None else sg.B
+    api.gemm_device(A.data_ptr(), Bdev.data_ptr(), C_local.data_ptr(), rows, n, n, opts)
     got = lib.eshkol_b200_get_phase_times(ph, 8)
     lib.eshkol_b200_set_phase_timing(0)
     phases = [float(x) for x in ph[:7]] if got == 7 else None
@@ -270,7 +270,7 @@ def run_b200(args):
             "frac": achieved / peak, "traffic": None,
             "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}); "
                            "int8 dense issues at twice the bf16 rate",
-            "phases_ms": dict(zip(["scan", "scales", "split_a", "split_b", "products_mod256",
+            "phases_ms": dict(zip(["scan_b", "split_b", "scan_a", "split_a", "products_mod256",
                                    "products_odd", "reconstruct"], phases)),
         }
         int8_peak = measure_int8_library_peak(torch, dev)

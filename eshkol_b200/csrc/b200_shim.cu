@@ -35,8 +35,24 @@ struct State {
   PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
   // optional per-stage timing of the Ozaki-II driver (CUDA events on the stream)
   bool timing = false;
-  cudaEvent_t ev[8] = {};
+  cudaEvent_t ev[9] = {};
   bool ev_made = false, ev_valid = false;
+  // prepared right-hand operand of the exact tier (its own allocation)
+  uint8_t* bside = nullptr;
+  size_t bside_bytes = 0;
+  struct Prepared {
+    bool valid = false;
+    long long K = 0, N = 0, Kp = 0, K0 = 0, Np = 0;
+    int n_chunks = 0, last_seg = 0, bn = 256, tiles_n = 0;
+    double* bmax = nullptr; int* nu = nullptr; double* sb = nullptr; double* sbi = nullptr;
+    int8_t* b0 = nullptr; int8_t* bodd = nullptr; long long bodd_stride = 0;
+    CUtensorMap mB0, mB1;
+    Oz2DeviceConsts consts;
+  } prep;
+  // host pipeline: upload / download streams and their hand-off events
+  bool pipe_made = false;
+  cudaStream_t s_in = nullptr, s_out = nullptr;
+  cudaEvent_t e_b_ready = nullptr, e_a_ready[2] = {}, e_a_free[2] = {}, e_c_ready[2] = {}, e_c_free[2] = {};
   // layout of the last Ozaki-II GEMM, for eshkol_b200_debug_fetch
   struct Last {
     bool valid = false;
@@ -223,8 +239,27 @@ static int oz2_exponent(double log2P, long long K, const double* amax, long long
 }
 
 // ------------------------------------------------------------ Ozaki-II driver
-static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long M, long long K,
-                       long long N, int n_mod, const EshkolB200GemmOpts& o) {
+struct Oz2Geom {
+  long long M, K, N, Kp, K0, Mp, Np;
+  int n_chunks, last_seg, tiles_m, tiles_n, bn;
+};
+
+static Oz2Geom oz2_geometry(long long M, long long K, long long N, int bn) {
+  Oz2Geom q;
+  q.M = M; q.K = K; q.N = N; q.bn = bn;
+  q.Kp = round_up(K, kBK);
+  q.n_chunks = static_cast<int>((K + kChunkK - 1) / kChunkK);
+  const int last_len = static_cast<int>(K - static_cast<long long>(q.n_chunks - 1) * kChunkK);
+  q.last_seg = static_cast<int>(round_up(last_len, kBK));
+  q.K0 = static_cast<long long>(q.n_chunks - 1) * kChunkExt + 3LL * q.last_seg;
+  q.tiles_m = static_cast<int>((M + kBM - 1) / kBM);
+  q.tiles_n = static_cast<int>((N + bn - 1) / bn);
+  q.Mp = static_cast<long long>(q.tiles_m) * kBM;
+  q.Np = static_cast<long long>(q.tiles_n) * bn;
+  return q;
+}
+
+static int oz2_check_shape(long long M, long long K, long long N, int n_mod) {
   if (n_mod < 2 || n_mod > 16) {
     fprintf(stderr, "[eshkol-b200] Ozaki-II: moduli count %d outside [2,16]\n", n_mod);
     return -1;
@@ -235,28 +270,189 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
     return -1;
   }
   if (M > 0x7fffff00LL || N > 0x7fffff00LL) return -1;
-  const int bn = (o.gemm_tile_n == 128) ? 128 : 256;
-  const long long Kp = round_up(K, kBK);
-  const int n_chunks = static_cast<int>((K + kChunkK - 1) / kChunkK);
-  const int last_len = static_cast<int>(K - static_cast<long long>(n_chunks - 1) * kChunkK);
-  const int last_seg = static_cast<int>(round_up(last_len, kBK));
-  const long long K0 = static_cast<long long>(n_chunks - 1) * kChunkExt + 3LL * last_seg;
-  const int tiles_m = static_cast<int>((M + kBM - 1) / kBM);
-  const int tiles_n = static_cast<int>((N + bn - 1) / bn);
-  const long long Mp = static_cast<long long>(tiles_m) * kBM, Np = static_cast<long long>(tiles_n) * bn;
-  const int n_odd = n_mod - 1;
-  if (static_cast<long long>(tiles_m) * tiles_n * n_mod > 0x7fffffffLL) return -1;
+  return 0;
+}
 
+#define B200_MARK(i) do { if (timed) B200_CHECK(cudaEventRecord(g.ev[i], st)); } while (0)
+
+// Right-hand operand of the exact tier, prepared once and kept: nu_j, 2^+-nu_j and
+// the residue planes of B.  Rows of A can then be multiplied block by block (the
+// host pipeline, the row-sharded multi-GPU driver) without touching B again.  Only
+// with all 16 moduli, where the exponent E is 52 whatever the data; with fewer moduli
+// E depends on the maxima of both operands and the one-shot path below is used.
+static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
+  if (oz2_check_shape(1, K, N, 16)) return -1;
+  const Oz2Geom q = oz2_geometry(1, K, N, bn);
+  const int n_odd = 15;
+  Carver cv;
+  const size_t o_bmax = cv.take(N * 8), o_nu = cv.take(N * 4), o_sb = cv.take(N * 8), o_sbi = cv.take(N * 8);
+  const size_t o_b0 = cv.take(static_cast<size_t>(N) * q.K0);
+  const size_t b_stride = static_cast<size_t>(N) * q.Kp;
+  const size_t o_bodd = cv.take(b_stride * n_odd);
+  g.prep.valid = false;
+  if (cv.off > g.bside_bytes) {
+    B200_CHECK(cudaStreamSynchronize(g.stream));
+    if (g.bside) B200_CHECK(cudaFree(g.bside));
+    g.bside = nullptr; g.bside_bytes = 0;
+    if (cudaMalloc(&g.bside, cv.off) != cudaSuccess) {
+      fprintf(stderr, "[eshkol-b200] allocation of %zu bytes for the prepared operand failed\n", cv.off);
+      cudaGetLastError();
+      return -1;
+    }
+    g.bside_bytes = cv.off;
+  }
+  uint8_t* ws = g.bside;
+  State::Prepared& P = g.prep;
+  P.K = K; P.N = N; P.Kp = q.Kp; P.K0 = q.K0; P.n_chunks = q.n_chunks; P.last_seg = q.last_seg;
+  P.bn = bn; P.Np = q.Np; P.tiles_n = q.tiles_n;
+  P.bmax = reinterpret_cast<double*>(ws + o_bmax);
+  P.nu = reinterpret_cast<int*>(ws + o_nu);
+  P.sb = reinterpret_cast<double*>(ws + o_sb);
+  P.sbi = reinterpret_cast<double*>(ws + o_sbi);
+  P.b0 = reinterpret_cast<int8_t*>(ws + o_b0);
+  P.bodd = reinterpret_cast<int8_t*>(ws + o_bodd);
+  P.bodd_stride = static_cast<long long>(b_stride);
+  oz2_host_consts(16, &P.consts, nullptr);
+  cudaStream_t st = g.stream;
+  const bool timed = g.timing && g.ev_made;
+  g.ev_valid = false;
+  B200_MARK(0);
+  B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(P.bmax), st));
+  B200_CHECK(launch_scales(P.bmax, N, 52, P.nu, P.sb, P.sbi, st));
+  B200_MARK(1);
+  SplitPlanes pb{N, K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, P.b0, P.bodd, P.bodd_stride};
+  B200_CHECK(launch_split_b(dB, P.sb, N, pb, P.consts, st));
+  B200_MARK(2);
+  g.launches += 3;
+  if (make_plane_map(&P.mB0, P.b0, q.K0, N, 1, static_cast<long long>(N) * q.K0, bn)) return -1;
+  if (make_plane_map(&P.mB1, P.bodd, q.Kp, N, n_odd, P.bodd_stride, bn)) return -1;
+  P.valid = true;
+  return 0;
+}
+
+// C[rows] = A[rows] * (prepared B): scan, split, products and reconstruction of one
+// block of rows.  Bit-identical to the same rows of a one-shot product.
+static int oz2_gemm_rows(const double* dA, double* dC, long long M, const EshkolB200GemmOpts& o) {
+  const State::Prepared& P = g.prep;
+  if (!P.valid) {
+    fprintf(stderr, "[eshkol-b200] no prepared right-hand operand\n");
+    return -1;
+  }
+  if (oz2_check_shape(M, P.K, P.N, 16)) return -1;
+  const Oz2Geom q = oz2_geometry(M, P.K, P.N, P.bn);
+  const int n_odd = 15;
+  if (static_cast<long long>(q.tiles_m) * q.tiles_n * 16 > 0x7fffffffLL) return -1;
+  Carver cv;
+  const size_t o_amax = cv.take(M * 8), o_mu = cv.take(M * 4), o_sa = cv.take(M * 8), o_sai = cv.take(M * 8);
+  const size_t o_jobs = cv.take(sizeof(GemmJob) * 16);
+  const size_t o_a0 = cv.take(static_cast<size_t>(M) * q.K0);
+  const size_t a_stride = static_cast<size_t>(M) * q.Kp;
+  const size_t o_aodd = cv.take(a_stride * n_odd);
+  const size_t w_stride = static_cast<size_t>(q.Mp) * q.Np;
+  const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
+  if (ensure_workspace(cv.off) != 0) return -1;
+  uint8_t* ws = g.ws;
+  double* amax = reinterpret_cast<double*>(ws + o_amax);
+  int* mu = reinterpret_cast<int*>(ws + o_mu);
+  double* sa = reinterpret_cast<double*>(ws + o_sa);
+  double* sai = reinterpret_cast<double*>(ws + o_sai);
+  GemmJob* d_jobs = reinterpret_cast<GemmJob*>(ws + o_jobs);
+  int8_t* a0 = reinterpret_cast<int8_t*>(ws + o_a0);
+  int8_t* aodd = reinterpret_cast<int8_t*>(ws + o_aodd);
+  int16_t* w0 = reinterpret_cast<int16_t*>(ws + o_w0);
+  int8_t* wodd = reinterpret_cast<int8_t*>(ws + o_wodd);
+  cudaStream_t st = g.stream;
+  const bool timed = g.timing && g.ev_made;
+
+  B200_MARK(3);
+  B200_CHECK(launch_scan_rows(dA, M, P.K, amax, st));
+  B200_CHECK(launch_scales(amax, M, 52, mu, sa, sai, st));
+  B200_MARK(4);
+  SplitPlanes pa{M, P.K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, a0, aodd, static_cast<long long>(a_stride)};
+  B200_CHECK(launch_split_a(dA, sa, pa, P.consts, st));
+  B200_MARK(5);
+  g.launches += 3;
+
+  GemmJob jobs[16];
+  fill_mod_job(&jobs[0], 0, 0, 0, 0);
+  for (int l = 1; l < 16; ++l) fill_mod_job(&jobs[l], l - 1, l - 1, l - 1, kModuli[l]);
+  B200_CHECK(cudaMemcpyAsync(d_jobs, jobs, sizeof(GemmJob) * 16, cudaMemcpyHostToDevice, st));
+
+  GemmParams p0;
+  p0.tiles_m = q.tiles_m; p0.tiles_n = q.tiles_n; p0.n_jobs = 1;
+  p0.kb_per_seg = static_cast<int>(q.K0 / kBK);
+  p0.kb_per_unit = kChunkExt / kBK;
+  p0.group_m = 16;
+  p0.jobs = d_jobs;
+  p0.out = reinterpret_cast<uint8_t*>(w0);
+  p0.out_plane_stride = 0;
+  p0.ldo = static_cast<int>(q.Np);
+  p0.status = g.d_status;
+  GemmParams p1 = p0;
+  p1.n_jobs = n_odd;
+  p1.kb_per_seg = static_cast<int>(q.Kp / kBK);
+  p1.kb_per_unit = 1 << 28;
+  p1.jobs = d_jobs + 1;
+  p1.out = reinterpret_cast<uint8_t*>(wodd);
+  p1.out_plane_stride = static_cast<long long>(w_stride);
+  const int tiles = q.tiles_m * q.tiles_n;
+  if (o.use_simt_products) {
+    SimtPlanes s0{a0, 0, static_cast<int>(q.K0), P.b0, 0, static_cast<int>(q.K0), static_cast<int>(M), static_cast<int>(P.N)};
+    SimtPlanes s1{aodd, static_cast<long long>(a_stride), static_cast<int>(q.Kp), P.bodd, P.bodd_stride,
+                  static_cast<int>(q.Kp), static_cast<int>(M), static_cast<int>(P.N)};
+    B200_CHECK(launch_modgemm_simt(kEpiMod256, s0, p0, st));
+    B200_MARK(6);
+    B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
+  } else {
+    CUtensorMap mA0, mA1;
+    if (make_plane_map(&mA0, a0, q.K0, M, 1, static_cast<long long>(M) * q.K0, kBM)) return -1;
+    if (make_plane_map(&mA1, aodd, q.Kp, M, n_odd, static_cast<long long>(a_stride), kBM)) return -1;
+    B200_CHECK(launch_modgemm(P.bn, kEpiMod256, mA0, P.mB0, p0, tiles, g.num_sms, st));
+    B200_MARK(6);
+    B200_CHECK(launch_modgemm(P.bn, kEpiModI8, mA1, P.mB1, p1, tiles * n_odd, g.num_sms, st));
+  }
+  B200_MARK(7);
+  CrtArgs ca;
+  ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = q.Np;
+  ca.n_mod = 16; ca.M = M; ca.N = P.N;
+  ca.inv_scale_a = sai; ca.inv_scale_b = P.sbi;
+  ca.C = dC; ca.ldc = P.N;
+  ca.bias_mode = o.bias ? o.bias_mode : 0; ca.bias = o.bias;
+  ca.activation = o.activation;
+  ca.pixels_per_image = o.pixels_per_image;
+  B200_CHECK(launch_crt(ca, P.consts, st));
+  B200_MARK(8);
+  g.launches += 3;
+  g.ev_valid = timed;
+
+  State::Last& L = g.last;
+  L.valid = true; L.M = M; L.K = P.K; L.N = P.N; L.Kp = q.Kp; L.K0 = q.K0; L.Mp = q.Mp; L.Np = q.Np;
+  L.n_mod = 16; L.n_chunks = q.n_chunks; L.last_seg = q.last_seg;
+  L.mu = mu; L.nu = P.nu; L.a0 = a0; L.aodd = aodd; L.aodd_stride = static_cast<long long>(a_stride);
+  L.b0 = P.b0; L.bodd = P.bodd; L.bodd_stride = P.bodd_stride;
+  L.w0 = w0; L.wodd = wodd; L.wodd_stride = static_cast<long long>(w_stride);
+  return 0;
+}
+
+// One-shot product with fewer than 16 moduli: the exponent E needs the maxima of both
+// operands (gpu_memory.mm:2510-2512), so the operands are scanned together.
+static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, long long M,
+                               long long K, long long N, int n_mod, const EshkolB200GemmOpts& o) {
+  if (oz2_check_shape(M, K, N, n_mod)) return -1;
+  const int bn = (o.gemm_tile_n == 128) ? 128 : 256;
+  const Oz2Geom q = oz2_geometry(M, K, N, bn);
+  const int n_odd = n_mod - 1;
+  if (static_cast<long long>(q.tiles_m) * q.tiles_n * n_mod > 0x7fffffffLL) return -1;
   Carver cv;
   const size_t o_amax = cv.take(M * 8), o_bmax = cv.take(N * 8);
   const size_t o_mu = cv.take(M * 4), o_nu = cv.take(N * 4);
   const size_t o_sa = cv.take(M * 8), o_sai = cv.take(M * 8);
   const size_t o_sb = cv.take(N * 8), o_sbi = cv.take(N * 8);
   const size_t o_jobs = cv.take(sizeof(GemmJob) * 16);
-  const size_t o_a0 = cv.take(static_cast<size_t>(M) * K0), o_b0 = cv.take(static_cast<size_t>(N) * K0);
-  const size_t a_stride = static_cast<size_t>(M) * Kp, b_stride = static_cast<size_t>(N) * Kp;
+  const size_t o_a0 = cv.take(static_cast<size_t>(M) * q.K0), o_b0 = cv.take(static_cast<size_t>(N) * q.K0);
+  const size_t a_stride = static_cast<size_t>(M) * q.Kp, b_stride = static_cast<size_t>(N) * q.Kp;
   const size_t o_aodd = cv.take(a_stride * n_odd), o_bodd = cv.take(b_stride * n_odd);
-  const size_t w_stride = static_cast<size_t>(Mp) * Np;
+  const size_t w_stride = static_cast<size_t>(q.Mp) * q.Np;
   const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
   if (ensure_workspace(cv.off) != 0) return -1;
   uint8_t* ws = g.ws;
@@ -276,88 +472,64 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
   int16_t* w0 = reinterpret_cast<int16_t*>(ws + o_w0);
   int8_t* wodd = reinterpret_cast<int8_t*>(ws + o_wodd);
   cudaStream_t st = g.stream;
+  g.ev_valid = false;
 
   double log2P = 0.0;
   Oz2DeviceConsts hc;
   oz2_host_consts(n_mod, &hc, &log2P);
-
-  const bool timed = g.timing && g.ev_made;
-  g.ev_valid = false;
-#define B200_MARK(i) do { if (timed) B200_CHECK(cudaEventRecord(g.ev[i], st)); } while (0)
-  B200_MARK(0);
   B200_CHECK(launch_scan_rows(dA, M, K, amax, st));
   B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(bmax), st));
-  g.launches += 2;
-  B200_MARK(1);
-
-  // With all 16 moduli, log2 P - 1 - log2 K - 2 > 104 for every admissible K, so E
-  // clamps to 52 whatever the data; fewer moduli need the data-dependent bound.
-  int E = 52;
-  if (n_mod < 16) {
-    std::vector<double> ha(M), hb(N);
-    B200_CHECK(cudaMemcpyAsync(ha.data(), amax, M * 8, cudaMemcpyDeviceToHost, st));
-    B200_CHECK(cudaMemcpyAsync(hb.data(), bmax, N * 8, cudaMemcpyDeviceToHost, st));
-    B200_CHECK(cudaStreamSynchronize(st));
-    E = oz2_exponent(log2P, K, ha.data(), M, hb.data(), N);
-  }
+  std::vector<double> ha(M), hb(N);
+  B200_CHECK(cudaMemcpyAsync(ha.data(), amax, M * 8, cudaMemcpyDeviceToHost, st));
+  B200_CHECK(cudaMemcpyAsync(hb.data(), bmax, N * 8, cudaMemcpyDeviceToHost, st));
+  B200_CHECK(cudaStreamSynchronize(st));
+  const int E = oz2_exponent(log2P, K, ha.data(), M, hb.data(), N);
   B200_CHECK(launch_scales(amax, M, E, mu, sa, sai, st));
   B200_CHECK(launch_scales(bmax, N, E, nu, sb, sbi, st));
-  g.launches += 2;
-  B200_MARK(2);
-
-  SplitPlanes pa{M, K, Kp, K0, n_chunks, last_seg, n_odd, a0, aodd, static_cast<long long>(a_stride)};
-  SplitPlanes pb{N, K, Kp, K0, n_chunks, last_seg, n_odd, b0, bodd, static_cast<long long>(b_stride)};
+  SplitPlanes pa{M, K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, a0, aodd, static_cast<long long>(a_stride)};
+  SplitPlanes pb{N, K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, b0, bodd, static_cast<long long>(b_stride)};
   B200_CHECK(launch_split_a(dA, sa, pa, hc, st));
-  B200_MARK(3);
   B200_CHECK(launch_split_b(dB, sb, N, pb, hc, st));
-  g.launches += 2;
-  B200_MARK(4);
 
   GemmJob jobs[16];
   fill_mod_job(&jobs[0], 0, 0, 0, 0);
   for (int l = 1; l < n_mod; ++l) fill_mod_job(&jobs[l], l - 1, l - 1, l - 1, kModuli[l]);
   B200_CHECK(cudaMemcpyAsync(d_jobs, jobs, sizeof(GemmJob) * n_mod, cudaMemcpyHostToDevice, st));
-
   GemmParams p0;
-  p0.tiles_m = tiles_m; p0.tiles_n = tiles_n; p0.n_jobs = 1;
-  p0.kb_per_seg = static_cast<int>(K0 / kBK);
+  p0.tiles_m = q.tiles_m; p0.tiles_n = q.tiles_n; p0.n_jobs = 1;
+  p0.kb_per_seg = static_cast<int>(q.K0 / kBK);
   p0.kb_per_unit = kChunkExt / kBK;
   p0.group_m = 16;
   p0.jobs = d_jobs;
   p0.out = reinterpret_cast<uint8_t*>(w0);
   p0.out_plane_stride = 0;
-  p0.ldo = static_cast<int>(Np);
+  p0.ldo = static_cast<int>(q.Np);
   p0.status = g.d_status;
   GemmParams p1 = p0;
   p1.n_jobs = n_odd;
-  p1.kb_per_seg = static_cast<int>(Kp / kBK);
+  p1.kb_per_seg = static_cast<int>(q.Kp / kBK);
   p1.kb_per_unit = 1 << 28;
   p1.jobs = d_jobs + 1;
   p1.out = reinterpret_cast<uint8_t*>(wodd);
   p1.out_plane_stride = static_cast<long long>(w_stride);
-
+  const int tiles = q.tiles_m * q.tiles_n;
   if (o.use_simt_products) {
-    SimtPlanes s0{a0, 0, static_cast<int>(K0), b0, 0, static_cast<int>(K0), static_cast<int>(M), static_cast<int>(N)};
-    SimtPlanes s1{aodd, static_cast<long long>(a_stride), static_cast<int>(Kp), bodd,
-                  static_cast<long long>(b_stride), static_cast<int>(Kp), static_cast<int>(M), static_cast<int>(N)};
+    SimtPlanes s0{a0, 0, static_cast<int>(q.K0), b0, 0, static_cast<int>(q.K0), static_cast<int>(M), static_cast<int>(N)};
+    SimtPlanes s1{aodd, static_cast<long long>(a_stride), static_cast<int>(q.Kp), bodd,
+                  static_cast<long long>(b_stride), static_cast<int>(q.Kp), static_cast<int>(M), static_cast<int>(N)};
     B200_CHECK(launch_modgemm_simt(kEpiMod256, s0, p0, st));
-    B200_MARK(5);
     B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
   } else {
     CUtensorMap mA0, mB0, mA1, mB1;
-    if (make_plane_map(&mA0, a0, K0, M, 1, static_cast<long long>(M) * K0, kBM)) return -1;
-    if (make_plane_map(&mB0, b0, K0, N, 1, static_cast<long long>(N) * K0, bn)) return -1;
-    if (make_plane_map(&mA1, aodd, Kp, M, n_odd, static_cast<long long>(a_stride), kBM)) return -1;
-    if (make_plane_map(&mB1, bodd, Kp, N, n_odd, static_cast<long long>(b_stride), bn)) return -1;
-    B200_CHECK(launch_modgemm(bn, kEpiMod256, mA0, mB0, p0, tiles_m * tiles_n, g.num_sms, st));
-    B200_MARK(5);
-    B200_CHECK(launch_modgemm(bn, kEpiModI8, mA1, mB1, p1, tiles_m * tiles_n * n_odd, g.num_sms, st));
+    if (make_plane_map(&mA0, a0, q.K0, M, 1, static_cast<long long>(M) * q.K0, kBM)) return -1;
+    if (make_plane_map(&mB0, b0, q.K0, N, 1, static_cast<long long>(N) * q.K0, bn)) return -1;
+    if (make_plane_map(&mA1, aodd, q.Kp, M, n_odd, static_cast<long long>(a_stride), kBM)) return -1;
+    if (make_plane_map(&mB1, bodd, q.Kp, N, n_odd, static_cast<long long>(b_stride), bn)) return -1;
+    B200_CHECK(launch_modgemm(bn, kEpiMod256, mA0, mB0, p0, tiles, g.num_sms, st));
+    B200_CHECK(launch_modgemm(bn, kEpiModI8, mA1, mB1, p1, tiles * n_odd, g.num_sms, st));
   }
-  g.launches += 2;
-  B200_MARK(6);
-
   CrtArgs ca;
-  ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = Np;
+  ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = q.Np;
   ca.n_mod = n_mod; ca.M = M; ca.N = N;
   ca.inv_scale_a = sai; ca.inv_scale_b = sbi;
   ca.C = dC; ca.ldc = N;
@@ -365,18 +537,92 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
   ca.activation = o.activation;
   ca.pixels_per_image = o.pixels_per_image;
   B200_CHECK(launch_crt(ca, hc, st));
-  g.launches += 1;
-  B200_MARK(7);
-#undef B200_MARK
-  g.ev_valid = timed;
+  g.launches += 9;
 
   State::Last& L = g.last;
-  L.valid = true; L.M = M; L.K = K; L.N = N; L.Kp = Kp; L.K0 = K0; L.Mp = Mp; L.Np = Np;
-  L.n_mod = n_mod; L.n_chunks = n_chunks; L.last_seg = last_seg;
+  L.valid = true; L.M = M; L.K = K; L.N = N; L.Kp = q.Kp; L.K0 = q.K0; L.Mp = q.Mp; L.Np = q.Np;
+  L.n_mod = n_mod; L.n_chunks = q.n_chunks; L.last_seg = q.last_seg;
   L.mu = mu; L.nu = nu; L.a0 = a0; L.aodd = aodd; L.aodd_stride = static_cast<long long>(a_stride);
   L.b0 = b0; L.bodd = bodd; L.bodd_stride = static_cast<long long>(b_stride);
   L.w0 = w0; L.wodd = wodd; L.wodd_stride = static_cast<long long>(w_stride);
   return 0;
+}
+#undef B200_MARK
+
+static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long M, long long K,
+                       long long N, int n_mod, const EshkolB200GemmOpts& o) {
+  if (n_mod != 16) return ozaki2_gemm_general(dA, dB, dC, M, K, N, n_mod, o);
+  if (oz2_check_shape(M, K, N, 16)) return -1;
+  if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256)) return -1;
+  const int rc = oz2_gemm_rows(dA, dC, M, o);
+  g.prep.valid = false;  // dB belongs to the caller and may change before the next call
+  return rc;
+}
+
+// Host-pointer product, pipelined over row blocks of A: B is uploaded and prepared
+// once; then block i+1 of A crosses PCIe while block i is multiplied and block i-1 of
+// C travels back.  Three streams (upload, compute = the library stream, download) and
+// double-buffered device blocks.  Pinned host memory overlaps fully; pageable memory
+// is staged by the runtime and still produces the same bits.
+static int oz2_matmul_host(const double* hA, const double* hB, double* hC, long long M, long long K,
+                           long long N, const EshkolB200GemmOpts& o) {
+  if (oz2_check_shape(M, K, N, 16)) return -1;
+  long long bm = 1024;
+  if (M <= 2048) bm = M;  // too small to be worth splitting
+  const long long nblk = (M + bm - 1) / bm;
+  const size_t bytesB = static_cast<size_t>(K) * N * 8;
+  const size_t bytesA = static_cast<size_t>(bm) * K * 8, bytesC = static_cast<size_t>(bm) * N * 8;
+  const size_t need = ((bytesB + 1023) & ~size_t(1023)) + 2 * ((bytesA + 1023) & ~size_t(1023)) +
+                      2 * ((bytesC + 1023) & ~size_t(1023));
+  uint8_t* base = aux_reserve(need);
+  if (!base) return -1;
+  double* dB = reinterpret_cast<double*>(base);
+  size_t off = (bytesB + 1023) & ~size_t(1023);
+  double* dA[2]; double* dC[2];
+  for (int i = 0; i < 2; ++i) { dA[i] = reinterpret_cast<double*>(base + off); off += (bytesA + 1023) & ~size_t(1023); }
+  for (int i = 0; i < 2; ++i) { dC[i] = reinterpret_cast<double*>(base + off); off += (bytesC + 1023) & ~size_t(1023); }
+  if (!g.pipe_made) {
+    B200_CHECK(cudaStreamCreateWithFlags(&g.s_in, cudaStreamNonBlocking));
+    B200_CHECK(cudaStreamCreateWithFlags(&g.s_out, cudaStreamNonBlocking));
+    for (int i = 0; i < 2; ++i) {
+      B200_CHECK(cudaEventCreateWithFlags(&g.e_a_ready[i], cudaEventDisableTiming));
+      B200_CHECK(cudaEventCreateWithFlags(&g.e_a_free[i], cudaEventDisableTiming));
+      B200_CHECK(cudaEventCreateWithFlags(&g.e_c_ready[i], cudaEventDisableTiming));
+      B200_CHECK(cudaEventCreateWithFlags(&g.e_c_free[i], cudaEventDisableTiming));
+    }
+    B200_CHECK(cudaEventCreateWithFlags(&g.e_b_ready, cudaEventDisableTiming));
+    g.pipe_made = true;
+  }
+  cudaStream_t st = g.stream;
+  // earlier work on the compute stream may still read the scratch block
+  B200_CHECK(cudaEventRecord(g.e_b_ready, st));
+  B200_CHECK(cudaStreamWaitEvent(g.s_in, g.e_b_ready, 0));
+  B200_CHECK(cudaMemcpyAsync(dB, hB, bytesB, cudaMemcpyHostToDevice, g.s_in));
+  B200_CHECK(cudaEventRecord(g.e_b_ready, g.s_in));
+  // first block of A rides behind B on the upload stream
+  B200_CHECK(cudaStreamWaitEvent(st, g.e_b_ready, 0));
+  if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256)) return -1;
+  int rc = 0;
+  for (long long i = 0; i < nblk && rc == 0; ++i) {
+    const int s = static_cast<int>(i & 1);
+    const long long r0 = i * bm, rows = (r0 + bm <= M) ? bm : M - r0;
+    if (i >= 2) B200_CHECK(cudaStreamWaitEvent(g.s_in, g.e_a_free[s], 0));
+    B200_CHECK(cudaMemcpyAsync(dA[s], hA + r0 * K, static_cast<size_t>(rows) * K * 8, cudaMemcpyHostToDevice, g.s_in));
+    B200_CHECK(cudaEventRecord(g.e_a_ready[s], g.s_in));
+    B200_CHECK(cudaStreamWaitEvent(st, g.e_a_ready[s], 0));
+    if (i >= 2) B200_CHECK(cudaStreamWaitEvent(st, g.e_c_free[s], 0));
+    rc = oz2_gemm_rows(dA[s], dC[s], rows, o);
+    if (rc) break;
+    B200_CHECK(cudaEventRecord(g.e_a_free[s], st));
+    B200_CHECK(cudaEventRecord(g.e_c_ready[s], st));
+    B200_CHECK(cudaStreamWaitEvent(g.s_out, g.e_c_ready[s], 0));
+    B200_CHECK(cudaMemcpyAsync(hC + r0 * N, dC[s], static_cast<size_t>(rows) * N * 8, cudaMemcpyDeviceToHost, g.s_out));
+    B200_CHECK(cudaEventRecord(g.e_c_free[s], g.s_out));
+  }
+  g.prep.valid = false;
+  B200_CHECK(cudaStreamSynchronize(g.s_out));
+  B200_CHECK(cudaStreamSynchronize(g.s_in));
+  return rc;
 }
 
 }  // namespace b200
@@ -426,7 +672,15 @@ void eshkol_b200_shutdown(void) {
   if (g.ws) cudaFree(g.ws);
   if (g.aux) cudaFree(g.aux);
   if (g.d_status) cudaFree(g.d_status);
-  if (g.ev_made) for (int i = 0; i < 8; ++i) cudaEventDestroy(g.ev[i]);
+  if (g.ev_made) for (int i = 0; i < 9; ++i) cudaEventDestroy(g.ev[i]);
+  if (g.bside) cudaFree(g.bside);
+  if (g.pipe_made) {
+    cudaStreamDestroy(g.s_in); cudaStreamDestroy(g.s_out); cudaEventDestroy(g.e_b_ready);
+    for (int i = 0; i < 2; ++i) {
+      cudaEventDestroy(g.e_a_ready[i]); cudaEventDestroy(g.e_a_free[i]);
+      cudaEventDestroy(g.e_c_ready[i]); cudaEventDestroy(g.e_c_free[i]);
+    }
+  }
   cudaStreamDestroy(g.stream);
   g = State();
 }
@@ -457,6 +711,35 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC, 
       fprintf(stderr, "[eshkol-b200] unknown tier %d\n", o.tier);
       return -1;
   }
+}
+
+int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, uint64_t M,
+                                uint64_t K, uint64_t N, const EshkolB200GemmOpts* opts) {
+  if (!g.ready) {
+    fprintf(stderr, "[eshkol-b200] matmul called before eshkol_b200_init succeeded\n");
+    return -1;
+  }
+  if (!hA || !hB || !hC || M == 0 || K == 0 || N == 0) return -1;
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  if (opts) o = *opts;
+  if (o.tier != ESHKOL_B200_TIER_OZAKI2 || (o.param != 0 && o.param != 16)) return -2;
+  return oz2_matmul_host(hA, hB, hC, static_cast<long long>(M), static_cast<long long>(K),
+                         static_cast<long long>(N), o);
+}
+
+int eshkol_b200_prepare_b_f64_device(const double* dB, uint64_t K, uint64_t N) {
+  if (!g.ready || !dB || K == 0 || N == 0) return -1;
+  return oz2_prepare_b(dB, static_cast<long long>(K), static_cast<long long>(N), 256);
+}
+
+int eshkol_b200_gemm_prepared_f64_device(const double* dA, double* dC, uint64_t M,
+                                         const EshkolB200GemmOpts* opts) {
+  if (!g.ready || !dA || !dC || M == 0) return -1;
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  if (opts) o = *opts;
+  return oz2_gemm_rows(dA, dC, static_cast<long long>(M), o);
 }
 
 int eshkol_b200_conv2d_f64_device(const double* d_in, int64_t batch, int64_t in_c, int64_t H,
@@ -531,7 +814,7 @@ int eshkol_b200_sync_status(void) {
 void eshkol_b200_set_phase_timing(int on) {
   if (!g.ready) return;
   if (on && !g.ev_made) {
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 9; ++i)
       if (cudaEventCreate(&g.ev[i]) != cudaSuccess) { cudaGetLastError(); return; }
     g.ev_made = true;
   }
@@ -542,13 +825,15 @@ void eshkol_b200_set_phase_timing(int on) {
 int eshkol_b200_get_phase_times(float* ms, int capacity) {
   if (!g.ready || !ms || capacity < 7 || !g.ev_valid) return -1;
   if (cudaStreamSynchronize(g.stream) != cudaSuccess) { cudaGetLastError(); return -1; }
+  // events 0-2 bracket the B side (scan + scales, split), events 3-8 the A side
+  static const int from[7] = {0, 1, 3, 4, 5, 6, 7};
   for (int i = 0; i < 7; ++i)
-    if (cudaEventElapsedTime(&ms[i], g.ev[i], g.ev[i + 1]) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (cudaEventElapsedTime(&ms[i], g.ev[from[i]], g.ev[from[i] + 1]) != cudaSuccess) { cudaGetLastError(); return -1; }
   return 7;
 }
 
 uint64_t eshkol_b200_launch_count(void) { return g.launches; }
-uint64_t eshkol_b200_workspace_bytes(void) { return g.ws_bytes + g.aux_bytes; }
+uint64_t eshkol_b200_workspace_bytes(void) { return g.ws_bytes + g.aux_bytes + g.bside_bytes; }
 
 int eshkol_b200_debug_fetch(int what, int index, void* host_dst, uint64_t capacity_bytes,
                             uint64_t info[6]) {

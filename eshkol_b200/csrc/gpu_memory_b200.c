@@ -418,7 +418,23 @@ void eshkol_matmul_dispatch(const double* A, const double* B, double* C, uint64_
     eshkol_matmul_f64(A, B, C, M, K, N); /* small shapes stay on the CPU: policy, not a fallback */
     return;
   }
-  if (g_backend == ESHKOL_GPU_CUDA && gpu_matmul_host(A, B, C, M, K, N) == 0) return;
+  if (g_backend == ESHKOL_GPU_CUDA) {
+    /* exact tier: upload, products and download pipelined over row blocks of A */
+    const TierChoice c = choose_tier(M, K, N);
+    int rc = -2;
+    if (c.tier == ESHKOL_B200_TIER_OZAKI2 && c.param == 16 && K <= 131071) {
+      EshkolB200GemmOpts o;
+      memset(&o, 0, sizeof(o));
+      o.tier = c.tier; o.param = c.param;
+      GPU_LOG("matmul %llux%llu @ %llux%llu -> Ozaki-II exact, host pipeline (%s)", (unsigned long long)M,
+              (unsigned long long)K, (unsigned long long)K, (unsigned long long)N, c.why);
+      rc = eshkol_b200_matmul_f64_host(A, B, C, M, K, N, &o);
+      if (rc == 0 && eshkol_b200_sync_status() != 0) rc = -1;
+      if (rc == 0) return;
+    }
+    /* other tiers: the buffer API, as the reference's dispatcher does */
+    if (rc == -2 && gpu_matmul_host(A, B, C, M, K, N) == 0) return;
+  }
   fprintf(stderr, "[GPU] eshkol_matmul_dispatch: the B200 path FAILED for %llux%llux%llu; "
                   "C is filled with NaN\n", (unsigned long long)M, (unsigned long long)K,
           (unsigned long long)N);

@@ -16,7 +16,7 @@ import eshkol_b200 as eb
 from eshkol_b200 import api, inputs
 
 TIERS = {"exact": eb.TIER_OZAKI2, "ozaki1": eb.TIER_OZAKI1, "fast": eb.TIER_OZAKI2_FAST, "dgemm": eb.TIER_DGEMM}
-STAGES = ["scan", "scales", "split_a", "split_b", "products_mod256", "products_odd", "reconstruct"]
+STAGES = ["scan_b", "split_b", "scan_a", "split_a", "products_mod256", "products_odd", "reconstruct"]
 
 
 def main() -> None:

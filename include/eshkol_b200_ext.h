@@ -66,6 +66,28 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC,
                                 uint64_t M, uint64_t K, uint64_t N,
                                 const EshkolB200GemmOpts* opts);
 
+/* Exact tier (16 moduli) with the right-hand operand prepared once: prepare_b scans
+ * and splits B (K x N, device memory) into library-owned residue planes; each
+ * gemm_prepared call then multiplies a block of rows, C[M x N] = A[M x K] * B, with
+ * the bits of the same rows of a one-shot product (rows are independent).  The
+ * prepared operand stays valid until the next prepare_b, any other GEMM of this
+ * library, or shutdown; B itself is not read again.  This is what lets a caller
+ * reuse one B (weights) across many products, pipeline row blocks against PCIe, or
+ * shard rows across GPUs.  The reference re-uploads and re-splits both operands on
+ * every call (lib/backend/gpu/gpu_memory.mm:2538-2583).  Asynchronous. */
+int eshkol_b200_prepare_b_f64_device(const double* dB, uint64_t K, uint64_t N);
+int eshkol_b200_gemm_prepared_f64_device(const double* dA, double* dC, uint64_t M,
+                                         const EshkolB200GemmOpts* opts);
+
+/* Exact tier on HOST arrays (what eshkol_matmul_dispatch runs for large shapes): B is
+ * uploaded and prepared once, then 1024-row blocks of A are uploaded, multiplied and
+ * their rows of C downloaded on three streams so PCIe and the tensor cores overlap.
+ * Returns when C is complete in host memory: 0, -1 on failure, -2 when opts ask for a
+ * tier this path does not serve (the caller then uses the buffer API).  Pinned host
+ * memory overlaps fully; pageable memory gives the same bits with less overlap. */
+int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, uint64_t M,
+                                uint64_t K, uint64_t N, const EshkolB200GemmOpts* opts);
+
 /* The same exact-tier product (16 moduli, identical bits) for callers that must not
  * allocate: a host whose own arena already owns all device memory, so that
  * cudaMalloc would fail, or one that cannot take the device-wide synchronisation
@@ -114,9 +136,10 @@ int eshkol_b200_sync_status(void);
  * ESHKOL_OZAKI_PROFILE line (lib/backend/gpu/gpu_memory.mm:2479, 2658-2664).  When
  * switched on, CUDA events on the library stream bracket each stage of every
  * Ozaki-II GEMM.  get_phase_times waits for the stream and writes the durations
- * of the LAST such GEMM in milliseconds: [0] row/column scan, [1] scales,
- * [2] split A, [3] split B, [4] products modulo 256, [5] products modulo the odd
- * moduli, [6] reconstruction.  Returns 7, or -1 when nothing was timed. */
+ * of the LAST 16-moduli GEMM in milliseconds: [0] column scan + scales of B,
+ * [1] split B, [2] row scan + scales of A, [3] split A, [4] products modulo 256,
+ * [5] products modulo the odd moduli, [6] reconstruction.  Returns 7, or -1 when
+ * nothing was timed. */
 void eshkol_b200_set_phase_timing(int on);
 int eshkol_b200_get_phase_times(float* ms, int capacity);
 

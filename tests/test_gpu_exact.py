@@ -166,3 +166,38 @@ def test_c2_4096_wide_exponent_sampled_rows_and_columns(gpu_lib):
     cols = np.sort(rng.choice(n, 24, replace=False))
     assert gu.same_bits(C[rows], ol.oz2_exact(A[rows], B, 52))
     assert gu.same_bits(C[:, cols], ol.oz2_exact(A, np.ascontiguousarray(B[:, cols]), 52))
+
+
+def test_prepared_b_row_blocks_have_the_bits_of_the_one_shot_product(gpu_lib):
+    import ctypes
+    import torch
+    A = inputs.full53(31, (700, 1300))
+    B = inputs.full53(32, (1300, 520))
+    want = gu.gemm(A, B)
+    dA = torch.from_numpy(A).cuda()
+    dB = torch.from_numpy(B).cuda()
+    dC = torch.full((700, 520), float("nan"), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    assert gpu_lib.eshkol_b200_prepare_b_f64_device(dB.data_ptr(), 1300, 520) == 0
+    dB.zero_()  # the prepared planes, not B, are what the products read
+    for r0, rows in ((0, 300), (300, 1), (301, 399)):
+        assert gpu_lib.eshkol_b200_gemm_prepared_f64_device(dA[r0:].data_ptr(), dC[r0:].data_ptr(), rows, None) == 0
+    assert api.sync_status() == 0
+    assert gu.same_bits(dC.cpu().numpy(), want)
+    assert gu.same_bits(want, ol.oz2_exact(A, B, 52))
+
+
+def test_host_pipeline_over_several_row_blocks(gpu_lib):
+    # eshkol_matmul_dispatch on host arrays: 1024-row blocks, three streams
+    A = inputs.uniform(41, (2500, 640))
+    B = inputs.wide(42, (640, 384), span=9, lo=-4)
+    gpu_lib.eshkol_gpu_set_threshold(1)
+    try:
+        C = eb.matmul_dispatch(A, B)
+        C2 = eb.matmul_dispatch(A, B)
+    finally:
+        gpu_lib.eshkol_gpu_set_threshold(100000)
+    want = gu.gemm(A, B)
+    assert gu.same_bits(C, want) and gu.same_bits(C2, want)
+    rows = [0, 1023, 1024, 2047, 2048, 2499]
+    assert gu.same_bits(C[rows], ol.oz2_exact(A[rows], B, 52))
