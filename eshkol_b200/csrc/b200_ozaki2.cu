@@ -172,22 +172,29 @@ __global__ void __launch_bounds__(256) split_a_kernel(const double* __restrict__
   }
   const double s = scale[row];
   double x[4];
+  uint32_t xlo[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) x[e] = trunc(a[e] * s);  // gpu_memory.mm:2541
+  for (int e = 0; e < 4; ++e) {
+    x[e] = trunc(a[e] * s);  // gpu_memory.mm:2541
+    xlo[e] = static_cast<uint32_t>(static_cast<long long>(x[e]));
+  }
 
   const long long o = row * g.Kp + k4;
+#pragma unroll 5
   for (int l = 0; l < g.n_odd; ++l) {
+    const double p_inv = c.p_inv[l + 1];
+    const int pi = c.p_i[l + 1];
     uint32_t word = 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e)
-      word |= (static_cast<uint32_t>(residue_odd(x[e], c.p_d[l + 1], c.p_inv[l + 1], c.p_i[l + 1])) & 0xffu) << (8 * e);
+      word |= (static_cast<uint32_t>(residue_odd(x[e], xlo[e], p_inv, pi)) & 0xffu) << (8 * e);
     *reinterpret_cast<uint32_t*>(g.odd + l * g.odd_stride + o) = word;
   }
   if (k4 < g.K) {
     uint32_t w0 = 0, w1 = 0, w2 = 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const Res256 r = residue_256(x[e]);
+      const Res256 r = residue_256(xlo[e]);
       w0 |= r.lo8 << (8 * e);
       w1 |= r.hi << (8 * e);   // pairs with B's odd flags
       w2 |= r.odd << (8 * e);  // pairs with B's +128 flags
@@ -216,19 +223,30 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
   const long long kbase = static_cast<long long>(blockIdx.y) * kSplitBK;
   const double s = (j < N) ? scale[j] : 0.0;
   const int n_planes = g.n_odd + 3;
-#pragma unroll 1
-  for (int qd = ty; qd < kSplitBK / 4; qd += 8) {
-    const long long k = kbase + qd * 4;
+  // all 16 loads of this thread are issued before any arithmetic: two resident blocks
+  // per SM then keep 64 KB of reads in flight, enough to cover HBM latency
+  double bv[4][4];
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const long long k = kbase + (ty + 8 * t) * 4;
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      bv[t][e] = (j < N && k + e < g.K) ? __ldg(B + (k + e) * N + j) : 0.0;
+  }
+#pragma unroll
+  for (int t = 0; t < 4; ++t) {
+    const int qd = ty + 8 * t;
     double x[4];
+    uint32_t xlo[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const double b = (j < N && k + e < g.K) ? __ldg(B + (k + e) * N + j) : 0.0;
-      x[e] = trunc(b * s);  // gpu_memory.mm:2546
+      x[e] = trunc(bv[t][e] * s);  // gpu_memory.mm:2546
+      xlo[e] = static_cast<uint32_t>(static_cast<long long>(x[e]));
     }
     uint32_t w0 = 0, w1 = 0, w2 = 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const Res256 r = residue_256(x[e]);
+      const Res256 r = residue_256(xlo[e]);
       w0 |= r.lo8 << (8 * e);
       w1 |= r.odd << (8 * e);  // pairs with A's +128 flags
       w2 |= r.hi << (8 * e);   // pairs with A's odd flags
@@ -236,11 +254,14 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
     sm[(0 * kSplitBJ + tx) * kSplitBPitch + qd] = w0;
     sm[(1 * kSplitBJ + tx) * kSplitBPitch + qd] = w1;
     sm[(2 * kSplitBJ + tx) * kSplitBPitch + qd] = w2;
+#pragma unroll 5
     for (int l = 0; l < g.n_odd; ++l) {
+      const double p_inv = c.p_inv[l + 1];
+      const int pi = c.p_i[l + 1];
       uint32_t word = 0;
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        word |= (static_cast<uint32_t>(residue_odd(x[e], c.p_d[l + 1], c.p_inv[l + 1], c.p_i[l + 1])) & 0xffu) << (8 * e);
+        word |= (static_cast<uint32_t>(residue_odd(x[e], xlo[e], p_inv, pi)) & 0xffu) << (8 * e);
       sm[((3 + l) * kSplitBJ + tx) * kSplitBPitch + qd] = word;
     }
   }
@@ -287,11 +308,13 @@ __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
     }
   }
   for (int l = 1; l < a.n_mod; ++l) {
-    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(a.w_odd + (l - 1) * a.w_odd_stride + wo));
+    // signed byte -> double through the mantissa: (2^52 + (b + 128)) - (2^52 + 128), exact,
+    // on the FP64 add pipe instead of the slower integer-to-double conversion unit
+    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(a.w_odd + (l - 1) * a.w_odd_stride + wo)) ^ 0x80808080u;
     const double s1 = c.sl1[l], s2 = c.sl2[l];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const double wd = static_cast<double>(static_cast<int8_t>((w >> (8 * e)) & 0xffu));
+      const double wd = __hiloint2double(0x43300000, static_cast<int>((w >> (8 * e)) & 0xffu)) - 4503599627370624.0;
       S1[e] = fma(s1, wd, S1[e]);
       S2[e] = fma(s2, wd, S2[e]);
     }

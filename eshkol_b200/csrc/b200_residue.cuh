@@ -6,18 +6,20 @@ namespace b200 {
 
 constexpr double kRoundMagic = 6755399441055744.0;  // 1.5 * 2^52
 
-// Centred residue of an integer-valued double |x| < 2^53 modulo odd p, in
-// [-(p-1)/2, (p-1)/2].  The reference evaluates x - p*rint(x*(1/p)) in f64
-// (lib/backend/gpu/gpu_memory.mm:2580); for odd p only the residue class reaches
-// the result, so the canonical representative (which always fits int8) is used.
-__device__ __forceinline__ int residue_odd(double x, double p, double p_inv, int pi) {
-  const double t = fma(x, p_inv, kRoundMagic);
-  const double q = t - kRoundMagic;          // x/p rounded to an integer, off by at most 1
-  const double r = fma(-p, q, x);            // exact, |r| <= p/2 + 1
-  int ri = __double2loint(r + kRoundMagic);  // low mantissa word = r in two's complement
-  const int h = pi >> 1;
-  ri = (ri > h) ? ri - pi : ri;
-  ri = (ri < -h) ? ri + pi : ri;
+// Residue of an integer-valued double |x| < 2^53 modulo odd p <= 255, as a value in
+// [-128, 127] of the right class; xlo is x modulo 2^32.  The reference evaluates
+// x - p*rint(x*(1/p)) in f64 (lib/backend/gpu/gpu_memory.mm:2580); for odd p only the
+// residue CLASS reaches the result (the product's final reduction has no ties), so
+// any representative that fits int8 serves.  q = x/p rounded to an integer comes out
+// of one fused multiply-add against 1.5*2^52 (its low mantissa word is q modulo 2^32;
+// q is off from the true nearest integer by at most 0.0052 because |x|/p * 2^-53 is),
+// and r = x - p*q is formed modulo 2^32 in one integer multiply-add.  |r| <= 0.5052*p,
+// i.e. within +-127 for p <= 253 and within +-128 for p = 255, where +128 is folded
+// to -127.
+__device__ __forceinline__ int residue_odd(double x, uint32_t xlo, double p_inv, int pi) {
+  const uint32_t qlo = static_cast<uint32_t>(__double2loint(fma(x, p_inv, kRoundMagic)));
+  int ri = static_cast<int>(xlo - static_cast<uint32_t>(pi) * qlo);
+  if (pi == 255) ri = (ri == 128) ? -127 : ri;
   return ri;
 }
 
@@ -27,9 +29,8 @@ struct Res256 {
 // Modulus 256: the reference's x - 256*rint(x/256) is exact; its value is the
 // centred residue with the half-even tie rule, +128 iff x = 128 (mod 512).  +128
 // does not fit int8: it is carried as the byte -128 plus a flag (times 16).
-__device__ __forceinline__ Res256 residue_256(double x) {
-  const long long xi = static_cast<long long>(x);
-  const uint32_t x512 = static_cast<uint32_t>(xi) & 511u;
+__device__ __forceinline__ Res256 residue_256(uint32_t xlo) {
+  const uint32_t x512 = xlo & 511u;
   Res256 r;
   r.lo8 = x512 & 255u;
   r.hi = (x512 == 128u) ? 16u : 0u;

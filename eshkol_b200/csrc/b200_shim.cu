@@ -168,7 +168,7 @@ static void fill_mod_job(GemmJob* j, int a_plane, int b_plane, int out_plane, un
   j->modulus = p;
   if (p) {
     j->magic = static_cast<unsigned>((1ull << 32) / p);
-    const unsigned long long bound = 2114044160ull;  // > 131071 * 127 * 127
+    const unsigned long long bound = 2147483648ull;  // > 131071 * 128 * 128
     j->offset = static_cast<unsigned>((bound + p - 1) / p * p);
   }
 }

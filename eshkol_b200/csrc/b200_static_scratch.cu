@@ -91,7 +91,7 @@ __global__ void fill_jobs_kernel(GemmJob* jobs) {
     const unsigned p = static_cast<unsigned>(c_moduli[l]);
     j.modulus = p;
     j.magic = static_cast<unsigned>((1ull << 32) / p);
-    j.offset = static_cast<unsigned>((2114044160ull + p - 1) / p * p);
+    j.offset = static_cast<unsigned>((2147483648ull + p - 1) / p * p);
   }
   jobs[l] = j;
 }

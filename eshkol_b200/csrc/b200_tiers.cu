@@ -228,9 +228,9 @@ __device__ __forceinline__ double fast_integerise(double a, int E, int es) {
   return (bits >> 63) ? -x : x;
 }
 
-__device__ __forceinline__ uint32_t fast_residue_byte(double x, int l, const Oz2DeviceConsts& c) {
-  if (c.p_i[l] == 256) return static_cast<uint32_t>(static_cast<long long>(x)) & 255u;
-  return static_cast<uint32_t>(residue_odd(x, c.p_d[l], c.p_inv[l], c.p_i[l])) & 0xffu;
+__device__ __forceinline__ uint32_t fast_residue_byte(double x, uint32_t xlo, int l, const Oz2DeviceConsts& c) {
+  if (c.p_i[l] == 256) return xlo & 255u;
+  return static_cast<uint32_t>(residue_odd(x, xlo, c.p_inv[l], c.p_i[l])) & 0xffu;
 }
 
 __global__ void __launch_bounds__(256) fast_split_a_kernel(const double* __restrict__ A,
@@ -245,12 +245,16 @@ __global__ void __launch_bounds__(256) fast_split_a_kernel(const double* __restr
   double a[4], x[4];
   load4(A + row * K + k4, k4, K, a);
   const int es = erow[row];
+  uint32_t xlo[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) x[e] = fast_integerise(a[e], E, es);
+  for (int e = 0; e < 4; ++e) {
+    x[e] = fast_integerise(a[e], E, es);
+    xlo[e] = static_cast<uint32_t>(static_cast<long long>(x[e]));
+  }
   for (int l = 0; l < c.n_mod; ++l) {
     uint32_t word = 0;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) word |= fast_residue_byte(x[e], l, c) << (8 * e);
+    for (int e = 0; e < 4; ++e) word |= fast_residue_byte(x[e], xlo[e], l, c) << (8 * e);
     *reinterpret_cast<uint32_t*>(planes + l * plane_stride + row * Kp + k4) = word;
   }
 }
@@ -270,15 +274,17 @@ __global__ void __launch_bounds__(256) fast_split_b_kernel(const double* __restr
   for (int qd = ty; qd < kTK / 4; qd += 8) {
     const long long k = kbase + qd * 4;
     double x[4];
+    uint32_t xlo[4];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const double b = (j < N && k + e < K) ? __ldg(B + (k + e) * N + j) : 0.0;
       x[e] = fast_integerise(b, E, es);
+      xlo[e] = static_cast<uint32_t>(static_cast<long long>(x[e]));
     }
     for (int l = 0; l < c.n_mod; ++l) {
       uint32_t word = 0;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) word |= fast_residue_byte(x[e], l, c) << (8 * e);
+      for (int e = 0; e < 4; ++e) word |= fast_residue_byte(x[e], xlo[e], l, c) << (8 * e);
       sm[(l * kTJ + tx) * kTPitch + qd] = word;
     }
   }

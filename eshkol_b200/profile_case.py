@@ -28,6 +28,7 @@ def main() -> None:
     ap.add_argument("--tier", default="exact", choices=sorted(TIERS))
     ap.add_argument("--param", type=int, default=0)
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--tile-n", type=int, default=0, choices=[0, 128, 256])
     ap.add_argument("--dist", default="normal", choices=["normal", "uniform", "wide"])
     args = ap.parse_args()
     M, K, N = args.m or args.n, args.k or args.n, args.n
@@ -41,7 +42,7 @@ def main() -> None:
     if lib.eshkol_b200_init(0) != 0:
         raise RuntimeError("no usable sm_100 device")
     lib.eshkol_b200_set_phase_timing(1)
-    opts = api.make_opts(TIERS[args.tier], args.param)
+    opts = api.make_opts(TIERS[args.tier], args.param, tile_n=args.tile_n)
     stream = torch.cuda.ExternalStream(api.stream_handle(), device=dev)
     out = {}
     for rep in range(args.reps):

@@ -36,17 +36,18 @@ def check_stages(A, B, simt):
     assert np.array_equal(lo.astype(np.int32), ((rb + 128) % 256) - 128)
     assert np.array_equal(hi, np.where(rb == 128, 16, 0))
     assert np.array_equal(odd, (rb & 1) * 16)
-    # odd moduli: canonical centred residue, same class as the reference's value
+    # odd moduli: an int8 representative of the same class as the reference's value
+    # (within half a modulus plus one of zero, so that K products still fit int32)
     for l in (1, 2, 8, 15):
         p = MODULI[l]
         ap, _ = api.debug_fetch(3, l - 1)
         got = ap[:, :K].astype(np.int32)
-        assert np.abs(got).max() <= (p - 1) // 2
+        assert np.abs(got).max() <= (p - 1) // 2 + 1
         assert not ((got - d["Ares"][l].astype(np.int32)) % p).any()
         assert not ap[:, K:].any()
         bp, _ = api.debug_fetch(5, l - 1)
         got = bp[:, :K].astype(np.int32)
-        assert np.abs(got).max() <= (p - 1) // 2
+        assert np.abs(got).max() <= (p - 1) // 2 + 1
         assert not ((got - d["Bres"][l].astype(np.int32).T) % p).any()
     # residues of the products
     w0, _ = api.debug_fetch(6)
@@ -201,3 +202,13 @@ def test_host_pipeline_over_several_row_blocks(gpu_lib):
     assert gu.same_bits(C, want) and gu.same_bits(C2, want)
     rows = [0, 1023, 1024, 2047, 2048, 2499]
     assert gu.same_bits(C[rows], ol.oz2_exact(A[rows], B, 52))
+
+
+def test_operands_at_the_top_of_the_53_bit_range(gpu_lib):
+    # scaled integers close to 2^53: the quotient x/p is least accurate there and the
+    # residue representatives reach their widest range
+    rng = np.random.default_rng(7)
+    A = np.ldexp(1.0 - rng.integers(0, 4096, (130, 900)) * 2.0 ** -53, 0) * rng.choice([-1.0, 1.0], (130, 900))
+    B = np.ldexp(1.0 - rng.integers(0, 4096, (900, 270)) * 2.0 ** -53, 3) * rng.choice([-1.0, 1.0], (900, 270))
+    assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, 52))
+    assert gu.same_bits(gu.gemm(A, B, simt=True), ol.oz2_exact(A, B, 52))
