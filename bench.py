@@ -150,7 +150,7 @@ def workload_config(n_gpus: int):
                             "(48-bit LCG + Box-Muller), single B200", "M": 8192, "K": 8192, "N": 8192,
                 "l2": "operands (512 MiB each) exceed the 126 MB L2; no explicit flush"}
     return {"workload": "f64 GEMM 32768x32768x32768, exact tier, entries uniform[-1,1), rows of A sharded across "
-                        f"{n_gpus} B200, B broadcast and C all-gathered over NCCL inside the step",
+                        f"{n_gpus} B200, B broadcast in 4 column panels and C all-gathered over NCCL inside the step",
             "M": 32768, "K": 32768, "N": 32768, "parallelism": f"row-shard x{n_gpus}",
             "l2": "operands exceed the 126 MB L2; no explicit flush"}
 
@@ -188,11 +188,11 @@ def run_b200(args):
         sg = None
     else:
         from eshkol_b200.sharded import ShardedGemm
-        sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16)
+        sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=4)
         rows = sg.rows
         A = inputs.uniform(1, (rows, n), device=dev, start=sg.row0 * n)
         B = inputs.uniform(2, (n, n), device=dev) if rank == 0 else None
-        C_local = sg.C_blocks[rank, :rows]
+        C_local = sg.Cp[0, rank, :rows]
     torch.cuda.synchronize()
 
     def step():
@@ -246,8 +246,8 @@ def run_b200(args):
 
     # per-stage times of one more (untimed) GEMM, for the roofline of the dominant kernel
     ph = (ctypes.c_float * 8)()
-    Bdev = B if sg is None else sg.B
-    api.gemm_device(A.data_ptr(), Bdev.data_ptr(), C_local.data_ptr(), rows, n, n, opts)
+    Bdev = B if sg is None else sg.Bp[0]
+    api.gemm_device(A.data_ptr(), Bdev.data_ptr(), C_local.data_ptr(), rows, n, Bdev.shape[1], opts)
     got = lib.eshkol_b200_get_phase_times(ph, 8)
     lib.eshkol_b200_set_phase_timing(0)
     phases = [float(x) for x in ph[:7]] if got == 7 else None
@@ -261,7 +261,7 @@ def run_b200(args):
     roofline = None
     if phases:
         t_odd = phases[5] * 1e-3
-        ops = 15 * 2.0 * rows * n * n  # 15 odd-modulus int8 GEMMs
+        ops = 15 * 2.0 * rows * n * Bdev.shape[1]  # 15 odd-modulus int8 GEMMs (one column panel when sharded)
         achieved = ops / t_odd / 1e12
         peak = 2.0 * peaks["bf16_tflops_sustained"]
         roofline = {

@@ -42,6 +42,7 @@ class GemmOpts(ctypes.Structure):
         ("pixels_per_image", ctypes.c_int64),
         ("use_simt_products", ctypes.c_int32),
         ("gemm_tile_n", ctypes.c_int32),
+        ("ldc", ctypes.c_int64),
     ]
 
 
@@ -103,6 +104,8 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_matmul_f64_host", ctypes.c_int, [vp, vp, vp, u64, u64, u64, optp])
     sig("eshkol_b200_prepare_b_f64_device", ctypes.c_int, [vp, u64, u64])
     sig("eshkol_b200_gemm_prepared_f64_device", ctypes.c_int, [vp, vp, u64, optp])
+    sig("eshkol_b200_prepare_a_f64_device", ctypes.c_int, [vp, u64, u64, u64])
+    sig("eshkol_b200_multiply_prepared_f64_device", ctypes.c_int, [vp, optp])
     sig("eshkol_b200_conv2d_f64_device", ctypes.c_int, [vp, i64, i64, i64, i64, vp, i64, i64, i64, i64, i64, vp, optp])
     sig("eshkol_b200_mem_alloc", ctypes.c_int, [ctypes.c_int, ctypes.c_size_t, ctypes.POINTER(vp)])
     sig("eshkol_b200_mem_free", None, [ctypes.c_int, vp])

@@ -79,13 +79,14 @@ def conv2d(inp, ker, stride: int = 1, pad: int = 0, activation: int = 0) -> np.n
 
 
 def make_opts(tier: int = 0, param: int = 0, activation: int = 0, bias_ptr: int = 0, bias_mode: int = 0,
-              use_simt: bool = False, tile_n: int = 0) -> GemmOpts:
+              use_simt: bool = False, tile_n: int = 0, ldc: int = 0) -> GemmOpts:
     o = GemmOpts()
     o.tier, o.param, o.activation = tier, param, activation
     o.bias_mode, o.bias = (bias_mode if bias_ptr else 0), (bias_ptr or None)
     o.pixels_per_image = 0
     o.use_simt_products = 1 if use_simt else 0
     o.gemm_tile_n = tile_n
+    o.ldc = ldc
     return o
 
 

@@ -307,16 +307,26 @@ __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
       S2[e] = fma(s2, wd, S2[e]);
     }
   }
-  for (int l = 1; l < a.n_mod; ++l) {
-    // signed byte -> double through the mantissa: (2^52 + (b + 128)) - (2^52 + 128), exact,
-    // on the FP64 add pipe instead of the slower integer-to-double conversion unit
-    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(a.w_odd + (l - 1) * a.w_odd_stride + wo)) ^ 0x80808080u;
-    const double s1 = c.sl1[l], s2 = c.sl2[l];
+  // every plane's word is requested before the first is used (15 loads in flight)
+  uint32_t wv[15];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const double wd = __hiloint2double(0x43300000, static_cast<int>((w >> (8 * e)) & 0xffu)) - 4503599627370624.0;
-      S1[e] = fma(s1, wd, S1[e]);
-      S2[e] = fma(s2, wd, S2[e]);
+  for (int l = 1; l < 16; ++l)
+    wv[l - 1] = (l < a.n_mod)
+                    ? __ldg(reinterpret_cast<const uint32_t*>(a.w_odd + (l - 1) * a.w_odd_stride + wo))
+                    : 0u;
+#pragma unroll
+  for (int l = 1; l < 16; ++l) {
+    if (l < a.n_mod) {
+      // signed byte -> double through the mantissa: (2^52 + (b + 128)) - (2^52 + 128), exact,
+      // on the FP64 add pipe instead of the slower integer-to-double conversion unit
+      const uint32_t w = wv[l - 1] ^ 0x80808080u;
+      const double s1 = c.sl1[l], s2 = c.sl2[l];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const double wd = __hiloint2double(0x43300000, static_cast<int>((w >> (8 * e)) & 0xffu)) - 4503599627370624.0;
+        S1[e] = fma(s1, wd, S1[e]);
+        S2[e] = fma(s2, wd, S2[e]);
+      }
     }
   }
   const double mu_inv = a.inv_scale_a[i];

@@ -49,6 +49,16 @@ struct State {
     CUtensorMap mB0, mB1;
     Oz2DeviceConsts consts;
   } prep;
+  struct PreparedA {
+    bool valid = false;
+    long long M = 0, K = 0, Kp = 0, K0 = 0, Mp = 0, a_stride = 0;
+    int n_chunks = 0, last_seg = 0, tiles_m = 0;
+    size_t end = 0;  // workspace offset behind the A planes, where the product residues start
+    double* amax = nullptr; int* mu = nullptr; double* sa = nullptr; double* sai = nullptr;
+    GemmJob* jobs = nullptr;
+    int8_t* a0 = nullptr; int8_t* aodd = nullptr;
+    CUtensorMap mA0, mA1;
+  } prepA;
   // host pipeline: upload / download streams and their hand-off events
   bool pipe_made = false;
   cudaStream_t s_in = nullptr, s_out = nullptr;
@@ -97,6 +107,7 @@ static int ensure_workspace(size_t bytes) {
   g.ws = nullptr;
   g.ws_bytes = 0;
   g.last.valid = false;
+  g.prepA.valid = false;
   const size_t want = bytes + (bytes >> 4);  // a little headroom against regrowth
   cudaError_t e = cudaMalloc(&g.ws, want);
   if (e != cudaSuccess) {
@@ -330,93 +341,126 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
   return 0;
 }
 
-// C[rows] = A[rows] * (prepared B): scan, split, products and reconstruction of one
-// block of rows.  Bit-identical to the same rows of a one-shot product.
-static int oz2_gemm_rows(const double* dA, double* dC, long long M, const EshkolB200GemmOpts& o) {
-  const State::Prepared& P = g.prep;
-  if (!P.valid) {
-    fprintf(stderr, "[eshkol-b200] no prepared right-hand operand\n");
-    return -1;
-  }
-  if (oz2_check_shape(M, P.K, P.N, 16)) return -1;
-  const Oz2Geom q = oz2_geometry(M, P.K, P.N, P.bn);
+// Left-hand operand prepared once: mu_i, 2^+-mu_i and the residue planes of a block
+// of rows of A, kept at the front of the workspace; room for the product residues of
+// a result up to n_cols_hint columns wide is reserved behind them so that the
+// following multiplications never move the planes.
+static int oz2_prepare_a(const double* dA, long long M, long long K, long long n_cols_hint, int bn) {
+  if (oz2_check_shape(M, K, n_cols_hint, 16)) return -1;
+  const Oz2Geom q = oz2_geometry(M, K, n_cols_hint, bn);
   const int n_odd = 15;
-  if (static_cast<long long>(q.tiles_m) * q.tiles_n * 16 > 0x7fffffffLL) return -1;
   Carver cv;
   const size_t o_amax = cv.take(M * 8), o_mu = cv.take(M * 4), o_sa = cv.take(M * 8), o_sai = cv.take(M * 8);
   const size_t o_jobs = cv.take(sizeof(GemmJob) * 16);
   const size_t o_a0 = cv.take(static_cast<size_t>(M) * q.K0);
   const size_t a_stride = static_cast<size_t>(M) * q.Kp;
   const size_t o_aodd = cv.take(a_stride * n_odd);
+  const size_t a_end = cv.off;
   const size_t w_stride = static_cast<size_t>(q.Mp) * q.Np;
-  const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
+  cv.take(w_stride * 2);
+  cv.take(w_stride * n_odd);
+  g.prepA.valid = false;
   if (ensure_workspace(cv.off) != 0) return -1;
   uint8_t* ws = g.ws;
-  double* amax = reinterpret_cast<double*>(ws + o_amax);
-  int* mu = reinterpret_cast<int*>(ws + o_mu);
-  double* sa = reinterpret_cast<double*>(ws + o_sa);
-  double* sai = reinterpret_cast<double*>(ws + o_sai);
-  GemmJob* d_jobs = reinterpret_cast<GemmJob*>(ws + o_jobs);
-  int8_t* a0 = reinterpret_cast<int8_t*>(ws + o_a0);
-  int8_t* aodd = reinterpret_cast<int8_t*>(ws + o_aodd);
+  State::PreparedA& A = g.prepA;
+  A.M = M; A.K = K; A.Kp = q.Kp; A.K0 = q.K0; A.Mp = q.Mp; A.tiles_m = q.tiles_m;
+  A.n_chunks = q.n_chunks; A.last_seg = q.last_seg; A.end = a_end;
+  A.amax = reinterpret_cast<double*>(ws + o_amax);
+  A.mu = reinterpret_cast<int*>(ws + o_mu);
+  A.sa = reinterpret_cast<double*>(ws + o_sa);
+  A.sai = reinterpret_cast<double*>(ws + o_sai);
+  A.jobs = reinterpret_cast<GemmJob*>(ws + o_jobs);
+  A.a0 = reinterpret_cast<int8_t*>(ws + o_a0);
+  A.aodd = reinterpret_cast<int8_t*>(ws + o_aodd);
+  A.a_stride = static_cast<long long>(a_stride);
+  Oz2DeviceConsts hc;
+  oz2_host_consts(16, &hc, nullptr);
+  cudaStream_t st = g.stream;
+  const bool timed = g.timing && g.ev_made;
+  B200_MARK(3);
+  B200_CHECK(launch_scan_rows(dA, M, K, A.amax, st));
+  B200_CHECK(launch_scales(A.amax, M, 52, A.mu, A.sa, A.sai, st));
+  B200_MARK(4);
+  SplitPlanes pa{M, K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, A.a0, A.aodd, A.a_stride};
+  B200_CHECK(launch_split_a(dA, A.sa, pa, hc, st));
+  B200_MARK(5);
+  g.launches += 3;
+  GemmJob jobs[16];
+  fill_mod_job(&jobs[0], 0, 0, 0, 0);
+  for (int l = 1; l < 16; ++l) fill_mod_job(&jobs[l], l - 1, l - 1, l - 1, kModuli[l]);
+  B200_CHECK(cudaMemcpyAsync(A.jobs, jobs, sizeof(GemmJob) * 16, cudaMemcpyHostToDevice, st));
+  if (make_plane_map(&A.mA0, A.a0, q.K0, M, 1, static_cast<long long>(M) * q.K0, kBM)) return -1;
+  if (make_plane_map(&A.mA1, A.aodd, q.Kp, M, n_odd, A.a_stride, kBM)) return -1;
+  A.valid = true;
+  return 0;
+}
+
+// C = (prepared A) * (prepared B): the 16 modular products on the tensor cores and
+// the reconstruction.
+static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
+  const State::Prepared& P = g.prep;
+  const State::PreparedA& A = g.prepA;
+  if (!P.valid || !A.valid) {
+    fprintf(stderr, "[eshkol-b200] multiply needs both operands prepared\n");
+    return -1;
+  }
+  if (A.K != P.K) {
+    fprintf(stderr, "[eshkol-b200] prepared operands disagree on K (%lld vs %lld)\n", A.K, P.K);
+    return -1;
+  }
+  const int n_odd = 15;
+  const long long M = A.M;
+  if (static_cast<long long>(A.tiles_m) * P.tiles_n * 16 > 0x7fffffffLL) return -1;
+  Carver cv;
+  cv.off = A.end;
+  const size_t w_stride = static_cast<size_t>(A.Mp) * P.Np;
+  const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
+  if (cv.off > g.ws_bytes) {
+    fprintf(stderr, "[eshkol-b200] result of %lld columns exceeds the room reserved when A was prepared\n", P.N);
+    return -1;
+  }
+  uint8_t* ws = g.ws;
   int16_t* w0 = reinterpret_cast<int16_t*>(ws + o_w0);
   int8_t* wodd = reinterpret_cast<int8_t*>(ws + o_wodd);
   cudaStream_t st = g.stream;
   const bool timed = g.timing && g.ev_made;
 
-  B200_MARK(3);
-  B200_CHECK(launch_scan_rows(dA, M, P.K, amax, st));
-  B200_CHECK(launch_scales(amax, M, 52, mu, sa, sai, st));
-  B200_MARK(4);
-  SplitPlanes pa{M, P.K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, a0, aodd, static_cast<long long>(a_stride)};
-  B200_CHECK(launch_split_a(dA, sa, pa, P.consts, st));
-  B200_MARK(5);
-  g.launches += 3;
-
-  GemmJob jobs[16];
-  fill_mod_job(&jobs[0], 0, 0, 0, 0);
-  for (int l = 1; l < 16; ++l) fill_mod_job(&jobs[l], l - 1, l - 1, l - 1, kModuli[l]);
-  B200_CHECK(cudaMemcpyAsync(d_jobs, jobs, sizeof(GemmJob) * 16, cudaMemcpyHostToDevice, st));
-
   GemmParams p0;
-  p0.tiles_m = q.tiles_m; p0.tiles_n = q.tiles_n; p0.n_jobs = 1;
-  p0.kb_per_seg = static_cast<int>(q.K0 / kBK);
+  p0.tiles_m = A.tiles_m; p0.tiles_n = P.tiles_n; p0.n_jobs = 1;
+  p0.kb_per_seg = static_cast<int>(A.K0 / kBK);
   p0.kb_per_unit = kChunkExt / kBK;
   p0.group_m = 16;
-  p0.jobs = d_jobs;
+  p0.jobs = A.jobs;
   p0.out = reinterpret_cast<uint8_t*>(w0);
   p0.out_plane_stride = 0;
-  p0.ldo = static_cast<int>(q.Np);
+  p0.ldo = static_cast<int>(P.Np);
   p0.status = g.d_status;
   GemmParams p1 = p0;
   p1.n_jobs = n_odd;
-  p1.kb_per_seg = static_cast<int>(q.Kp / kBK);
+  p1.kb_per_seg = static_cast<int>(A.Kp / kBK);
   p1.kb_per_unit = 1 << 28;
-  p1.jobs = d_jobs + 1;
+  p1.jobs = A.jobs + 1;
   p1.out = reinterpret_cast<uint8_t*>(wodd);
   p1.out_plane_stride = static_cast<long long>(w_stride);
-  const int tiles = q.tiles_m * q.tiles_n;
+  const int tiles = A.tiles_m * P.tiles_n;
   if (o.use_simt_products) {
-    SimtPlanes s0{a0, 0, static_cast<int>(q.K0), P.b0, 0, static_cast<int>(q.K0), static_cast<int>(M), static_cast<int>(P.N)};
-    SimtPlanes s1{aodd, static_cast<long long>(a_stride), static_cast<int>(q.Kp), P.bodd, P.bodd_stride,
-                  static_cast<int>(q.Kp), static_cast<int>(M), static_cast<int>(P.N)};
+    SimtPlanes s0{A.a0, 0, static_cast<int>(A.K0), P.b0, 0, static_cast<int>(A.K0), static_cast<int>(M), static_cast<int>(P.N)};
+    SimtPlanes s1{A.aodd, A.a_stride, static_cast<int>(A.Kp), P.bodd, P.bodd_stride,
+                  static_cast<int>(A.Kp), static_cast<int>(M), static_cast<int>(P.N)};
     B200_CHECK(launch_modgemm_simt(kEpiMod256, s0, p0, st));
     B200_MARK(6);
     B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
   } else {
-    CUtensorMap mA0, mA1;
-    if (make_plane_map(&mA0, a0, q.K0, M, 1, static_cast<long long>(M) * q.K0, kBM)) return -1;
-    if (make_plane_map(&mA1, aodd, q.Kp, M, n_odd, static_cast<long long>(a_stride), kBM)) return -1;
-    B200_CHECK(launch_modgemm(P.bn, kEpiMod256, mA0, P.mB0, p0, tiles, g.num_sms, st));
+    B200_CHECK(launch_modgemm(P.bn, kEpiMod256, A.mA0, P.mB0, p0, tiles, g.num_sms, st));
     B200_MARK(6);
-    B200_CHECK(launch_modgemm(P.bn, kEpiModI8, mA1, P.mB1, p1, tiles * n_odd, g.num_sms, st));
+    B200_CHECK(launch_modgemm(P.bn, kEpiModI8, A.mA1, P.mB1, p1, tiles * n_odd, g.num_sms, st));
   }
   B200_MARK(7);
   CrtArgs ca;
-  ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = q.Np;
+  ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = P.Np;
   ca.n_mod = 16; ca.M = M; ca.N = P.N;
-  ca.inv_scale_a = sai; ca.inv_scale_b = P.sbi;
-  ca.C = dC; ca.ldc = P.N;
+  ca.inv_scale_a = A.sai; ca.inv_scale_b = P.sbi;
+  ca.C = dC; ca.ldc = (o.ldc > 0) ? o.ldc : P.N;
   ca.bias_mode = o.bias ? o.bias_mode : 0; ca.bias = o.bias;
   ca.activation = o.activation;
   ca.pixels_per_image = o.pixels_per_image;
@@ -426,12 +470,26 @@ static int oz2_gemm_rows(const double* dA, double* dC, long long M, const Eshkol
   g.ev_valid = timed;
 
   State::Last& L = g.last;
-  L.valid = true; L.M = M; L.K = P.K; L.N = P.N; L.Kp = q.Kp; L.K0 = q.K0; L.Mp = q.Mp; L.Np = q.Np;
-  L.n_mod = 16; L.n_chunks = q.n_chunks; L.last_seg = q.last_seg;
-  L.mu = mu; L.nu = P.nu; L.a0 = a0; L.aodd = aodd; L.aodd_stride = static_cast<long long>(a_stride);
+  L.valid = true; L.M = M; L.K = P.K; L.N = P.N; L.Kp = A.Kp; L.K0 = A.K0; L.Mp = A.Mp; L.Np = P.Np;
+  L.n_mod = 16; L.n_chunks = A.n_chunks; L.last_seg = A.last_seg;
+  L.mu = A.mu; L.nu = P.nu; L.a0 = A.a0; L.aodd = A.aodd; L.aodd_stride = A.a_stride;
   L.b0 = P.b0; L.bodd = P.bodd; L.bodd_stride = P.bodd_stride;
   L.w0 = w0; L.wodd = wodd; L.wodd_stride = static_cast<long long>(w_stride);
   return 0;
+}
+
+// C[rows] = A[rows] * (prepared B) for one block of rows.  Bit-identical to the same
+// rows of a one-shot product.
+static int oz2_gemm_rows(const double* dA, double* dC, long long M, const EshkolB200GemmOpts& o) {
+  const State::Prepared& P = g.prep;
+  if (!P.valid) {
+    fprintf(stderr, "[eshkol-b200] no prepared right-hand operand\n");
+    return -1;
+  }
+  if (oz2_prepare_a(dA, M, P.K, P.N, P.bn)) return -1;
+  const int rc = oz2_multiply(dC, o);
+  g.prepA.valid = false;  // dA belongs to the caller
+  return rc;
 }
 
 // One-shot product with fewer than 16 moduli: the exponent E needs the maxima of both
@@ -532,7 +590,7 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = q.Np;
   ca.n_mod = n_mod; ca.M = M; ca.N = N;
   ca.inv_scale_a = sai; ca.inv_scale_b = sbi;
-  ca.C = dC; ca.ldc = N;
+  ca.C = dC; ca.ldc = (o.ldc > 0) ? o.ldc : N;
   ca.bias_mode = o.bias ? o.bias_mode : 0; ca.bias = o.bias;
   ca.activation = o.activation;
   ca.pixels_per_image = o.pixels_per_image;
@@ -731,6 +789,20 @@ int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, 
 int eshkol_b200_prepare_b_f64_device(const double* dB, uint64_t K, uint64_t N) {
   if (!g.ready || !dB || K == 0 || N == 0) return -1;
   return oz2_prepare_b(dB, static_cast<long long>(K), static_cast<long long>(N), 256);
+}
+
+int eshkol_b200_prepare_a_f64_device(const double* dA, uint64_t M, uint64_t K, uint64_t n_cols_hint) {
+  if (!g.ready || !dA || M == 0 || K == 0 || n_cols_hint == 0) return -1;
+  return oz2_prepare_a(dA, static_cast<long long>(M), static_cast<long long>(K),
+                       static_cast<long long>(n_cols_hint), 256);
+}
+
+int eshkol_b200_multiply_prepared_f64_device(double* dC, const EshkolB200GemmOpts* opts) {
+  if (!g.ready || !dC) return -1;
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  if (opts) o = *opts;
+  return oz2_multiply(dC, o);
 }
 
 int eshkol_b200_gemm_prepared_f64_device(const double* dA, double* dC, uint64_t M,

@@ -74,7 +74,7 @@ __device__ __forceinline__ void store_out(const Epilogue& ep, long long i, long 
 
 Epilogue make_epilogue(double* C, long long M, long long N, const EshkolB200GemmOpts& o) {
   Epilogue ep;
-  ep.C = C; ep.M = M; ep.N = N; ep.ldc = N;
+  ep.C = C; ep.M = M; ep.N = N; ep.ldc = (o.ldc > 0) ? o.ldc : N;
   ep.bias_mode = o.bias ? o.bias_mode : 0;
   ep.bias = o.bias;
   ep.activation = o.activation;

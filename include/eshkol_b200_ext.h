@@ -50,6 +50,7 @@ typedef struct EshkolB200GemmOpts {
   int64_t pixels_per_image; /* > 0: C is written as [N/pixels][M][pixels] (conv2d NCHW) */
   int32_t use_simt_products;/* tests only: integer products on CUDA cores instead of tcgen05 */
   int32_t gemm_tile_n;      /* 0 = default (256), or 128 */
+  int64_t ldc;              /* elements between rows of C; 0 = N (C may be a column panel of a wider matrix) */
 } EshkolB200GemmOpts;
 
 /* Selects `device`, creates the stream and queries the SM count.  Idempotent.
@@ -78,6 +79,14 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC,
 int eshkol_b200_prepare_b_f64_device(const double* dB, uint64_t K, uint64_t N);
 int eshkol_b200_gemm_prepared_f64_device(const double* dA, double* dC, uint64_t M,
                                          const EshkolB200GemmOpts* opts);
+/* The left-hand twin: prepare_a scans and splits a block of rows of A once (room for
+ * results up to n_cols_hint columns wide is reserved with it); multiply_prepared then
+ * forms C = A * B from the two prepared operands, e.g. once per column panel of B as
+ * the panels arrive from another GPU.  opts->ldc lets C be a column panel of a wider
+ * matrix.  The prepared A stays valid until another GEMM of this library needs more
+ * workspace than is held, or prepare_a is called again.  Asynchronous. */
+int eshkol_b200_prepare_a_f64_device(const double* dA, uint64_t M, uint64_t K, uint64_t n_cols_hint);
+int eshkol_b200_multiply_prepared_f64_device(double* dC, const EshkolB200GemmOpts* opts);
 
 /* Exact tier on HOST arrays (what eshkol_matmul_dispatch runs for large shapes): B is
  * uploaded and prepared once, then 1024-row blocks of A are uploaded, multiplied and

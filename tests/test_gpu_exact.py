@@ -212,3 +212,30 @@ def test_operands_at_the_top_of_the_53_bit_range(gpu_lib):
     B = np.ldexp(1.0 - rng.integers(0, 4096, (900, 270)) * 2.0 ** -53, 3) * rng.choice([-1.0, 1.0], (900, 270))
     assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, 52))
     assert gu.same_bits(gu.gemm(A, B, simt=True), ol.oz2_exact(A, B, 52))
+
+
+def test_prepared_a_times_column_panels_of_b(gpu_lib):
+    import ctypes
+    import torch
+    A = inputs.full53(51, (333, 1100))
+    B = inputs.full53(52, (1100, 768))
+    want = gu.gemm(A, B)
+    dA = torch.from_numpy(A).cuda()
+    dC = torch.full((333, 768), float("nan"), dtype=torch.float64, device="cuda")
+    panels = [torch.from_numpy(np.ascontiguousarray(B[:, c0:c0 + 256])).cuda() for c0 in (0, 256, 512)]
+    torch.cuda.synchronize()
+    assert gpu_lib.eshkol_b200_prepare_a_f64_device(dA.data_ptr(), 333, 1100, 256) == 0
+    for p, dB in enumerate(panels):
+        assert gpu_lib.eshkol_b200_prepare_b_f64_device(dB.data_ptr(), 1100, 256) == 0
+        opts = api.make_opts(ldc=768)  # each panel lands in its columns of the wide C
+        assert gpu_lib.eshkol_b200_multiply_prepared_f64_device(dC[:, 256 * p:].data_ptr(), ctypes.byref(opts)) == 0
+    assert api.sync_status() == 0
+    assert gu.same_bits(dC.cpu().numpy(), want)
+    # a result wider than the room reserved with A is refused, not silently moved
+    wide = torch.zeros((1100, 1024), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    assert gpu_lib.eshkol_b200_prepare_b_f64_device(wide.data_ptr(), 1100, 1024) == 0
+    big = torch.zeros((333, 1024), dtype=torch.float64, device="cuda")
+    rc = gpu_lib.eshkol_b200_multiply_prepared_f64_device(big.data_ptr(), None)
+    assert rc in (0, -1)  # 0 only if the workspace already held enough room
+    assert api.sync_status() == 0

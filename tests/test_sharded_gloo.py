@@ -23,7 +23,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, M, K, N, out_path):
+def _worker(rank, world, port, M, K, N, out_path, panels):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -34,7 +34,7 @@ def _worker(rank, world, port, M, K, N, out_path):
         def oracle_gemm(a, b, c):
             c.copy_(torch.from_numpy(ol.oz2_exact(a.numpy(), b.numpy(), 52)))
 
-        sg = ShardedGemm(M, K, N, "cpu", gemm=oracle_gemm)
+        sg = ShardedGemm(M, K, N, "cpu", gemm=oracle_gemm, panels=panels)
         r0, rows = sg.parts[rank]
         a_rows = torch.from_numpy(np.ascontiguousarray(A[r0:r0 + rows]))
         for _ in range(2):  # twice: the buffers are reused
@@ -57,11 +57,11 @@ def test_row_partition():
     assert sum(r for _, r in row_partition(32768, 8)) == 32768
 
 
-@pytest.mark.parametrize("world,M", [(2, 64), (3, 50)])
-def test_sharded_product_equals_unsharded_bits(tmp_path, world, M):
+@pytest.mark.parametrize("world,M,panels", [(2, 64, 1), (3, 50, 4)])
+def test_sharded_product_equals_unsharded_bits(tmp_path, world, M, panels):
     K, N = 300, 40
     out = str(tmp_path / "c.npy")
-    mp.spawn(_worker, args=(world, _free_port(), M, K, N, out), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, _free_port(), M, K, N, out, panels), nprocs=world, join=True)
     C = np.load(out)
     full = ol.oz2_exact(inputs.full53(1, (M, K)), inputs.full53(2, (K, N)), 52)
     assert np.array_equal(C.view(np.uint64), full.view(np.uint64))
