@@ -40,6 +40,7 @@ struct GemmParams {
   long long out_plane_stride;  // bytes
   int ldo;                     // elements per output row
   int* status;
+  int* work_counter;  // zero at launch; hands out work items beyond the first gridDim.x
 };
 
 // Launchers (b200_modgemm.cu).  bn is 128 or 256.

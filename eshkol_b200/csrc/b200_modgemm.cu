@@ -62,6 +62,9 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __shared__ uint64_t empty_bar[kStages];
   __shared__ uint64_t acc_full[2];
   __shared__ uint64_t acc_empty[2];
+  __shared__ uint64_t sched_full[2];
+  __shared__ uint64_t sched_empty[2];
+  __shared__ int sched_work[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
 
@@ -79,6 +82,8 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
       mbar_init(&acc_empty[b], 128);
+      mbar_init(&sched_full[b], 1);
+      mbar_init(&sched_empty[b], 129);  // the MMA lane and the 128 epilogue threads
     }
     abort_flag = 0;
     fence_barrier_init();
@@ -102,7 +107,20 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       uint32_t phase = 0;
       uint32_t issued = 0, last_parity = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      // Work items are handed out by a global counter, so a CTA that starts late (its
+      // SM was busy with another kernel) simply takes fewer tiles.  This lane claims
+      // the items and publishes each id to the other roles through a 2-slot ring.
+      int w = blockIdx.x;
+      for (uint32_t item = 0; ok; ++item) {
+        const uint32_t slot = item & 1u, sphase = (item >> 1) & 1u;
+        if (!mbar_wait<false>(&sched_empty[slot], sphase ^ 1u, &abort_flag)) {
+          atomicCAS(prm.status, kStatusOk, kStatusProducerTimeout);
+          abort_flag = 1;
+          break;
+        }
+        sched_work[slot] = (w < total_work) ? w : -1;
+        mbar_arrive(&sched_full[slot]);
+        if (w >= total_work) break;
         const WorkItem it = decode_work(w, prm);
         const GemmJob* job = &prm.jobs[it.job];
         const int nseg = job->n_seg;
@@ -124,6 +142,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
         }
+        w = atomicAdd(prm.work_counter, 1) + static_cast<int>(gridDim.x);
       }
       if (!ok || abort_flag) {
         // leaving early: let every copy this thread started land before the CTA exits
@@ -139,7 +158,16 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0;
       uint32_t phase = 0, unit = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      for (uint32_t item = 0; ok; ++item) {
+        const uint32_t slot = item & 1u, sphase = (item >> 1) & 1u;
+        if (!mbar_wait<false>(&sched_full[slot], sphase, &abort_flag)) {
+          atomicCAS(prm.status, kStatusOk, kStatusMmaTimeout);
+          abort_flag = 1;
+          break;
+        }
+        const int w = sched_work[slot];
+        mbar_arrive(&sched_empty[slot]);
+        if (w < 0) break;
         const WorkItem it = decode_work(w, prm);
         const int kb_total = prm.jobs[it.job].n_seg * prm.kb_per_seg;
         for (int kb0 = 0; kb0 < kb_total && ok; kb0 += prm.kb_per_unit) {
@@ -183,7 +211,16 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     uint32_t unit = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+    for (uint32_t item = 0; ok; ++item) {
+      const uint32_t slot = item & 1u, sphase = (item >> 1) & 1u;
+      if (!mbar_wait<true>(&sched_full[slot], sphase, &abort_flag)) {
+        atomicCAS(prm.status, kStatusOk, kStatusEpilogueTimeout);
+        abort_flag = 1;
+        break;
+      }
+      const int w = sched_work[slot];
+      mbar_arrive(&sched_empty[slot]);
+      if (w < 0) break;
       const WorkItem it = decode_work(w, prm);
       const GemmJob* job = &prm.jobs[it.job];
       const long long row = static_cast<long long>(it.tm) * kBM + row_in_tile;
@@ -305,6 +342,8 @@ cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
                        int total_work, int num_sms, cudaStream_t stream) {
   const int grid = total_work < num_sms ? total_work : num_sms;
   if (grid <= 0) return cudaSuccess;
+  const cudaError_t e = cudaMemsetAsync(prm.work_counter, 0, sizeof(int), stream);
+  if (e != cudaSuccess) return e;
   modgemm_kernel<BN, EPI><<<grid, kNumThreads, smem_bytes<BN>(), stream>>>(tmA, tmB, prm, total_work);
   return cudaGetLastError();
 }

@@ -435,6 +435,7 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   p0.out_plane_stride = 0;
   p0.ldo = static_cast<int>(P.Np);
   p0.status = g.d_status;
+  p0.work_counter = g.d_status + 1;
   GemmParams p1 = p0;
   p1.n_jobs = n_odd;
   p1.kb_per_seg = static_cast<int>(A.Kp / kBK);
@@ -563,6 +564,7 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   p0.out_plane_stride = 0;
   p0.ldo = static_cast<int>(q.Np);
   p0.status = g.d_status;
+  p0.work_counter = g.d_status + 1;
   GemmParams p1 = p0;
   p1.n_jobs = n_odd;
   p1.kb_per_seg = static_cast<int>(q.Kp / kBK);
@@ -706,8 +708,9 @@ int eshkol_b200_init(int device) {
   g.device = device;
   g.num_sms = prop.multiProcessorCount;
   B200_CHECK(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
-  B200_CHECK(cudaMalloc(&g.d_status, sizeof(int)));
-  B200_CHECK(cudaMemset(g.d_status, 0, sizeof(int)));
+  // [0] kernel status word, [1] work counter of the persistent products kernel
+  B200_CHECK(cudaMalloc(&g.d_status, 2 * sizeof(int)));
+  B200_CHECK(cudaMemset(g.d_status, 0, 2 * sizeof(int)));
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
   B200_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));

@@ -225,6 +225,7 @@ extern "C" int eshkol_b200_gemm_f64_static_scratch(const double* dA, const doubl
   p0.out_plane_stride = 0;
   p0.ldo = static_cast<int>(L.Np);
   p0.status = lib_status_word();
+  p0.work_counter = lib_status_word() + 1;
   GemmParams p1 = p0;
   p1.n_jobs = 15;
   p1.kb_per_seg = static_cast<int>(L.Kp / kBK);

@@ -570,6 +570,7 @@ int ozaki1_gemm(const double* dA, const double* dB, double* dC, long long M, lon
   prm.out_plane_stride = static_cast<long long>(g_stride) * 4;
   prm.ldo = static_cast<int>(Np);
   prm.status = lib_status_word();
+  prm.work_counter = lib_status_word() + 1;
   if (o.use_simt_products) {
     SimtPlanes sp{ap, static_cast<long long>(a_stride), static_cast<int>(Kp), bp,
                   static_cast<long long>(b_stride), static_cast<int>(Kp), static_cast<int>(M), static_cast<int>(N)};
@@ -667,6 +668,7 @@ int ozaki2_fast_gemm(const double* dA, const double* dB, double* dC, long long M
   prm.out_plane_stride = static_cast<long long>(w_stride);
   prm.ldo = static_cast<int>(Np);
   prm.status = lib_status_word();
+  prm.work_counter = lib_status_word() + 1;
   if (o.use_simt_products) {
     SimtPlanes sp{ap, static_cast<long long>(a_stride), static_cast<int>(Kp), bp,
                   static_cast<long long>(b_stride), static_cast<int>(Kp), static_cast<int>(M), static_cast<int>(N)};
