@@ -144,13 +144,13 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(n_gpus: int):
+def workload_config(n_gpus: int, panels: int = 0):
     if n_gpus == 1:
         return {"workload": "f64 GEMM 8192x8192x8192, exact (Ozaki-II, 16 moduli) tier, entries standard normal "
                             "(48-bit LCG + Box-Muller), single B200", "M": 8192, "K": 8192, "N": 8192,
                 "l2": "operands (512 MiB each) exceed the 126 MB L2; no explicit flush"}
     return {"workload": "f64 GEMM 32768x32768x32768, exact tier, entries uniform[-1,1), rows of A sharded across "
-                        f"{n_gpus} B200, B broadcast in 4 column panels and C all-gathered over NCCL inside the step",
+                        f"{n_gpus} B200, B broadcast and C all-gathered over NCCL inside the step",
             "M": 32768, "K": 32768, "N": 32768, "parallelism": f"row-shard x{n_gpus}",
             "l2": "operands exceed the 126 MB L2; no explicit flush"}
 
@@ -188,7 +188,10 @@ def run_b200(args):
         sg = None
     else:
         from eshkol_b200.sharded import ShardedGemm
-        sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=4)
+        # column panels of B overlap the broadcast and the gather with the products; worth it
+        # once the collectives are a visible share of the step (4 ranks and more)
+        panels = int(os.environ.get("ESHKOL_B200_PANELS", "4" if world >= 4 else "1"))
+        sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=panels)
         rows = sg.rows
         A = inputs.uniform(1, (rows, n), device=dev, start=sg.row0 * n)
         B = inputs.uniform(2, (n, n), device=dev) if rank == 0 else None
@@ -314,7 +317,7 @@ def run_b200(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f64",
-        "data": "synthetic", "config": workload_config(world), "clocks": clocks,
+        "data": "synthetic", "config": dict(workload_config(world), **({"b_panels": sg.panels} if sg else {})), "clocks": clocks,
         "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)

@@ -10,8 +10,8 @@ constexpr int kBM = 128;       // output tile rows (UMMA M, one TMEM lane per ro
 constexpr int kBK = 128;       // int8 elements per k-block = one 128-byte swizzle row
 constexpr int kMaxSeg = 8;     // operand-plane pairs accumulated into one tile
 constexpr int kChunkK = 1008;  // modulus-256 extraction interval of the reference
-constexpr int kChunkSeg = 1024;         // a chunk's segment, padded to whole k-blocks
-constexpr int kChunkExt = 3 * kChunkSeg;  // three segments per chunk (see split kernels)
+constexpr int kChunkSeg = 1024;   // a chunk inside the modulus-256 plane, padded to whole k-blocks
+constexpr int kChunkUnits = 64;   // 16-bit flag units per chunk and row (63 used: 1008 = 63 * 16)
 
 enum GemmEpilogue : int {
   kEpiModI8 = 0,     // centred residue mod an odd modulus -> int8 plane
@@ -41,6 +41,14 @@ struct GemmParams {
   int ldo;                     // elements per output row
   int* status;
   int* work_counter;  // zero at launch; hands out work items beyond the first gridDim.x
+  // kEpiMod256 only: per row / column and chunk, 64 16-bit units of flags along k
+  const uint16_t* a_hi;   // A residue == +128
+  const uint16_t* a_odd;  // A residue odd
+  const uint16_t* b_odd;  // B residue odd
+  const uint16_t* b_hi;   // B residue == +128
+  int n_chunks;
+  // kEpiMod256: per chunk, row and 32 columns, (tie mask, bit-8 mask) of the byte sums
+  uint32_t* tie_bits;
 };
 
 // Launchers (b200_modgemm.cu).  bn is 128 or 256.
@@ -48,6 +56,10 @@ cudaError_t launch_modgemm(int bn, int epi, const CUtensorMap& tmA, const CUtens
                            const GemmParams& prm, int total_work, int num_sms,
                            cudaStream_t stream);
 cudaError_t modgemm_set_attributes();
+// After a kEpiMod256 launch: flip_bits[row][word] = which elements' sums need 256 added.
+// The CUDA-core checker resolves its ties itself; its flip bits must be cleared instead.
+cudaError_t launch_tie_resolve(const GemmParams& prm, uint32_t* flip_bits, int M, int N,
+                               cudaStream_t stream);
 
 // Plain CUDA-core version of the same job table, used by tests to localise a
 // fault to the tensor-core kernel; never on the product path.
@@ -56,6 +68,19 @@ struct SimtPlanes {
   const int8_t* b_base; long long b_plane_stride; int ldb;
   int M, N;
 };
+
+// Zero-initialised parameter block (flag pointers null unless the caller sets them).
+inline GemmParams make_gemm_params() {
+  GemmParams p;
+  p.tiles_m = p.tiles_n = p.n_jobs = 0;
+  p.kb_per_seg = 0; p.kb_per_unit = 1 << 28; p.group_m = 16;
+  p.jobs = nullptr; p.out = nullptr; p.out_plane_stride = 0; p.ldo = 0;
+  p.status = nullptr; p.work_counter = nullptr;
+  p.a_hi = p.a_odd = p.b_odd = p.b_hi = nullptr;
+  p.n_chunks = 0;
+  p.tie_bits = nullptr;
+  return p;
+}
 cudaError_t launch_modgemm_simt(int epi, const SimtPlanes& pl, const GemmParams& prm,
                                 cudaStream_t stream);
 

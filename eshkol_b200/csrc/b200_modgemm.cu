@@ -5,7 +5,8 @@
 //   warp 1      allocates TMEM; one lane issues tcgen05.mma (M=128, N=BN, K=32)
 //               into one of two TMEM accumulators and commits to mbarriers
 //   warps 2-5   drain a finished accumulator with tcgen05.ld and run the epilogue
-//               (residue mod p -> int8, raw int32, or the chunked mod-256 rule)
+//               (residue mod p -> int8, raw int32, or the chunked mod-256 rule with its
+//               tie look-up in the operands' flag bit-planes)
 // Work items are (job, output tile); a job is a sum of plane-pair products, so a
 // whole diagonal of slice products or one modulus accumulates without leaving TMEM.
 //
@@ -14,12 +15,18 @@
 // calls (lib/backend/gpu/gpu_memory_cuda.cpp:413-436).
 #include "b200_common.cuh"
 #include "b200_internal.h"
+#include "b200_residue.cuh"
 
 namespace b200 {
 
 namespace {
 
-constexpr int kNumThreads = 192;
+// warps 0 and 1 load and issue; 4 epilogue warps, or 8 for the chunked modulus-256 mode whose
+// epilogue runs once per 8 k-blocks instead of once per tile
+template <int EPI> struct EpiShape {
+  static constexpr int kWarps = (EPI == kEpiMod256) ? 8 : 4;
+  static constexpr int kThreads = 64 + 32 * kWarps;
+};
 constexpr int kUmmaK = 32;
 
 struct WorkItem {
@@ -49,7 +56,7 @@ __device__ __forceinline__ int center256(uint32_t x512) {
 }
 
 template <int BN, int EPI>
-__global__ void __launch_bounds__(kNumThreads, 1)
+__global__ void __launch_bounds__(EpiShape<EPI>::kThreads, 1)
 modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const GemmParams prm, const int total_work) {
   constexpr int kStages = (BN == 256) ? 4 : 6;
@@ -81,9 +88,9 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&acc_full[b], 1);
-      mbar_init(&acc_empty[b], 128);
+      mbar_init(&acc_empty[b], 32 * EpiShape<EPI>::kWarps);
       mbar_init(&sched_full[b], 1);
-      mbar_init(&sched_empty[b], 129);  // the MMA lane and the 128 epilogue threads
+      mbar_init(&sched_empty[b], 1 + 32 * EpiShape<EPI>::kWarps);  // the MMA lane and the epilogue threads
     }
     abort_flag = 0;
     fence_barrier_init();
@@ -228,11 +235,21 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       const long long elem0 = row * prm.ldo + static_cast<long long>(it.tn) * BN;
 
       if (EPI == kEpiMod256) {
+        // Eight warps: warps w and w+4 read the same 32 TMEM lanes and take half of the
+        // columns each.  The accumulator holds the chunk sum formed with the int8 bytes:
+        // the true sum modulo 256, and modulo 512 up to the parity of the +128 / odd flag
+        // products.  Bit 8 only matters when the sum is 128 modulo 256 (it then decides
+        // +128 against -128), so those elements are only marked here, for a parity look-up
+        // by tie_resolve_kernel.  Arithmetic runs on two 16-bit lanes per register:
+        //   t = sum & 255;  residue mod 512 = t + 256*[t > 128]  (a tie counts as +128).
+        constexpr int kHalfCc = BN / 64;  // 32-column groups per warp
+        const int half = (warp - 2) >> 2;
         const int kb_total = job->n_seg * prm.kb_per_seg;
-        uint32_t wsum[BN / 2];  // running sum of chunk residues, two 16-bit lanes per word
+        uint32_t wsum[BN / 4];
 #pragma unroll
-        for (int i = 0; i < BN / 2; ++i) wsum[i] = 0u;
-        for (int kb0 = 0; kb0 < kb_total && ok; kb0 += prm.kb_per_unit) {
+        for (int i = 0; i < BN / 4; ++i) wsum[i] = 0u;
+        int chunk = 0;
+        for (int kb0 = 0; kb0 < kb_total && ok; kb0 += prm.kb_per_unit, ++chunk) {
           const uint32_t buf = unit & 1u, aphase = (unit >> 1) & 1u;
           if (!mbar_wait<true>(&acc_full[buf], aphase, &abort_flag)) {
             atomicCAS(prm.status, kStatusOk, kStatusEpilogueTimeout);
@@ -242,37 +259,42 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           tc_fence_after();
 #pragma unroll
-          for (int cc = 0; cc < BN / 32; ++cc) {
+          for (int c2 = 0; c2 < kHalfCc; ++c2) {
+            const int cc = half * kHalfCc + c2;
             uint32_t v[32];
             tmem_ld32(tmem_base + lane_addr + buf * BN + cc * 32, v);
             tmem_ld_wait();
+            uint32_t tie = 0, bit8 = 0;  // bit p: element 2p, bit 16+p: element 2p+1
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              const int r0 = center256(v[e] & 511u);
-              const int r1 = center256(v[e + 1] & 511u);
-              const uint32_t packed = (static_cast<uint32_t>(r0) & 0xffffu) |
-                                      (static_cast<uint32_t>(r1) << 16);
-              wsum[cc * 16 + e / 2] = __vadd2(wsum[cc * 16 + e / 2], packed);
+            for (int p2 = 0; p2 < 16; ++p2) {
+              const uint32_t pr = __byte_perm(v[2 * p2], v[2 * p2 + 1], 0x5410);  // low halves
+              const uint32_t t = pr & 0x00ff00ffu;
+              const uint32_t gt = (t + 0x007f007fu) & 0x01000100u;   // 256 where t > 128
+              wsum[c2 * 16 + p2] += t + gt;                          // lanes stay below 2^16
+              const uint32_t x = t ^ 0x00800080u;                    // zero lane <=> t == 128
+              const uint32_t z = (x - 0x00010001u) & ~x & 0x80008000u;
+              tie |= __funnelshift_r(z, z, (15 - p2) & 31);
+              const uint32_t b8 = pr & 0x01000100u;
+              bit8 |= __funnelshift_r(b8, b8, (8 - p2) & 31);
             }
+            uint2* rec = reinterpret_cast<uint2*>(prm.tie_bits) +
+                         ((static_cast<long long>(chunk) * prm.tiles_m * kBM + row) * (prm.ldo / 32) +
+                          static_cast<long long>(it.tn) * (BN / 32) + cc);
+            *rec = make_uint2(tie, bit8);
           }
           tc_fence_before();
           mbar_arrive(&acc_empty[buf]);
           ++unit;
         }
         if (ok) {
-          int16_t* dst = reinterpret_cast<int16_t*>(out_plane) + elem0;
+          // sum of the chunk residues modulo 512, ties counted as +128; the reconstruction
+          // adds 256 per tie that was really -128 and centres
+          int16_t* dst = reinterpret_cast<int16_t*>(out_plane) + elem0 + half * (BN / 2);
 #pragma unroll
-          for (int i = 0; i < BN / 2; i += 4) {
-            uint32_t o[4];
-#pragma unroll
-            for (int t = 0; t < 4; ++t) {
-              const uint32_t ws = wsum[i + t];
-              const int w0 = center256(ws & 511u);
-              const int w1 = center256((ws >> 16) & 511u);
-              o[t] = (static_cast<uint32_t>(w0) & 0xffffu) | (static_cast<uint32_t>(w1) << 16);
-            }
-            *reinterpret_cast<uint4*>(dst + 2 * i) = make_uint4(o[0], o[1], o[2], o[3]);
-          }
+          for (int i = 0; i < BN / 4; i += 4)
+            *reinterpret_cast<uint4*>(dst + 2 * i) =
+                make_uint4(wsum[i] & 0x01ff01ffu, wsum[i + 1] & 0x01ff01ffu, wsum[i + 2] & 0x01ff01ffu,
+                           wsum[i + 3] & 0x01ff01ffu);
         }
       } else {
         const uint32_t buf = unit & 1u, aphase = (unit >> 1) & 1u;
@@ -344,7 +366,7 @@ cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   if (grid <= 0) return cudaSuccess;
   const cudaError_t e = cudaMemsetAsync(prm.work_counter, 0, sizeof(int), stream);
   if (e != cudaSuccess) return e;
-  modgemm_kernel<BN, EPI><<<grid, kNumThreads, smem_bytes<BN>(), stream>>>(tmA, tmB, prm, total_work);
+  modgemm_kernel<BN, EPI><<<grid, EpiShape<EPI>::kThreads, smem_bytes<BN>(), stream>>>(tmA, tmB, prm, total_work);
   return cudaGetLastError();
 }
 
@@ -365,15 +387,21 @@ __global__ void modgemm_simt_kernel(int epi, SimtPlanes pl, GemmParams prm, int 
     const int8_t* b = pl.b_base + static_cast<long long>(job->b_plane[0]) * pl.b_plane_stride +
                       static_cast<long long>(j) * pl.ldb;
     const int unit_k = prm.kb_per_unit * kBK;
-    int w = 0;
-    for (int k0 = 0; k0 < K_per_seg; k0 += unit_k) {
+    int w = 0, chunk = 0;
+    for (int k0 = 0; k0 < K_per_seg; k0 += unit_k, ++chunk) {
       int acc = 0;
       const int k1 = min(k0 + unit_k, K_per_seg);
       for (int k = k0; k < k1; ++k) acc += static_cast<int>(a[k]) * static_cast<int>(b[k]);
-      w += center256(static_cast<uint32_t>(acc) & 511u);
+      uint32_t x = static_cast<uint32_t>(acc) & 511u;
+      if ((x & 255u) == 128u) {
+        const long long fa = (static_cast<long long>(i) * prm.n_chunks + chunk) * kChunkUnits;
+        const long long fb = (static_cast<long long>(j) * prm.n_chunks + chunk) * kChunkUnits;
+        x ^= chunk_flag_parity(prm.a_hi + fa, prm.a_odd + fa, prm.b_odd + fb, prm.b_hi + fb) << 8;
+      }
+      w += center256(x);
     }
-    reinterpret_cast<int16_t*>(out_plane)[o] =
-        static_cast<int16_t>(center256(static_cast<uint32_t>(w) & 511u));
+    // ties are resolved here, so the value is final: the flip bits of this element stay clear
+    reinterpret_cast<int16_t*>(out_plane)[o] = static_cast<int16_t>(static_cast<uint32_t>(w) & 511u);
     return;
   }
   int acc = 0;
@@ -393,6 +421,61 @@ __global__ void modgemm_simt_kernel(int epi, SimtPlanes pl, GemmParams prm, int 
     if (r > (p >> 1)) r -= p;
     reinterpret_cast<int8_t*>(out_plane)[o] = static_cast<int8_t>(r);
   }
+}
+
+// One warp per (row, 32 words of 32 columns).  The products kernel marked the elements
+// whose byte sum was 128 modulo 256 in some chunk; for each of them the warp forms the
+// parity of the flag products sum_k hi_a*odd_b + odd_a*hi_b over that chunk -- lane l holds
+// 32-bit word l of the row's two flag vectors and loads word l of the column's -- and
+// compares it with bit 8 of the byte sum: if they differ the true sum was 384 modulo 512,
+// the residue -128 rather than +128, and 256 has to be added to the element's total.  The
+// XOR of those corrections over the chunks is the element's flip bit.
+__global__ void __launch_bounds__(256) tie_resolve_kernel(const uint2* __restrict__ tie_bits,
+                                                          uint32_t* __restrict__ flip_bits,
+                                                          GemmParams prm, int M, int N) {
+  const int lane = threadIdx.x & 31;
+  const int words = prm.ldo / 32;
+  const int groups = (words + 31) / 32;
+  const long long rows_p = static_cast<long long>(prm.tiles_m) * kBM;
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  if (gw >= rows_p * groups) return;
+  const long long row = gw / groups;
+  const int cw = static_cast<int>(gw - row * groups) * 32 + lane;
+  const bool valid = cw < words;
+  const uint32_t* a_hi = reinterpret_cast<const uint32_t*>(prm.a_hi);
+  const uint32_t* a_odd = reinterpret_cast<const uint32_t*>(prm.a_odd);
+  const uint32_t* b_hi = reinterpret_cast<const uint32_t*>(prm.b_hi);
+  const uint32_t* b_odd = reinterpret_cast<const uint32_t*>(prm.b_odd);
+  constexpr int kWordsPerChunk = kChunkUnits / 2;  // 32
+  uint32_t flip = 0;
+  if (row < M) {
+    for (int chunk = 0; chunk < prm.n_chunks; ++chunk) {
+      uint2 rec = make_uint2(0u, 0u);
+      if (valid) rec = __ldg(tie_bits + (static_cast<long long>(chunk) * rows_p + row) * words + cw);
+      uint32_t tie = rec.x;
+      uint32_t bal = __ballot_sync(0xffffffffu, tie != 0u);
+      if (bal == 0u) continue;
+      const long long fa = (row * prm.n_chunks + chunk) * kWordsPerChunk + lane;
+      const uint32_t ahi = __ldg(a_hi + fa), aodd = __ldg(a_odd + fa);
+      while (bal != 0u) {
+        const int src = __ffs(bal) - 1;
+        const int b = __shfl_sync(0xffffffffu, __ffs(tie) - 1, src);  // mask bit p: element 2p, 16+p: 2p+1
+        const int scw = __shfl_sync(0xffffffffu, cw, src);
+        const int e = (b < 16) ? 2 * b : 2 * (b - 16) + 1;
+        const long long col = static_cast<long long>(scw) * 32 + e;
+        if (col < N) {
+          const long long fb = (col * prm.n_chunks + chunk) * kWordsPerChunk + lane;
+          uint32_t x = __popc(ahi & __ldg(b_odd + fb)) ^ __popc(aodd & __ldg(b_hi + fb));
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) x ^= __shfl_xor_sync(0xffffffffu, x, o);
+          if (lane == src) flip ^= (((rec.y >> b) & 1u) ^ (x & 1u)) << e;
+        }
+        if (lane == src) tie &= tie - 1u;
+        bal = __ballot_sync(0xffffffffu, tie != 0u);
+      }
+    }
+  }
+  if (valid) flip_bits[row * words + cw] = flip;
 }
 
 }  // namespace
@@ -426,6 +509,16 @@ cudaError_t launch_modgemm(int bn, int epi, const CUtensorMap& tmA, const CUtens
     if (epi == kEpiMod256) return launch_one<128, kEpiMod256>(tmA, tmB, prm, total_work, num_sms, stream);
   }
   return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_tie_resolve(const GemmParams& prm, uint32_t* flip_bits, int M, int N,
+                               cudaStream_t stream) {
+  const int words = prm.ldo / 32;
+  const long long warps = static_cast<long long>(prm.tiles_m) * kBM * ((words + 31) / 32);
+  if (warps <= 0) return cudaSuccess;
+  tie_resolve_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, stream>>>(
+      reinterpret_cast<const uint2*>(prm.tie_bits), flip_bits, prm, M, N);
+  return cudaGetLastError();
 }
 
 cudaError_t launch_modgemm_simt(int epi, const SimtPlanes& pl, const GemmParams& prm,

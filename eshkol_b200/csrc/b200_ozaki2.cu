@@ -1,7 +1,8 @@
 // Bandwidth-bound stages of the Ozaki-II exact f64 GEMM:
 //   scan      per-row max|A|, per-column max|B|
 //   scales    mu_i = E - floor(log2 amax_i), nu_j likewise, and the 2^(+/-mu) factors
-//   split     trunc(a * 2^mu) -> centred residues for every modulus, int8 planes
+//   split     trunc(a * 2^mu) -> residues for every modulus, int8 planes (+ two flag
+//             bit-planes for modulus 256, whose representative +128 does not fit int8)
 //             (A planes row-major M x Kp, B planes TRANSPOSED to N x Kp so both GEMM
 //             operands are K-major), 128-bit loads, whole-word / 16-byte stores
 //   crt       S1/S2 accumulation over the residue planes of the products, Q, the two
@@ -135,21 +136,23 @@ __global__ void scales_kernel(const double* __restrict__ vmax, long long n, int 
 struct SplitGeom {
   long long rows;      // M for A, N for B
   long long K, Kp;     // logical and padded (multiple of 128) inner extent
-  long long K0;        // inner extent of the modulus-256 plane (three segments per chunk)
+  long long K0;        // inner extent of the modulus-256 plane (1024 per chunk of 1008)
   int n_chunks;        // ceil(K / 1008)
-  int last_seg;        // segment length of the last chunk, a multiple of 128
   int n_odd;           // number of odd-modulus planes (n_mod - 1)
-  int8_t* plane0;      // rows x K0
+  int8_t* plane0;      // rows x K0: the residue bytes modulo 256
+  uint16_t* flag_hi;   // rows x n_chunks x 64 units: residue == +128
+  uint16_t* flag_odd;  // rows x n_chunks x 64 units: residue odd
   int8_t* odd;         // n_odd planes of rows x Kp
   long long odd_stride;
 };
 
-// column of element k of the first segment inside the modulus-256 plane
-__device__ __forceinline__ void ext_cols(const SplitGeom& g, long long k, long long* c0, int* seglen) {
+// element k of a row -> column inside the modulus-256 plane and 16-bit flag unit
+__device__ __forceinline__ void chunk_cols(const SplitGeom& g, long long k, long long* col,
+                                           long long* unit) {
   const int c = static_cast<int>(k / kChunkK);
   const int off = static_cast<int>(k - static_cast<long long>(c) * kChunkK);
-  *seglen = (c == g.n_chunks - 1) ? g.last_seg : kChunkSeg;
-  *c0 = static_cast<long long>(c) * kChunkExt + off;
+  *col = static_cast<long long>(c) * kChunkSeg + off;
+  *unit = static_cast<long long>(c) * kChunkUnits + (off >> 4);
 }
 
 // A: one thread per 4 consecutive k of one row.  grid = (rows, ceil(Kp/1024)).
@@ -190,21 +193,31 @@ __global__ void __launch_bounds__(256) split_a_kernel(const double* __restrict__
       word |= (static_cast<uint32_t>(residue_odd(x[e], xlo[e], p_inv, pi)) & 0xffu) << (8 * e);
     *reinterpret_cast<uint32_t*>(g.odd + l * g.odd_stride + o) = word;
   }
-  if (k4 < g.K) {
-    uint32_t w0 = 0, w1 = 0, w2 = 0;
+  // modulus 256: the byte, and the two flag bits of each element gathered into 16-bit
+  // units along k (4 lanes x 4 elements; chunk boundaries are multiples of 16)
+  uint32_t w0 = 0, nib_hi = 0, nib_odd = 0;
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const Res256 r = residue_256(xlo[e]);
-      w0 |= r.lo8 << (8 * e);
-      w1 |= r.hi << (8 * e);   // pairs with B's odd flags
-      w2 |= r.odd << (8 * e);  // pairs with B's +128 flags
+  for (int e = 0; e < 4; ++e) {
+    const Res256 r = residue_256(xlo[e]);
+    w0 |= r.lo8 << (8 * e);
+    nib_hi |= r.hi << e;
+    nib_odd |= r.odd << e;
+  }
+  const int sh = 4 * (threadIdx.x & 3);
+  uint32_t u_hi = nib_hi << sh, u_odd = nib_odd << sh;
+  u_hi |= __shfl_xor_sync(0xffffffffu, u_hi, 1);
+  u_odd |= __shfl_xor_sync(0xffffffffu, u_odd, 1);
+  u_hi |= __shfl_xor_sync(0xffffffffu, u_hi, 2);
+  u_odd |= __shfl_xor_sync(0xffffffffu, u_odd, 2);
+  if (k4 < g.K) {
+    long long col, unit;
+    chunk_cols(g, k4, &col, &unit);
+    *reinterpret_cast<uint32_t*>(g.plane0 + row * g.K0 + col) = w0;
+    if ((threadIdx.x & 3) == 0) {
+      const long long fo = row * g.n_chunks * kChunkUnits + unit;
+      g.flag_hi[fo] = static_cast<uint16_t>(u_hi);
+      g.flag_odd[fo] = static_cast<uint16_t>(u_odd);
     }
-    long long c0; int seglen;
-    ext_cols(g, k4, &c0, &seglen);
-    int8_t* dst = g.plane0 + row * g.K0 + c0;
-    *reinterpret_cast<uint32_t*>(dst) = w0;
-    *reinterpret_cast<uint32_t*>(dst + seglen) = w1;
-    *reinterpret_cast<uint32_t*>(dst + 2 * seglen) = w2;
   }
 }
 
@@ -217,12 +230,12 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
                                                       const double* __restrict__ scale,
                                                       long long N, const SplitGeom g,
                                                       const __grid_constant__ Oz2DeviceConsts c) {
-  extern __shared__ uint32_t sm[];  // [n_odd + 3][32][33]
+  extern __shared__ uint32_t sm[];  // [n_odd + 2][32][33]: bytes mod 256, flag nibbles, odd moduli
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const long long j = static_cast<long long>(blockIdx.x) * kSplitBJ + tx;
   const long long kbase = static_cast<long long>(blockIdx.y) * kSplitBK;
   const double s = (j < N) ? scale[j] : 0.0;
-  const int n_planes = g.n_odd + 3;
+  const int n_planes = g.n_odd + 2;
   // all 16 loads of this thread are issued before any arithmetic: two resident blocks
   // per SM then keep 64 KB of reads in flight, enough to cover HBM latency
   double bv[4][4];
@@ -243,17 +256,15 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
       x[e] = trunc(bv[t][e] * s);  // gpu_memory.mm:2546
       xlo[e] = static_cast<uint32_t>(static_cast<long long>(x[e]));
     }
-    uint32_t w0 = 0, w1 = 0, w2 = 0;
+    uint32_t w0 = 0, nib = 0;
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const Res256 r = residue_256(xlo[e]);
       w0 |= r.lo8 << (8 * e);
-      w1 |= r.odd << (8 * e);  // pairs with A's +128 flags
-      w2 |= r.hi << (8 * e);   // pairs with A's odd flags
+      nib |= (r.odd << e) | (r.hi << (8 + e));  // byte 0: odd flags, byte 1: +128 flags
     }
     sm[(0 * kSplitBJ + tx) * kSplitBPitch + qd] = w0;
-    sm[(1 * kSplitBJ + tx) * kSplitBPitch + qd] = w1;
-    sm[(2 * kSplitBJ + tx) * kSplitBPitch + qd] = w2;
+    sm[(1 * kSplitBJ + tx) * kSplitBPitch + qd] = nib;
 #pragma unroll 5
     for (int l = 0; l < g.n_odd; ++l) {
       const double p_inv = c.p_inv[l + 1];
@@ -262,7 +273,7 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
 #pragma unroll
       for (int e = 0; e < 4; ++e)
         word |= (static_cast<uint32_t>(residue_odd(x[e], xlo[e], p_inv, pi)) & 0xffu) << (8 * e);
-      sm[((3 + l) * kSplitBJ + tx) * kSplitBPitch + qd] = word;
+      sm[((2 + l) * kSplitBJ + tx) * kSplitBPitch + qd] = word;
     }
   }
   __syncthreads();
@@ -273,14 +284,25 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
   const long long k16 = kbase + gq * 16;
   for (int pl = 0; pl < n_planes; ++pl) {
     const uint32_t* srcw = &sm[(pl * kSplitBJ + jj) * kSplitBPitch + gq * 4];
-    const uint4 v = make_uint4(srcw[0], srcw[1], srcw[2], srcw[3]);
-    if (pl >= 3) {
+    if (pl >= 2) {
       if (k16 < g.Kp)
-        *reinterpret_cast<uint4*>(g.odd + (pl - 3) * g.odd_stride + jo * g.Kp + k16) = v;
+        *reinterpret_cast<uint4*>(g.odd + (pl - 2) * g.odd_stride + jo * g.Kp + k16) =
+            make_uint4(srcw[0], srcw[1], srcw[2], srcw[3]);
     } else if (k16 < g.K) {
-      long long c0; int seglen;
-      ext_cols(g, k16, &c0, &seglen);
-      *reinterpret_cast<uint4*>(g.plane0 + jo * g.K0 + c0 + static_cast<long long>(pl) * seglen) = v;
+      long long col, unit;
+      chunk_cols(g, k16, &col, &unit);
+      if (pl == 0) {
+        *reinterpret_cast<uint4*>(g.plane0 + jo * g.K0 + col) = make_uint4(srcw[0], srcw[1], srcw[2], srcw[3]);
+      } else {
+        // four nibbles per flag -> one 16-bit unit each
+        const uint32_t f_odd = (srcw[0] & 15u) | ((srcw[1] & 15u) << 4) | ((srcw[2] & 15u) << 8) |
+                               ((srcw[3] & 15u) << 12);
+        const uint32_t f_hi = ((srcw[0] >> 8) & 15u) | (((srcw[1] >> 8) & 15u) << 4) |
+                              (((srcw[2] >> 8) & 15u) << 8) | (((srcw[3] >> 8) & 15u) << 12);
+        const long long fo = jo * g.n_chunks * kChunkUnits + unit;
+        g.flag_odd[fo] = static_cast<uint16_t>(f_odd);
+        g.flag_hi[fo] = static_cast<uint16_t>(f_hi);
+      }
     }
   }
 }
@@ -296,13 +318,17 @@ __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
   const long long wo = i * a.ldw + j4;
   double S1[4] = {0.0, 0.0, 0.0, 0.0}, S2[4] = {0.0, 0.0, 0.0, 0.0};
   {
+    // modulus 256: finish the reduction the products kernel left open -- apply the tie
+    // corrections, then centre with the half-even rule (+128 iff the sum is 128 mod 512)
     const uint2 w = __ldg(reinterpret_cast<const uint2*>(a.w0 + wo));
-    const int v[4] = {static_cast<int16_t>(w.x & 0xffffu), static_cast<int16_t>(w.x >> 16),
-                      static_cast<int16_t>(w.y & 0xffffu), static_cast<int16_t>(w.y >> 16)};
+    const uint32_t fl = __ldg(a.flip + i * (a.ldw >> 5) + (j4 >> 5)) >> (j4 & 31);
+    const uint32_t raw[4] = {w.x & 0xffffu, w.x >> 16, w.y & 0xffffu, w.y >> 16};
     const double s1 = c.sl1[0], s2 = c.sl2[0];
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      const double wd = static_cast<double>(v[e]);
+      const uint32_t x = (raw[e] + (((fl >> e) & 1u) << 8)) & 511u;
+      const int v = (x == 128u) ? 128 : static_cast<int>((x + 128u) & 255u) - 128;
+      const double wd = static_cast<double>(v);
       S1[e] = fma(s1, wd, S1[e]);
       S2[e] = fma(s2, wd, S2[e]);
     }
@@ -331,26 +357,43 @@ __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
   }
   const double mu_inv = a.inv_scale_a[i];
   const double P1 = c.P1, P2 = c.P2, Pinv = c.Pinv;
+  double out[4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) {
-    const long long j = j4 + e;
-    if (j >= a.N) break;
+    const long long j = (j4 + e < a.N) ? j4 + e : a.N - 1;
     const double s = __dadd_rn(S1[e], S2[e]);
     const double Q = round(__dmul_rn(s, Pinv));  // half away from zero, as round()
     const double c1 = fma(-P1, Q, S1[e]);
     const double c2 = fma(-P2, Q, S2[e]);
-    double c = __dmul_rn(__dmul_rn(__dadd_rn(c1, c2), mu_inv), a.inv_scale_b[j]);
-    if (a.bias_mode == 1) c = __dadd_rn(c, a.bias[i]);
-    else if (a.bias_mode == 2) c = __dadd_rn(c, a.bias[j]);
-    if (a.activation == 1) c = (c > 0.0) ? c : 0.0;  // gpu_cuda_kernels.cu:37
-    long long o;
-    if (a.pixels_per_image > 0) {
+    double v = __dmul_rn(__dmul_rn(__dadd_rn(c1, c2), mu_inv), a.inv_scale_b[j]);
+    if (a.bias_mode == 1) v = __dadd_rn(v, a.bias[i]);
+    else if (a.bias_mode == 2) v = __dadd_rn(v, a.bias[j]);
+    if (a.activation == 1) v = (v > 0.0) ? v : 0.0;  // gpu_cuda_kernels.cu:37
+    out[e] = v;
+  }
+  if (a.pixels_per_image > 0) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const long long j = j4 + e;
+      if (j >= a.N) break;
       const long long img = j / a.pixels_per_image, pix = j - img * a.pixels_per_image;
-      o = (img * a.M + i) * a.pixels_per_image + pix;  // [image][row][pixel]
-    } else {
-      o = i * a.ldc + j;
+      a.C[(img * a.M + i) * a.pixels_per_image + pix] = out[e];  // [image][row][pixel]
     }
-    a.C[o] = c;
+    return;
+  }
+  double* dst = a.C + i * a.ldc + j4;
+  if (j4 + 3 < a.N && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+    // one 32-byte store per thread: whole sectors, a quarter of the store instructions
+    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst),
+                 "f"(__int_as_float(__double2loint(out[0]))), "f"(__int_as_float(__double2hiint(out[0]))),
+                 "f"(__int_as_float(__double2loint(out[1]))), "f"(__int_as_float(__double2hiint(out[1]))),
+                 "f"(__int_as_float(__double2loint(out[2]))), "f"(__int_as_float(__double2hiint(out[2]))),
+                 "f"(__int_as_float(__double2loint(out[3]))), "f"(__int_as_float(__double2hiint(out[3])))
+                 : "memory");
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (j4 + e < a.N) dst[e] = out[e];
   }
 }
 
@@ -382,17 +425,28 @@ cudaError_t launch_scales(const double* vmax, long long n, int E, int* shift, do
   return cudaGetLastError();
 }
 
+// the padding inside the modulus-256 plane and the unused flag units must read as zero
+static cudaError_t clear_plane0(const SplitPlanes& p, cudaStream_t st) {
+  cudaError_t e = cudaMemsetAsync(p.plane0, 0, static_cast<size_t>(p.rows) * p.K0, st);
+  if (e != cudaSuccess) return e;
+  const size_t fb = static_cast<size_t>(p.rows) * p.n_chunks * kChunkUnits * sizeof(uint16_t);
+  e = cudaMemsetAsync(p.flag_hi, 0, fb, st);
+  if (e != cudaSuccess) return e;
+  return cudaMemsetAsync(p.flag_odd, 0, fb, st);
+}
+
 static SplitGeom make_geom(const SplitPlanes& p) {
   SplitGeom g;
   g.rows = p.rows; g.K = p.K; g.Kp = p.Kp; g.K0 = p.K0;
-  g.n_chunks = p.n_chunks; g.last_seg = p.last_seg; g.n_odd = p.n_odd;
-  g.plane0 = p.plane0; g.odd = p.odd; g.odd_stride = p.odd_stride;
+  g.n_chunks = p.n_chunks; g.n_odd = p.n_odd;
+  g.plane0 = p.plane0; g.flag_hi = p.flag_hi; g.flag_odd = p.flag_odd;
+  g.odd = p.odd; g.odd_stride = p.odd_stride;
   return g;
 }
 
 cudaError_t launch_split_a(const double* A, const double* scale, const SplitPlanes& p,
                            const Oz2DeviceConsts& c, cudaStream_t st) {
-  cudaError_t e = cudaMemsetAsync(p.plane0, 0, static_cast<size_t>(p.rows) * p.K0, st);
+  cudaError_t e = clear_plane0(p, st);
   if (e != cudaSuccess) return e;
   const dim3 grid(static_cast<unsigned>(p.rows), static_cast<unsigned>((p.Kp + 1023) / 1024));
   if (grid.y > 65535u) return cudaErrorInvalidValue;
@@ -401,7 +455,7 @@ cudaError_t launch_split_a(const double* A, const double* scale, const SplitPlan
 }
 
 size_t split_b_smem_bytes(int n_odd) {
-  return static_cast<size_t>(n_odd + 3) * kSplitBJ * kSplitBPitch * sizeof(uint32_t);
+  return static_cast<size_t>(n_odd + 2) * kSplitBJ * kSplitBPitch * sizeof(uint32_t);
 }
 
 cudaError_t split_set_attributes() {
@@ -411,7 +465,7 @@ cudaError_t split_set_attributes() {
 
 cudaError_t launch_split_b(const double* B, const double* scale, long long N, const SplitPlanes& p,
                            const Oz2DeviceConsts& c, cudaStream_t st) {
-  cudaError_t e = cudaMemsetAsync(p.plane0, 0, static_cast<size_t>(p.rows) * p.K0, st);
+  cudaError_t e = clear_plane0(p, st);
   if (e != cudaSuccess) return e;
   const dim3 grid(static_cast<unsigned>((N + kSplitBJ - 1) / kSplitBJ),
                   static_cast<unsigned>(p.Kp / kSplitBK));

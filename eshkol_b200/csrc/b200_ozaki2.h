@@ -18,14 +18,17 @@ struct Oz2DeviceConsts {
 struct SplitPlanes {
   long long rows;       // M (A) or N (B)
   long long K, Kp, K0;  // logical, padded-to-128, and modulus-256-plane inner extents
-  int n_chunks, last_seg, n_odd;
-  int8_t* plane0;       // rows x K0
+  int n_chunks, n_odd;
+  int8_t* plane0;       // rows x K0 (1024 bytes per 1008-element chunk)
+  uint16_t* flag_hi;    // rows x n_chunks x 64 units of 16 bits along k: residue == +128
+  uint16_t* flag_odd;   // same shape: residue odd
   int8_t* odd;          // n_odd planes, each rows x Kp
   long long odd_stride; // bytes between odd planes
 };
 
 struct CrtArgs {
-  const int16_t* w0;     // modulus-256 residues of the products, M_pad x ldw
+  const int16_t* w0;     // modulus 256: sum of the chunk residues mod 512, ties taken as +128; M_pad x ldw
+  const uint32_t* flip;  // one bit per element of w0: add 256 (a tie was -128); M_pad x ldw/32 words
   const int8_t* w_odd;   // odd-modulus residues, (n_mod-1) planes of M_pad x ldw
   long long w_odd_stride;
   long long ldw;

@@ -24,18 +24,38 @@ __device__ __forceinline__ int residue_odd(double x, uint32_t xlo, double p_inv,
 }
 
 struct Res256 {
-  uint32_t lo8, hi, odd;  // a (mod 256) as a byte, 16*[a == +128], 16*[a odd]
+  uint32_t lo8, hi, odd;  // a (mod 256) as a byte, [a == +128], [a odd]
 };
 // Modulus 256: the reference's x - 256*rint(x/256) is exact; its value is the
 // centred residue with the half-even tie rule, +128 iff x = 128 (mod 512).  +128
-// does not fit int8: it is carried as the byte -128 plus a flag (times 16).
+// does not fit int8: it is carried as the byte -128 plus a flag bit.
 __device__ __forceinline__ Res256 residue_256(uint32_t xlo) {
   const uint32_t x512 = xlo & 511u;
   Res256 r;
   r.lo8 = x512 & 255u;
-  r.hi = (x512 == 128u) ? 16u : 0u;
-  r.odd = (x512 & 1u) ? 16u : 0u;
+  r.hi = (x512 == 128u) ? 1u : 0u;
+  r.odd = x512 & 1u;
   return r;
+}
+
+// Parity of sum_k hi_a[k]*odd_b[k] + odd_a[k]*hi_b[k] over one chunk, from the 128-byte
+// flag rows of the two operands.  This is bit 8 of the true chunk sum minus bit 8 of
+// the sum formed with the int8 bytes alone: a = a8 + 256*[a = +128] gives
+// a*b = a8*b8 + 256*([a=+128]*b + a8*[b=+128]) (mod 512), and 256*x depends on x mod 2.
+__device__ __forceinline__ uint32_t chunk_flag_parity(const uint16_t* a_hi, const uint16_t* a_odd,
+                                                      const uint16_t* b_odd, const uint16_t* b_hi) {
+  const uint4* ah = reinterpret_cast<const uint4*>(a_hi);
+  const uint4* ao = reinterpret_cast<const uint4*>(a_odd);
+  const uint4* bo = reinterpret_cast<const uint4*>(b_odd);
+  const uint4* bh = reinterpret_cast<const uint4*>(b_hi);
+  uint32_t acc = 0;
+#pragma unroll 2
+  for (int w = 0; w < 8; ++w) {
+    const uint4 x = __ldg(ah + w), y = __ldg(bo + w), z = __ldg(ao + w), t = __ldg(bh + w);
+    acc ^= __popc(x.x & y.x) ^ __popc(x.y & y.y) ^ __popc(x.z & y.z) ^ __popc(x.w & y.w);
+    acc ^= __popc(z.x & t.x) ^ __popc(z.y & t.y) ^ __popc(z.z & t.z) ^ __popc(z.w & t.w);
+  }
+  return acc & 1u;
 }
 
 }  // namespace b200

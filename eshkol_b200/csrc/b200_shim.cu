@@ -46,6 +46,7 @@ struct State {
     int n_chunks = 0, last_seg = 0, bn = 256, tiles_n = 0;
     double* bmax = nullptr; int* nu = nullptr; double* sb = nullptr; double* sbi = nullptr;
     int8_t* b0 = nullptr; int8_t* bodd = nullptr; long long bodd_stride = 0;
+    uint16_t* b_hi = nullptr; uint16_t* b_odd = nullptr;  // flag bit-planes of the modulus-256 residues
     CUtensorMap mB0, mB1;
     Oz2DeviceConsts consts;
   } prep;
@@ -57,6 +58,7 @@ struct State {
     double* amax = nullptr; int* mu = nullptr; double* sa = nullptr; double* sai = nullptr;
     GemmJob* jobs = nullptr;
     int8_t* a0 = nullptr; int8_t* aodd = nullptr;
+    uint16_t* a_hi = nullptr; uint16_t* a_odd = nullptr;
     CUtensorMap mA0, mA1;
   } prepA;
   // host pipeline: upload / download streams and their hand-off events
@@ -72,6 +74,8 @@ struct State {
     int8_t* a0 = nullptr; int8_t* aodd = nullptr; long long aodd_stride = 0;
     int8_t* b0 = nullptr; int8_t* bodd = nullptr; long long bodd_stride = 0;
     int16_t* w0 = nullptr; int8_t* wodd = nullptr; long long wodd_stride = 0;
+    uint16_t* a_hi = nullptr; uint16_t* a_odd = nullptr; uint16_t* b_hi = nullptr; uint16_t* b_odd = nullptr;
+    uint32_t* flip = nullptr;
   } last;
 };
 static State g;
@@ -262,7 +266,7 @@ static Oz2Geom oz2_geometry(long long M, long long K, long long N, int bn) {
   q.n_chunks = static_cast<int>((K + kChunkK - 1) / kChunkK);
   const int last_len = static_cast<int>(K - static_cast<long long>(q.n_chunks - 1) * kChunkK);
   q.last_seg = static_cast<int>(round_up(last_len, kBK));
-  q.K0 = static_cast<long long>(q.n_chunks - 1) * kChunkExt + 3LL * q.last_seg;
+  q.K0 = static_cast<long long>(q.n_chunks - 1) * kChunkSeg + q.last_seg;
   q.tiles_m = static_cast<int>((M + kBM - 1) / kBM);
   q.tiles_n = static_cast<int>((N + bn - 1) / bn);
   q.Mp = static_cast<long long>(q.tiles_m) * kBM;
@@ -298,6 +302,8 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
   Carver cv;
   const size_t o_bmax = cv.take(N * 8), o_nu = cv.take(N * 4), o_sb = cv.take(N * 8), o_sbi = cv.take(N * 8);
   const size_t o_b0 = cv.take(static_cast<size_t>(N) * q.K0);
+  const size_t flag_bytes = static_cast<size_t>(N) * q.n_chunks * kChunkUnits * sizeof(uint16_t);
+  const size_t o_bhi = cv.take(flag_bytes), o_bodd_f = cv.take(flag_bytes);
   const size_t b_stride = static_cast<size_t>(N) * q.Kp;
   const size_t o_bodd = cv.take(b_stride * n_odd);
   g.prep.valid = false;
@@ -321,6 +327,8 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
   P.sb = reinterpret_cast<double*>(ws + o_sb);
   P.sbi = reinterpret_cast<double*>(ws + o_sbi);
   P.b0 = reinterpret_cast<int8_t*>(ws + o_b0);
+  P.b_hi = reinterpret_cast<uint16_t*>(ws + o_bhi);
+  P.b_odd = reinterpret_cast<uint16_t*>(ws + o_bodd_f);
   P.bodd = reinterpret_cast<int8_t*>(ws + o_bodd);
   P.bodd_stride = static_cast<long long>(b_stride);
   oz2_host_consts(16, &P.consts, nullptr);
@@ -331,7 +339,7 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
   B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(P.bmax), st));
   B200_CHECK(launch_scales(P.bmax, N, 52, P.nu, P.sb, P.sbi, st));
   B200_MARK(1);
-  SplitPlanes pb{N, K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, P.b0, P.bodd, P.bodd_stride};
+  SplitPlanes pb{N, K, q.Kp, q.K0, q.n_chunks, n_odd, P.b0, P.b_hi, P.b_odd, P.bodd, P.bodd_stride};
   B200_CHECK(launch_split_b(dB, P.sb, N, pb, P.consts, st));
   B200_MARK(2);
   g.launches += 3;
@@ -353,12 +361,16 @@ static int oz2_prepare_a(const double* dA, long long M, long long K, long long n
   const size_t o_amax = cv.take(M * 8), o_mu = cv.take(M * 4), o_sa = cv.take(M * 8), o_sai = cv.take(M * 8);
   const size_t o_jobs = cv.take(sizeof(GemmJob) * 16);
   const size_t o_a0 = cv.take(static_cast<size_t>(M) * q.K0);
+  const size_t flag_bytes = static_cast<size_t>(M) * q.n_chunks * kChunkUnits * sizeof(uint16_t);
+  const size_t o_ahi = cv.take(flag_bytes), o_aodd_f = cv.take(flag_bytes);
   const size_t a_stride = static_cast<size_t>(M) * q.Kp;
   const size_t o_aodd = cv.take(a_stride * n_odd);
   const size_t a_end = cv.off;
   const size_t w_stride = static_cast<size_t>(q.Mp) * q.Np;
   cv.take(w_stride * 2);
   cv.take(w_stride * n_odd);
+  cv.take(w_stride / 32 * 8 * q.n_chunks);  // tie / bit-8 masks per chunk
+  cv.take(w_stride / 32 * 4);               // flip bits
   g.prepA.valid = false;
   if (ensure_workspace(cv.off) != 0) return -1;
   uint8_t* ws = g.ws;
@@ -371,6 +383,8 @@ static int oz2_prepare_a(const double* dA, long long M, long long K, long long n
   A.sai = reinterpret_cast<double*>(ws + o_sai);
   A.jobs = reinterpret_cast<GemmJob*>(ws + o_jobs);
   A.a0 = reinterpret_cast<int8_t*>(ws + o_a0);
+  A.a_hi = reinterpret_cast<uint16_t*>(ws + o_ahi);
+  A.a_odd = reinterpret_cast<uint16_t*>(ws + o_aodd_f);
   A.aodd = reinterpret_cast<int8_t*>(ws + o_aodd);
   A.a_stride = static_cast<long long>(a_stride);
   Oz2DeviceConsts hc;
@@ -381,7 +395,7 @@ static int oz2_prepare_a(const double* dA, long long M, long long K, long long n
   B200_CHECK(launch_scan_rows(dA, M, K, A.amax, st));
   B200_CHECK(launch_scales(A.amax, M, 52, A.mu, A.sa, A.sai, st));
   B200_MARK(4);
-  SplitPlanes pa{M, K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, A.a0, A.aodd, A.a_stride};
+  SplitPlanes pa{M, K, q.Kp, q.K0, q.n_chunks, n_odd, A.a0, A.a_hi, A.a_odd, A.aodd, A.a_stride};
   B200_CHECK(launch_split_a(dA, A.sa, pa, hc, st));
   B200_MARK(5);
   g.launches += 3;
@@ -415,6 +429,7 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   cv.off = A.end;
   const size_t w_stride = static_cast<size_t>(A.Mp) * P.Np;
   const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
+  const size_t o_tie = cv.take(w_stride / 32 * 8 * A.n_chunks), o_flip = cv.take(w_stride / 32 * 4);
   if (cv.off > g.ws_bytes) {
     fprintf(stderr, "[eshkol-b200] result of %lld columns exceeds the room reserved when A was prepared\n", P.N);
     return -1;
@@ -422,13 +437,18 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   uint8_t* ws = g.ws;
   int16_t* w0 = reinterpret_cast<int16_t*>(ws + o_w0);
   int8_t* wodd = reinterpret_cast<int8_t*>(ws + o_wodd);
+  uint32_t* tie_bits = reinterpret_cast<uint32_t*>(ws + o_tie);
+  uint32_t* flip_bits = reinterpret_cast<uint32_t*>(ws + o_flip);
   cudaStream_t st = g.stream;
   const bool timed = g.timing && g.ev_made;
 
-  GemmParams p0;
+  GemmParams p0 = make_gemm_params();
+  p0.tie_bits = tie_bits;
   p0.tiles_m = A.tiles_m; p0.tiles_n = P.tiles_n; p0.n_jobs = 1;
   p0.kb_per_seg = static_cast<int>(A.K0 / kBK);
-  p0.kb_per_unit = kChunkExt / kBK;
+  p0.kb_per_unit = kChunkSeg / kBK;
+  p0.a_hi = A.a_hi; p0.a_odd = A.a_odd; p0.b_odd = P.b_odd; p0.b_hi = P.b_hi;
+  p0.n_chunks = A.n_chunks;
   p0.group_m = 16;
   p0.jobs = A.jobs;
   p0.out = reinterpret_cast<uint8_t*>(w0);
@@ -449,16 +469,18 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
     SimtPlanes s1{A.aodd, A.a_stride, static_cast<int>(A.Kp), P.bodd, P.bodd_stride,
                   static_cast<int>(A.Kp), static_cast<int>(M), static_cast<int>(P.N)};
     B200_CHECK(launch_modgemm_simt(kEpiMod256, s0, p0, st));
+    B200_CHECK(cudaMemsetAsync(flip_bits, 0, w_stride / 32 * 4, st));
     B200_MARK(6);
     B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
   } else {
     B200_CHECK(launch_modgemm(P.bn, kEpiMod256, A.mA0, P.mB0, p0, tiles, g.num_sms, st));
+    B200_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(P.N), st));
     B200_MARK(6);
     B200_CHECK(launch_modgemm(P.bn, kEpiModI8, A.mA1, P.mB1, p1, tiles * n_odd, g.num_sms, st));
   }
   B200_MARK(7);
   CrtArgs ca;
-  ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = P.Np;
+  ca.w0 = w0; ca.flip = flip_bits; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = P.Np;
   ca.n_mod = 16; ca.M = M; ca.N = P.N;
   ca.inv_scale_a = A.sai; ca.inv_scale_b = P.sbi;
   ca.C = dC; ca.ldc = (o.ldc > 0) ? o.ldc : P.N;
@@ -467,7 +489,7 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   ca.pixels_per_image = o.pixels_per_image;
   B200_CHECK(launch_crt(ca, P.consts, st));
   B200_MARK(8);
-  g.launches += 3;
+  g.launches += 4;
   g.ev_valid = timed;
 
   State::Last& L = g.last;
@@ -476,6 +498,7 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   L.mu = A.mu; L.nu = P.nu; L.a0 = A.a0; L.aodd = A.aodd; L.aodd_stride = A.a_stride;
   L.b0 = P.b0; L.bodd = P.bodd; L.bodd_stride = P.bodd_stride;
   L.w0 = w0; L.wodd = wodd; L.wodd_stride = static_cast<long long>(w_stride);
+  L.a_hi = A.a_hi; L.a_odd = A.a_odd; L.b_hi = P.b_hi; L.b_odd = P.b_odd; L.flip = flip_bits;
   return 0;
 }
 
@@ -509,12 +532,19 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   const size_t o_sb = cv.take(N * 8), o_sbi = cv.take(N * 8);
   const size_t o_jobs = cv.take(sizeof(GemmJob) * 16);
   const size_t o_a0 = cv.take(static_cast<size_t>(M) * q.K0), o_b0 = cv.take(static_cast<size_t>(N) * q.K0);
+  const size_t fa_bytes = static_cast<size_t>(M) * q.n_chunks * kChunkUnits * sizeof(uint16_t);
+  const size_t fb_bytes = static_cast<size_t>(N) * q.n_chunks * kChunkUnits * sizeof(uint16_t);
+  const size_t o_ahi = cv.take(fa_bytes), o_aoddf = cv.take(fa_bytes);
+  const size_t o_bhi = cv.take(fb_bytes), o_boddf = cv.take(fb_bytes);
   const size_t a_stride = static_cast<size_t>(M) * q.Kp, b_stride = static_cast<size_t>(N) * q.Kp;
   const size_t o_aodd = cv.take(a_stride * n_odd), o_bodd = cv.take(b_stride * n_odd);
   const size_t w_stride = static_cast<size_t>(q.Mp) * q.Np;
   const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
+  const size_t o_tie = cv.take(w_stride / 32 * 8 * q.n_chunks), o_flip = cv.take(w_stride / 32 * 4);
   if (ensure_workspace(cv.off) != 0) return -1;
   uint8_t* ws = g.ws;
+  uint32_t* tie_bits = reinterpret_cast<uint32_t*>(ws + o_tie);
+  uint32_t* flip_bits = reinterpret_cast<uint32_t*>(ws + o_flip);
   double* amax = reinterpret_cast<double*>(ws + o_amax);
   double* bmax = reinterpret_cast<double*>(ws + o_bmax);
   int* mu = reinterpret_cast<int*>(ws + o_mu);
@@ -528,6 +558,10 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   int8_t* b0 = reinterpret_cast<int8_t*>(ws + o_b0);
   int8_t* aodd = reinterpret_cast<int8_t*>(ws + o_aodd);
   int8_t* bodd = reinterpret_cast<int8_t*>(ws + o_bodd);
+  uint16_t* a_hi = reinterpret_cast<uint16_t*>(ws + o_ahi);
+  uint16_t* a_oddf = reinterpret_cast<uint16_t*>(ws + o_aoddf);
+  uint16_t* b_hi = reinterpret_cast<uint16_t*>(ws + o_bhi);
+  uint16_t* b_oddf = reinterpret_cast<uint16_t*>(ws + o_boddf);
   int16_t* w0 = reinterpret_cast<int16_t*>(ws + o_w0);
   int8_t* wodd = reinterpret_cast<int8_t*>(ws + o_wodd);
   cudaStream_t st = g.stream;
@@ -545,8 +579,8 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   const int E = oz2_exponent(log2P, K, ha.data(), M, hb.data(), N);
   B200_CHECK(launch_scales(amax, M, E, mu, sa, sai, st));
   B200_CHECK(launch_scales(bmax, N, E, nu, sb, sbi, st));
-  SplitPlanes pa{M, K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, a0, aodd, static_cast<long long>(a_stride)};
-  SplitPlanes pb{N, K, q.Kp, q.K0, q.n_chunks, q.last_seg, n_odd, b0, bodd, static_cast<long long>(b_stride)};
+  SplitPlanes pa{M, K, q.Kp, q.K0, q.n_chunks, n_odd, a0, a_hi, a_oddf, aodd, static_cast<long long>(a_stride)};
+  SplitPlanes pb{N, K, q.Kp, q.K0, q.n_chunks, n_odd, b0, b_hi, b_oddf, bodd, static_cast<long long>(b_stride)};
   B200_CHECK(launch_split_a(dA, sa, pa, hc, st));
   B200_CHECK(launch_split_b(dB, sb, N, pb, hc, st));
 
@@ -554,10 +588,13 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   fill_mod_job(&jobs[0], 0, 0, 0, 0);
   for (int l = 1; l < n_mod; ++l) fill_mod_job(&jobs[l], l - 1, l - 1, l - 1, kModuli[l]);
   B200_CHECK(cudaMemcpyAsync(d_jobs, jobs, sizeof(GemmJob) * n_mod, cudaMemcpyHostToDevice, st));
-  GemmParams p0;
+  GemmParams p0 = make_gemm_params();
   p0.tiles_m = q.tiles_m; p0.tiles_n = q.tiles_n; p0.n_jobs = 1;
   p0.kb_per_seg = static_cast<int>(q.K0 / kBK);
-  p0.kb_per_unit = kChunkExt / kBK;
+  p0.kb_per_unit = kChunkSeg / kBK;
+  p0.a_hi = a_hi; p0.a_odd = a_oddf; p0.b_odd = b_oddf; p0.b_hi = b_hi;
+  p0.n_chunks = q.n_chunks;
+  p0.tie_bits = tie_bits;
   p0.group_m = 16;
   p0.jobs = d_jobs;
   p0.out = reinterpret_cast<uint8_t*>(w0);
@@ -578,6 +615,7 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
     SimtPlanes s1{aodd, static_cast<long long>(a_stride), static_cast<int>(q.Kp), bodd,
                   static_cast<long long>(b_stride), static_cast<int>(q.Kp), static_cast<int>(M), static_cast<int>(N)};
     B200_CHECK(launch_modgemm_simt(kEpiMod256, s0, p0, st));
+    B200_CHECK(cudaMemsetAsync(flip_bits, 0, w_stride / 32 * 4, st));
     B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
   } else {
     CUtensorMap mA0, mB0, mA1, mB1;
@@ -586,10 +624,11 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
     if (make_plane_map(&mA1, aodd, q.Kp, M, n_odd, static_cast<long long>(a_stride), kBM)) return -1;
     if (make_plane_map(&mB1, bodd, q.Kp, N, n_odd, static_cast<long long>(b_stride), bn)) return -1;
     B200_CHECK(launch_modgemm(bn, kEpiMod256, mA0, mB0, p0, tiles, g.num_sms, st));
+    B200_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(N), st));
     B200_CHECK(launch_modgemm(bn, kEpiModI8, mA1, mB1, p1, tiles * n_odd, g.num_sms, st));
   }
   CrtArgs ca;
-  ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = q.Np;
+  ca.w0 = w0; ca.flip = flip_bits; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = q.Np;
   ca.n_mod = n_mod; ca.M = M; ca.N = N;
   ca.inv_scale_a = sai; ca.inv_scale_b = sbi;
   ca.C = dC; ca.ldc = (o.ldc > 0) ? o.ldc : N;
@@ -597,7 +636,7 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   ca.activation = o.activation;
   ca.pixels_per_image = o.pixels_per_image;
   B200_CHECK(launch_crt(ca, hc, st));
-  g.launches += 9;
+  g.launches += 10;
 
   State::Last& L = g.last;
   L.valid = true; L.M = M; L.K = K; L.N = N; L.Kp = q.Kp; L.K0 = q.K0; L.Mp = q.Mp; L.Np = q.Np;
@@ -605,6 +644,7 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   L.mu = mu; L.nu = nu; L.a0 = a0; L.aodd = aodd; L.aodd_stride = static_cast<long long>(a_stride);
   L.b0 = b0; L.bodd = bodd; L.bodd_stride = static_cast<long long>(b_stride);
   L.w0 = w0; L.wodd = wodd; L.wodd_stride = static_cast<long long>(w_stride);
+  L.a_hi = a_hi; L.a_odd = a_oddf; L.b_hi = b_hi; L.b_odd = b_oddf; L.flip = flip_bits;
   return 0;
 }
 #undef B200_MARK
@@ -929,6 +969,11 @@ int eshkol_b200_debug_fetch(int what, int index, void* host_dst, uint64_t capaci
     case 6: src = L.w0; rows = L.Mp; pitch = L.Np; esz = 2; break;
     case 7: if (index < 0 || index >= n_odd) return -1;
             src = L.wodd + index * L.wodd_stride; rows = L.Mp; pitch = L.Np; break;
+    case 8: src = L.a_hi; rows = L.M; pitch = static_cast<uint64_t>(L.n_chunks) * kChunkUnits; esz = 2; break;
+    case 9: src = L.a_odd; rows = L.M; pitch = static_cast<uint64_t>(L.n_chunks) * kChunkUnits; esz = 2; break;
+    case 10: src = L.b_hi; rows = L.N; pitch = static_cast<uint64_t>(L.n_chunks) * kChunkUnits; esz = 2; break;
+    case 12: src = L.flip; rows = L.Mp; pitch = L.Np / 32; esz = 4; break;
+    case 11: src = L.b_odd; rows = L.N; pitch = static_cast<uint64_t>(L.n_chunks) * kChunkUnits; esz = 2; break;
     default: return -1;
   }
   const uint64_t bytes = rows * pitch * esz;

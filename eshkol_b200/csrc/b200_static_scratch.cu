@@ -22,8 +22,8 @@
 // that loads the library holds those 24 MiB until the process exits.
 //
 // All calls share the one array.  It keeps whatever the previous call left; the
-// parts that must start from zero (the modulus-256 planes, the column-maximum
-// accumulators) are cleared inside each call.  Calls are ordered by the library's
+// parts that must start from zero (the modulus-256 planes and their flag bit-planes,
+// the column-maximum accumulators) are cleared inside each call.  Calls are ordered by the library's
 // stream; two calls made to overlap on the GPU by other means would race on the
 // array and must not be issued.
 //
@@ -100,7 +100,7 @@ struct Layout {
   long long Kp, K0, Mp, Np;
   int n_chunks, last_seg, tiles_m, tiles_n;
   size_t o_amax, o_bmax, o_mu, o_nu, o_sa, o_sai, o_sb, o_sbi, o_jobs, o_a0, o_b0, o_aodd, o_bodd,
-      o_w0, o_wodd, total;
+      o_w0, o_wodd, o_ahi, o_aoddf, o_bhi, o_boddf, o_tie, o_flip, total;
   size_t a_stride, b_stride, w_stride;
 };
 
@@ -110,8 +110,8 @@ inline size_t take(size_t& off, size_t bytes) {
   return o;
 }
 
-// Scratch a shape needs: vectors of M and N, 18 bytes per element of A and of B
-// (padded), 17 bytes per element of the padded C.
+// Scratch a shape needs: vectors of M and N, a little over 16 bytes per element of A
+// and of B (padded), 17 bytes per element of the padded C.
 Layout scratch_need(long long M, long long K, long long N) {
   Layout L;
   const int bn = 256;
@@ -119,7 +119,7 @@ Layout scratch_need(long long M, long long K, long long N) {
   L.n_chunks = static_cast<int>((K + kChunkK - 1) / kChunkK);
   const int last_len = static_cast<int>(K - static_cast<long long>(L.n_chunks - 1) * kChunkK);
   L.last_seg = (last_len + kBK - 1) / kBK * kBK;
-  L.K0 = static_cast<long long>(L.n_chunks - 1) * kChunkExt + 3LL * L.last_seg;
+  L.K0 = static_cast<long long>(L.n_chunks - 1) * kChunkSeg + L.last_seg;
   L.tiles_m = static_cast<int>((M + kBM - 1) / kBM);
   L.tiles_n = static_cast<int>((N + bn - 1) / bn);
   L.Mp = static_cast<long long>(L.tiles_m) * kBM;
@@ -132,6 +132,10 @@ Layout scratch_need(long long M, long long K, long long N) {
   L.o_jobs = take(off, sizeof(GemmJob) * 16);
   L.o_a0 = take(off, static_cast<size_t>(M) * L.K0);
   L.o_b0 = take(off, static_cast<size_t>(N) * L.K0);
+  const size_t fa = static_cast<size_t>(M) * L.n_chunks * kChunkUnits * 2;
+  const size_t fb = static_cast<size_t>(N) * L.n_chunks * kChunkUnits * 2;
+  L.o_ahi = take(off, fa); L.o_aoddf = take(off, fa);
+  L.o_bhi = take(off, fb); L.o_boddf = take(off, fb);
   L.a_stride = static_cast<size_t>(M) * L.Kp;
   L.b_stride = static_cast<size_t>(N) * L.Kp;
   L.o_aodd = take(off, L.a_stride * 15);
@@ -139,6 +143,8 @@ Layout scratch_need(long long M, long long K, long long N) {
   L.w_stride = static_cast<size_t>(L.Mp) * L.Np;
   L.o_w0 = take(off, L.w_stride * 2);
   L.o_wodd = take(off, L.w_stride * 15);
+  L.o_tie = take(off, L.w_stride / 32 * 8 * L.n_chunks);
+  L.o_flip = take(off, L.w_stride / 32 * 4);
   L.total = off;
   return L;
 }
@@ -196,8 +202,14 @@ extern "C" int eshkol_b200_gemm_f64_static_scratch(const double* dA, const doubl
   int8_t* b0 = reinterpret_cast<int8_t*>(ws + L.o_b0);
   int8_t* aodd = reinterpret_cast<int8_t*>(ws + L.o_aodd);
   int8_t* bodd = reinterpret_cast<int8_t*>(ws + L.o_bodd);
+  uint16_t* a_hi = reinterpret_cast<uint16_t*>(ws + L.o_ahi);
+  uint16_t* a_oddf = reinterpret_cast<uint16_t*>(ws + L.o_aoddf);
+  uint16_t* b_hi = reinterpret_cast<uint16_t*>(ws + L.o_bhi);
+  uint16_t* b_oddf = reinterpret_cast<uint16_t*>(ws + L.o_boddf);
   int16_t* w0 = reinterpret_cast<int16_t*>(ws + L.o_w0);
   int8_t* wodd = reinterpret_cast<int8_t*>(ws + L.o_wodd);
+  uint32_t* tie_bits = reinterpret_cast<uint32_t*>(ws + L.o_tie);
+  uint32_t* flip_bits = reinterpret_cast<uint32_t*>(ws + L.o_flip);
 
   Oz2DeviceConsts hc;
   oz2_host_consts(16, &hc, nullptr);
@@ -207,18 +219,21 @@ extern "C" int eshkol_b200_gemm_f64_static_scratch(const double* dA, const doubl
   SS_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(bmax), st));
   SS_CHECK(launch_scales(amax, M, 52, mu, sa, sai, st));
   SS_CHECK(launch_scales(bmax, N, 52, nu, sb, sbi, st));
-  SplitPlanes pa{M, K, L.Kp, L.K0, L.n_chunks, L.last_seg, 15, a0, aodd, static_cast<long long>(L.a_stride)};
-  SplitPlanes pb{N, K, L.Kp, L.K0, L.n_chunks, L.last_seg, 15, b0, bodd, static_cast<long long>(L.b_stride)};
-  // each clears its modulus-256 plane before writing into it
+  SplitPlanes pa{M, K, L.Kp, L.K0, L.n_chunks, 15, a0, a_hi, a_oddf, aodd, static_cast<long long>(L.a_stride)};
+  SplitPlanes pb{N, K, L.Kp, L.K0, L.n_chunks, 15, b0, b_hi, b_oddf, bodd, static_cast<long long>(L.b_stride)};
+  // each clears its modulus-256 plane and flag bit-planes before writing into them
   SS_CHECK(launch_split_a(dA, sa, pa, hc, st));
   SS_CHECK(launch_split_b(dB, sb, N, pb, hc, st));
   fill_jobs_kernel<<<1, 32, 0, st>>>(jobs);
   SS_CHECK(cudaGetLastError());
 
-  GemmParams p0;
+  GemmParams p0 = make_gemm_params();
   p0.tiles_m = L.tiles_m; p0.tiles_n = L.tiles_n; p0.n_jobs = 1;
   p0.kb_per_seg = static_cast<int>(L.K0 / kBK);
-  p0.kb_per_unit = kChunkExt / kBK;
+  p0.kb_per_unit = kChunkSeg / kBK;
+  p0.a_hi = a_hi; p0.a_odd = a_oddf; p0.b_odd = b_oddf; p0.b_hi = b_hi;
+  p0.n_chunks = L.n_chunks;
+  p0.tie_bits = tie_bits;
   p0.group_m = 16;
   p0.jobs = jobs;
   p0.out = reinterpret_cast<uint8_t*>(w0);
@@ -239,15 +254,16 @@ extern "C" int eshkol_b200_gemm_f64_static_scratch(const double* dA, const doubl
   if (make_plane_map(&mA1, aodd, L.Kp, M, 15, static_cast<long long>(L.a_stride), kBM)) return -1;
   if (make_plane_map(&mB1, bodd, L.Kp, N, 15, static_cast<long long>(L.b_stride), 256)) return -1;
   SS_CHECK(launch_modgemm(256, kEpiMod256, mA0, mB0, p0, L.tiles_m * L.tiles_n, lib_num_sms(), st));
+  SS_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(N), st));
   SS_CHECK(launch_modgemm(256, kEpiModI8, mA1, mB1, p1, L.tiles_m * L.tiles_n * 15, lib_num_sms(), st));
 
   CrtArgs ca;
-  ca.w0 = w0; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(L.w_stride); ca.ldw = L.Np;
+  ca.w0 = w0; ca.flip = flip_bits; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(L.w_stride); ca.ldw = L.Np;
   ca.n_mod = 16; ca.M = M; ca.N = N;
   ca.inv_scale_a = sai; ca.inv_scale_b = sbi;
   ca.C = dC; ca.ldc = N;
   ca.bias_mode = 0; ca.bias = nullptr; ca.activation = 0; ca.pixels_per_image = 0;
   SS_CHECK(launch_crt(ca, hc, st));
-  count_launches(10);
+  count_launches(11);
   return 0;
 }

@@ -560,7 +560,7 @@ int ozaki1_gemm(const double* dA, const double* dB, double* dC, long long M, lon
   }
   TIER_CHECK(cudaMemcpyAsync(d_jobs, jobs.data(), sizeof(GemmJob) * jobs.size(), cudaMemcpyHostToDevice, st));
 
-  GemmParams prm;
+  GemmParams prm = make_gemm_params();
   prm.tiles_m = tiles_m; prm.tiles_n = tiles_n; prm.n_jobs = nbuf;
   prm.kb_per_seg = static_cast<int>(Kp / kBK);
   prm.kb_per_unit = 1 << 28;
@@ -658,7 +658,7 @@ int ozaki2_fast_gemm(const double* dA, const double* dB, double* dC, long long M
     jobs[l].offset = static_cast<unsigned>((2147483648ull + p - 1) / p * p);
   }
   TIER_CHECK(cudaMemcpyAsync(d_jobs, jobs, sizeof(GemmJob) * n_mod, cudaMemcpyHostToDevice, st));
-  GemmParams prm;
+  GemmParams prm = make_gemm_params();
   prm.tiles_m = tiles_m; prm.tiles_n = tiles_n; prm.n_jobs = n_mod;
   prm.kb_per_seg = static_cast<int>(Kp / kBK);
   prm.kb_per_unit = 1 << 28;

@@ -104,7 +104,7 @@ int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, 
  * streams.  Every intermediate lives in a fixed 24 MiB array inside the library
  * (held by each GPU that loads it, until exit); no allocating routine is called.
  * A, B and C are device pointers owned by the caller.  Shapes whose scratch need
- * exceeds the array (roughly 18*(M+N)*K + 17*M*N bytes after padding; 512x512x512
+ * exceeds the array (roughly 16*(M+N)*K + 17*M*N bytes after padding; 512x512x512
  * and 256x2048x256 fit) are refused with a message and -1.  Calls share the array:
  * they are ordered on the library stream and must not be made to overlap on the GPU.
  * The first call on a device resolves the array's address and should come before
@@ -162,7 +162,9 @@ uint64_t eshkol_b200_workspace_bytes(void);
  * what: 0 mu (int32[M])          1 nu (int32[N])
  *       2 A residues, modulus 256 plane   3 A residues, odd plane `index` (0-based)
  *       4 B residues, modulus 256 plane   5 B residues, odd plane `index`
- *       6 product residues mod 256 (int16)  7 product residues, odd plane `index` (int8)
+ *       6 products mod 256: sum of chunk residues mod 512, ties as +128 (int16); 12 its flip bits
+ *       7 product residues, odd plane `index` (int8)
+ *       8 / 9 A flags (+128, odd)   10 / 11 B flags (+128, odd): uint16 units, 64 per chunk
  * info[0..5] receive rows, row pitch (elements), element size, n_chunks, last
  * segment length, bytes copied.  Synchronises the stream. */
 int eshkol_b200_debug_fetch(int what, int index, void* host_dst, uint64_t capacity_bytes,

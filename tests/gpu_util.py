@@ -27,20 +27,18 @@ def gemm(A, B, tier=eb.TIER_OZAKI2, param=0, simt=False, tile_n=0, activation=0,
     return dC.cpu().numpy()
 
 
-def decode_plane0(p0: np.ndarray, K: int, meta: dict, operand: str):
-    """modulus-256 plane -> (byte residue, +128 flag, odd flag), each rows x K"""
-    CH, SEG, EXT = 1008, 1024, 3072
+def decode_plane0(p0: np.ndarray, K: int):
+    """modulus-256 plane (1024 bytes per 1008-element chunk) -> rows x K residue bytes"""
     k = np.arange(K)
-    c = k // CH
-    off = k % CH
-    seglen = np.where(c == meta["n_chunks"] - 1, meta["last_seg"], SEG)
-    col = c * EXT + off
-    lo = p0[:, col]
-    s1 = p0[:, col + seglen]
-    s2 = p0[:, col + 2 * seglen]
-    if operand == "A":
-        return lo, s1, s2      # A: segment 1 = +128 flags, segment 2 = odd flags
-    return lo, s2, s1          # B: segment 1 = odd flags, segment 2 = +128 flags
+    return p0[:, (k // 1008) * 1024 + (k % 1008)]
+
+
+def decode_flags(units: np.ndarray, K: int):
+    """flag bit-plane (64 16-bit units per chunk, bit b of unit u = element 16u + b) -> rows x K of 0/1"""
+    k = np.arange(K)
+    c, off = k // 1008, k % 1008
+    u = units.view(np.uint16)[:, c * 64 + off // 16]
+    return ((u >> (off % 16).astype(np.uint16)) & 1).astype(np.int32)
 
 
 def same_bits(x: np.ndarray, y: np.ndarray) -> bool:

@@ -23,19 +23,18 @@ def check_stages(A, B, simt):
     nu, _ = api.debug_fetch(1)
     assert np.array_equal(mu[0, :M], d["mu"])
     assert np.array_equal(nu[0, :N], d["nu"])
-    # modulus 256: representative in [-128, 128] with the reference's tie rule
-    a0, meta = api.debug_fetch(2)
-    lo, hi, odd = gu.decode_plane0(a0, K, meta, "A")
+    # modulus 256: representative in [-128, 128] with the reference's tie rule, carried as
+    # the int8 byte plus two flag bit-planes (+128, odd)
+    a0, _ = api.debug_fetch(2)
     ra = d["Ares"][0].astype(np.int32)
-    assert np.array_equal(lo.astype(np.int32), ((ra + 128) % 256) - 128)
-    assert np.array_equal(hi, np.where(ra == 128, 16, 0))
-    assert np.array_equal(odd, (ra & 1) * 16)
-    b0, meta = api.debug_fetch(4)
-    lo, hi, odd = gu.decode_plane0(b0, K, meta, "B")
+    assert np.array_equal(gu.decode_plane0(a0, K).astype(np.int32), ((ra + 128) % 256) - 128)
+    assert np.array_equal(gu.decode_flags(api.debug_fetch(8)[0], K), (ra == 128).astype(np.int32))
+    assert np.array_equal(gu.decode_flags(api.debug_fetch(9)[0], K), ra & 1)
+    b0, _ = api.debug_fetch(4)
     rb = d["Bres"][0].astype(np.int32).T
-    assert np.array_equal(lo.astype(np.int32), ((rb + 128) % 256) - 128)
-    assert np.array_equal(hi, np.where(rb == 128, 16, 0))
-    assert np.array_equal(odd, (rb & 1) * 16)
+    assert np.array_equal(gu.decode_plane0(b0, K).astype(np.int32), ((rb + 128) % 256) - 128)
+    assert np.array_equal(gu.decode_flags(api.debug_fetch(10)[0], K), (rb == 128).astype(np.int32))
+    assert np.array_equal(gu.decode_flags(api.debug_fetch(11)[0], K), rb & 1)
     # odd moduli: an int8 representative of the same class as the reference's value
     # (within half a modulus plus one of zero, so that K products still fit int32)
     for l in (1, 2, 8, 15):
@@ -51,7 +50,11 @@ def check_stages(A, B, simt):
         assert not ((got - d["Bres"][l].astype(np.int32).T) % p).any()
     # residues of the products
     w0, _ = api.debug_fetch(6)
-    assert np.array_equal(w0[:M, :N].astype(np.int32), d["W"][0].astype(np.int32))
+    flip, _ = api.debug_fetch(12)
+    fl = ((flip.view(np.uint32)[:, np.arange(N) // 32] >> (np.arange(N) % 32).astype(np.uint32)) & 1).astype(np.int64)
+    x = (w0[:M, :N].astype(np.int64) + 256 * fl[:M]) % 512
+    got0 = np.where(x == 128, 128, ((x + 128) % 256) - 128)
+    assert np.array_equal(got0, d["W"][0].astype(np.int64))
     for l in range(1, 16):
         wl, _ = api.debug_fetch(7, l - 1)
         assert np.array_equal(wl[:M, :N].astype(np.int32), d["W"][l].astype(np.int32)), l
