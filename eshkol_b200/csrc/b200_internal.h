@@ -61,6 +61,12 @@ cudaError_t modgemm_set_attributes();
 cudaError_t launch_tie_resolve(const GemmParams& prm, uint32_t* flip_bits, int M, int N,
                                cudaStream_t stream);
 
+// Two-SM variant (b200_modgemm2.cu): pairs of CTAs on 256 x 256 tiles; tmB_half is tiled in
+// boxes of 128 rows.  kEpiModI8 and kEpiRawI32 only.
+cudaError_t launch_modgemm_pair(int epi, const CUtensorMap& tmA, const CUtensorMap& tmB_half,
+                                const GemmParams& prm, int tiles_m2, int num_sms, cudaStream_t stream);
+cudaError_t modgemm2_set_attributes();
+
 // Plain CUDA-core version of the same job table, used by tests to localise a
 // fault to the tensor-core kernel; never on the product path.
 struct SimtPlanes {

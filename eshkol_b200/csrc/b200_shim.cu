@@ -35,6 +35,7 @@ struct State {
   PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
   // optional per-stage timing of the Ozaki-II driver (CUDA events on the stream)
   bool timing = false;
+  bool pair_gemm = false;  // odd-moduli products on CTA pairs (tcgen05 cta_group::2)
   cudaEvent_t ev[9] = {};
   bool ev_made = false, ev_valid = false;
   // prepared right-hand operand of the exact tier (its own allocation)
@@ -47,7 +48,7 @@ struct State {
     double* bmax = nullptr; int* nu = nullptr; double* sb = nullptr; double* sbi = nullptr;
     int8_t* b0 = nullptr; int8_t* bodd = nullptr; long long bodd_stride = 0;
     uint16_t* b_hi = nullptr; uint16_t* b_odd = nullptr;  // flag bit-planes of the modulus-256 residues
-    CUtensorMap mB0, mB1;
+    CUtensorMap mB0, mB1, mB1_half;  // mB1_half: boxes of 128 rows, for the two-SM kernel
     Oz2DeviceConsts consts;
   } prep;
   struct PreparedA {
@@ -269,7 +270,7 @@ static Oz2Geom oz2_geometry(long long M, long long K, long long N, int bn) {
   q.K0 = static_cast<long long>(q.n_chunks - 1) * kChunkSeg + q.last_seg;
   q.tiles_m = static_cast<int>((M + kBM - 1) / kBM);
   q.tiles_n = static_cast<int>((N + bn - 1) / bn);
-  q.Mp = static_cast<long long>(q.tiles_m) * kBM;
+  q.Mp = round_up(M, 2 * kBM);  // whole pair tiles, for the two-SM products kernel
   q.Np = static_cast<long long>(q.tiles_n) * bn;
   return q;
 }
@@ -345,6 +346,7 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
   g.launches += 3;
   if (make_plane_map(&P.mB0, P.b0, q.K0, N, 1, static_cast<long long>(N) * q.K0, bn)) return -1;
   if (make_plane_map(&P.mB1, P.bodd, q.Kp, N, n_odd, P.bodd_stride, bn)) return -1;
+  if (make_plane_map(&P.mB1_half, P.bodd, q.Kp, N, n_odd, P.bodd_stride, kBM)) return -1;
   P.valid = true;
   return 0;
 }
@@ -476,7 +478,12 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
     B200_CHECK(launch_modgemm(P.bn, kEpiMod256, A.mA0, P.mB0, p0, tiles, g.num_sms, st));
     B200_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(P.N), st));
     B200_MARK(6);
-    B200_CHECK(launch_modgemm(P.bn, kEpiModI8, A.mA1, P.mB1, p1, tiles * n_odd, g.num_sms, st));
+    if (g.pair_gemm && P.bn == 256) {
+      B200_CHECK(launch_modgemm_pair(kEpiModI8, A.mA1, P.mB1_half, p1, static_cast<int>(A.Mp / (2 * kBM)),
+                                     g.num_sms, st));
+    } else {
+      B200_CHECK(launch_modgemm(P.bn, kEpiModI8, A.mA1, P.mB1, p1, tiles * n_odd, g.num_sms, st));
+    }
   }
   B200_MARK(7);
   CrtArgs ca;
@@ -760,6 +767,11 @@ int eshkol_b200_init(int device) {
   }
   g.encode = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(fn);
   B200_CHECK(modgemm_set_attributes());
+  B200_CHECK(modgemm2_set_attributes());
+  {
+    const char* e = getenv("ESHKOL_B200_PAIR_GEMM");
+    g.pair_gemm = e && e[0] == '1';
+  }
   B200_CHECK(split_set_attributes());
   B200_CHECK(tiers_set_attributes());
   g.ready = true;
@@ -925,6 +937,8 @@ int eshkol_b200_sync_status(void) {
   }
   return h;
 }
+
+void eshkol_b200_set_pair_gemm(int on) { g.pair_gemm = on != 0; }
 
 void eshkol_b200_set_phase_timing(int on) {
   if (!g.ready) return;

@@ -29,6 +29,7 @@ def main() -> None:
     ap.add_argument("--param", type=int, default=0)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--tile-n", type=int, default=0, choices=[0, 128, 256])
+    ap.add_argument("--pair", type=int, default=-1, help="1: two-SM products kernel, 0: one-SM")
     ap.add_argument("--dist", default="normal", choices=["normal", "uniform", "wide"])
     args = ap.parse_args()
     M, K, N = args.m or args.n, args.k or args.n, args.n
@@ -42,6 +43,8 @@ def main() -> None:
     if lib.eshkol_b200_init(0) != 0:
         raise RuntimeError("no usable sm_100 device")
     lib.eshkol_b200_set_phase_timing(1)
+    if args.pair >= 0:
+        lib.eshkol_b200_set_pair_gemm(args.pair)
     opts = api.make_opts(TIERS[args.tier], args.param, tile_n=args.tile_n)
     stream = torch.cuda.ExternalStream(api.stream_handle(), device=dev)
     out = {}

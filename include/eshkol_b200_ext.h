@@ -141,6 +141,11 @@ int eshkol_b200_elementwise_f64_device(const double* a, const double* b, double*
  * kernel ran out, or -1 on a CUDA error. */
 int eshkol_b200_sync_status(void);
 
+/* Selects the products kernel of the exact tier's odd moduli: 0 = one CTA per 128 x 256
+ * tile, 1 = CTA pairs on 256 x 256 tiles (tcgen05 cta_group::2, each SM loads half of the B
+ * tile).  Same results either way.  Initial value: environment ESHKOL_B200_PAIR_GEMM. */
+void eshkol_b200_set_pair_gemm(int on);
+
 /* Per-stage timing of the Ozaki-II driver, the counterpart of the reference's
  * ESHKOL_OZAKI_PROFILE line (lib/backend/gpu/gpu_memory.mm:2479, 2658-2664).  When
  * switched on, CUDA events on the library stream bracket each stage of every

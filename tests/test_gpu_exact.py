@@ -242,3 +242,16 @@ def test_prepared_a_times_column_panels_of_b(gpu_lib):
     rc = gpu_lib.eshkol_b200_multiply_prepared_f64_device(big.data_ptr(), None)
     assert rc in (0, -1)  # 0 only if the workspace already held enough room
     assert api.sync_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(256, 1024, 256), (300, 1100, 520), (1, 130, 1), (513, 4000, 300)])
+def test_two_sm_products_kernel_bit_exact(gpu_lib, shape):
+    M, K, N = shape
+    A = inputs.full53(61, (M, K))
+    B = inputs.full53(62, (K, N))
+    gpu_lib.eshkol_b200_set_pair_gemm(1)
+    try:
+        got = gu.gemm(A, B)
+    finally:
+        gpu_lib.eshkol_b200_set_pair_gemm(0)
+    assert gu.same_bits(got, ol.oz2_exact(A, B, 52))
