@@ -183,15 +183,22 @@ __global__ void __launch_bounds__(256) split_a_kernel(const double* __restrict__
   }
 
   const long long o = row * g.Kp + k4;
-#pragma unroll 5
-  for (int l = 0; l < g.n_odd; ++l) {
+  // plane 0 is modulus 255, the only one whose residue can come out as +128
+  int8_t* dst_odd = g.odd + o;
+  {
+    const double p_inv = c.p_inv[1];
+    *reinterpret_cast<uint32_t*>(dst_odd) =
+        pack_bytes4(residue_odd_t<true>(x[0], xlo[0], p_inv, 255), residue_odd_t<true>(x[1], xlo[1], p_inv, 255),
+                    residue_odd_t<true>(x[2], xlo[2], p_inv, 255), residue_odd_t<true>(x[3], xlo[3], p_inv, 255));
+  }
+#pragma unroll 7
+  for (int l = 1; l < g.n_odd; ++l) {
     const double p_inv = c.p_inv[l + 1];
     const int pi = c.p_i[l + 1];
-    uint32_t word = 0;
-#pragma unroll
-    for (int e = 0; e < 4; ++e)
-      word |= (static_cast<uint32_t>(residue_odd(x[e], xlo[e], p_inv, pi)) & 0xffu) << (8 * e);
-    *reinterpret_cast<uint32_t*>(g.odd + l * g.odd_stride + o) = word;
+    dst_odd += g.odd_stride;
+    *reinterpret_cast<uint32_t*>(dst_odd) =
+        pack_bytes4(residue_odd_t<false>(x[0], xlo[0], p_inv, pi), residue_odd_t<false>(x[1], xlo[1], p_inv, pi),
+                    residue_odd_t<false>(x[2], xlo[2], p_inv, pi), residue_odd_t<false>(x[3], xlo[3], p_inv, pi));
   }
   // modulus 256: the byte, and the two flag bits of each element gathered into 16-bit
   // units along k (4 lanes x 4 elements; chunk boundaries are multiples of 16)
@@ -265,15 +272,19 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
     }
     sm[(0 * kSplitBJ + tx) * kSplitBPitch + qd] = w0;
     sm[(1 * kSplitBJ + tx) * kSplitBPitch + qd] = nib;
-#pragma unroll 5
-    for (int l = 0; l < g.n_odd; ++l) {
+    {
+      const double p_inv = c.p_inv[1];  // modulus 255: the only residue that can come out as +128
+      sm[(2 * kSplitBJ + tx) * kSplitBPitch + qd] =
+          pack_bytes4(residue_odd_t<true>(x[0], xlo[0], p_inv, 255), residue_odd_t<true>(x[1], xlo[1], p_inv, 255),
+                      residue_odd_t<true>(x[2], xlo[2], p_inv, 255), residue_odd_t<true>(x[3], xlo[3], p_inv, 255));
+    }
+#pragma unroll 7
+    for (int l = 1; l < g.n_odd; ++l) {
       const double p_inv = c.p_inv[l + 1];
       const int pi = c.p_i[l + 1];
-      uint32_t word = 0;
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        word |= (static_cast<uint32_t>(residue_odd(x[e], xlo[e], p_inv, pi)) & 0xffu) << (8 * e);
-      sm[((2 + l) * kSplitBJ + tx) * kSplitBPitch + qd] = word;
+      sm[((2 + l) * kSplitBJ + tx) * kSplitBPitch + qd] =
+          pack_bytes4(residue_odd_t<false>(x[0], xlo[0], p_inv, pi), residue_odd_t<false>(x[1], xlo[1], p_inv, pi),
+                      residue_odd_t<false>(x[2], xlo[2], p_inv, pi), residue_odd_t<false>(x[3], xlo[3], p_inv, pi));
     }
   }
   __syncthreads();

@@ -16,11 +16,22 @@ constexpr double kRoundMagic = 6755399441055744.0;  // 1.5 * 2^52
 // and r = x - p*q is formed modulo 2^32 in one integer multiply-add.  |r| <= 0.5052*p,
 // i.e. within +-127 for p <= 253 and within +-128 for p = 255, where +128 is folded
 // to -127.
-__device__ __forceinline__ int residue_odd(double x, uint32_t xlo, double p_inv, int pi) {
+template <bool kMay128>
+__device__ __forceinline__ int residue_odd_t(double x, uint32_t xlo, double p_inv, int pi) {
   const uint32_t qlo = static_cast<uint32_t>(__double2loint(fma(x, p_inv, kRoundMagic)));
   int ri = static_cast<int>(xlo - static_cast<uint32_t>(pi) * qlo);
-  if (pi == 255) ri = (ri == 128) ? -127 : ri;
+  if (kMay128) ri = (ri == 128) ? 128 - pi : ri;  // only p = 255 can reach +128
   return ri;
+}
+__device__ __forceinline__ int residue_odd(double x, uint32_t xlo, double p_inv, int pi) {
+  return (pi == 255) ? residue_odd_t<true>(x, xlo, p_inv, pi) : residue_odd_t<false>(x, xlo, p_inv, pi);
+}
+
+// low bytes of four values -> one word (three byte-permutes instead of shifts and masks)
+__device__ __forceinline__ uint32_t pack_bytes4(int r0, int r1, int r2, int r3) {
+  const uint32_t lo = __byte_perm(static_cast<uint32_t>(r0), static_cast<uint32_t>(r1), 0x0040);
+  const uint32_t hi = __byte_perm(static_cast<uint32_t>(r2), static_cast<uint32_t>(r3), 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
 }
 
 struct Res256 {
