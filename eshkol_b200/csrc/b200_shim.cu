@@ -37,6 +37,7 @@ struct State {
   bool timing = false;
   bool pair_gemm = false;  // odd-moduli products on CTA pairs (tcgen05 cta_group::2)
   cudaEvent_t ev[9] = {};
+  cudaEvent_t ev_scratch = nullptr;
   bool ev_made = false, ev_valid = false;
   // prepared right-hand operand of the exact tier (its own allocation)
   uint8_t* bside = nullptr;
@@ -62,6 +63,19 @@ struct State {
     uint16_t* a_hi = nullptr; uint16_t* a_odd = nullptr;
     CUtensorMap mA0, mA1;
   } prepA;
+  GemmJob* d_jobs16 = nullptr;  // job table of the 16 modular products, uploaded once
+  // row-band pipeline of the one-shot device product: band r+1 is split while band r is
+  // multiplied and band r-1 reconstructed, on three streams over two workspace slots
+  long long band_rows = 0;  // off unless asked for: measured, the overlap slows the power-capped products as much as it hides
+  bool lanes_made = false;
+  cudaStream_t s_prep = nullptr, s_post = nullptr;
+  cudaEvent_t eb_start = nullptr, eb_done = nullptr;
+  cudaEvent_t eb_a_ready[2] = {}, eb_g0[2] = {}, eb_g1[2] = {}, eb_w_free[2] = {};
+  PreparedA bandA[2];
+  static constexpr int kMaxBands = 16, kBandEvents = 10;
+  cudaEvent_t ev_band[kMaxBands * kBandEvents] = {};
+  bool ev_band_made = false;
+  int bands_timed = 0;  // > 0: the last timed product ran as this many bands
   // host pipeline: upload / download streams and their hand-off events
   bool pipe_made = false;
   cudaStream_t s_in = nullptr, s_out = nullptr;
@@ -351,6 +365,67 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
   return 0;
 }
 
+// Where the pieces of one prepared block of rows of A sit behind a base address, and how
+// much room the product residues of a result n_cols wide need behind them.
+struct ALayout {
+  size_t amax, mu, sa, sai, a0, ahi, aoddf, aodd, end, total;
+};
+
+static ALayout oz2_a_layout(const Oz2Geom& q) {
+  const int n_odd = 15;
+  ALayout L;
+  Carver cv;
+  L.amax = cv.take(q.M * 8); L.mu = cv.take(q.M * 4); L.sa = cv.take(q.M * 8); L.sai = cv.take(q.M * 8);
+  L.a0 = cv.take(static_cast<size_t>(q.M) * q.K0);
+  const size_t flag_bytes = static_cast<size_t>(q.M) * q.n_chunks * kChunkUnits * sizeof(uint16_t);
+  L.ahi = cv.take(flag_bytes); L.aoddf = cv.take(flag_bytes);
+  L.aodd = cv.take(static_cast<size_t>(q.M) * q.Kp * n_odd);
+  L.end = cv.off;
+  const size_t w_stride = static_cast<size_t>(q.Mp) * q.Np;
+  cv.take(w_stride * 2);
+  cv.take(w_stride * n_odd);
+  cv.take(w_stride / 32 * 8 * q.n_chunks);  // tie / bit-8 masks per chunk
+  cv.take(w_stride / 32 * 4);               // flip bits
+  L.total = cv.off;
+  return L;
+}
+
+// scan, scale and split one block of rows on stream st into the planes behind ws.
+// tev (optional): three events recorded before the scan, after the scales, after the split.
+static int oz2_prepare_a_at(State::PreparedA& A, uint8_t* ws, const Oz2Geom& q, const double* dA,
+                            cudaStream_t st, cudaEvent_t* tev) {
+  const int n_odd = 15;
+  const ALayout L = oz2_a_layout(q);
+  const long long M = q.M;
+  A.valid = false;
+  A.M = M; A.K = q.K; A.Kp = q.Kp; A.K0 = q.K0; A.Mp = q.Mp; A.tiles_m = q.tiles_m;
+  A.n_chunks = q.n_chunks; A.last_seg = q.last_seg; A.end = L.end;
+  A.amax = reinterpret_cast<double*>(ws + L.amax);
+  A.mu = reinterpret_cast<int*>(ws + L.mu);
+  A.sa = reinterpret_cast<double*>(ws + L.sa);
+  A.sai = reinterpret_cast<double*>(ws + L.sai);
+  A.jobs = g.d_jobs16;
+  A.a0 = reinterpret_cast<int8_t*>(ws + L.a0);
+  A.a_hi = reinterpret_cast<uint16_t*>(ws + L.ahi);
+  A.a_odd = reinterpret_cast<uint16_t*>(ws + L.aoddf);
+  A.aodd = reinterpret_cast<int8_t*>(ws + L.aodd);
+  A.a_stride = static_cast<long long>(M) * q.Kp;
+  Oz2DeviceConsts hc;
+  oz2_host_consts(16, &hc, nullptr);
+  if (tev) B200_CHECK(cudaEventRecord(tev[0], st));
+  B200_CHECK(launch_scan_rows(dA, M, q.K, A.amax, st));
+  B200_CHECK(launch_scales(A.amax, M, 52, A.mu, A.sa, A.sai, st));
+  if (tev) B200_CHECK(cudaEventRecord(tev[1], st));
+  SplitPlanes pa{M, q.K, q.Kp, q.K0, q.n_chunks, n_odd, A.a0, A.a_hi, A.a_odd, A.aodd, A.a_stride};
+  B200_CHECK(launch_split_a(dA, A.sa, pa, hc, st));
+  if (tev) B200_CHECK(cudaEventRecord(tev[2], st));
+  g.launches += 3;
+  if (make_plane_map(&A.mA0, A.a0, q.K0, M, 1, static_cast<long long>(M) * q.K0, kBM)) return -1;
+  if (make_plane_map(&A.mA1, A.aodd, q.Kp, M, n_odd, A.a_stride, kBM)) return -1;
+  A.valid = true;
+  return 0;
+}
+
 // Left-hand operand prepared once: mu_i, 2^+-mu_i and the residue planes of a block
 // of rows of A, kept at the front of the workspace; room for the product residues of
 // a result up to n_cols_hint columns wide is reserved behind them so that the
@@ -358,64 +433,27 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
 static int oz2_prepare_a(const double* dA, long long M, long long K, long long n_cols_hint, int bn) {
   if (oz2_check_shape(M, K, n_cols_hint, 16)) return -1;
   const Oz2Geom q = oz2_geometry(M, K, n_cols_hint, bn);
-  const int n_odd = 15;
-  Carver cv;
-  const size_t o_amax = cv.take(M * 8), o_mu = cv.take(M * 4), o_sa = cv.take(M * 8), o_sai = cv.take(M * 8);
-  const size_t o_jobs = cv.take(sizeof(GemmJob) * 16);
-  const size_t o_a0 = cv.take(static_cast<size_t>(M) * q.K0);
-  const size_t flag_bytes = static_cast<size_t>(M) * q.n_chunks * kChunkUnits * sizeof(uint16_t);
-  const size_t o_ahi = cv.take(flag_bytes), o_aodd_f = cv.take(flag_bytes);
-  const size_t a_stride = static_cast<size_t>(M) * q.Kp;
-  const size_t o_aodd = cv.take(a_stride * n_odd);
-  const size_t a_end = cv.off;
-  const size_t w_stride = static_cast<size_t>(q.Mp) * q.Np;
-  cv.take(w_stride * 2);
-  cv.take(w_stride * n_odd);
-  cv.take(w_stride / 32 * 8 * q.n_chunks);  // tie / bit-8 masks per chunk
-  cv.take(w_stride / 32 * 4);               // flip bits
   g.prepA.valid = false;
-  if (ensure_workspace(cv.off) != 0) return -1;
-  uint8_t* ws = g.ws;
-  State::PreparedA& A = g.prepA;
-  A.M = M; A.K = K; A.Kp = q.Kp; A.K0 = q.K0; A.Mp = q.Mp; A.tiles_m = q.tiles_m;
-  A.n_chunks = q.n_chunks; A.last_seg = q.last_seg; A.end = a_end;
-  A.amax = reinterpret_cast<double*>(ws + o_amax);
-  A.mu = reinterpret_cast<int*>(ws + o_mu);
-  A.sa = reinterpret_cast<double*>(ws + o_sa);
-  A.sai = reinterpret_cast<double*>(ws + o_sai);
-  A.jobs = reinterpret_cast<GemmJob*>(ws + o_jobs);
-  A.a0 = reinterpret_cast<int8_t*>(ws + o_a0);
-  A.a_hi = reinterpret_cast<uint16_t*>(ws + o_ahi);
-  A.a_odd = reinterpret_cast<uint16_t*>(ws + o_aodd_f);
-  A.aodd = reinterpret_cast<int8_t*>(ws + o_aodd);
-  A.a_stride = static_cast<long long>(a_stride);
-  Oz2DeviceConsts hc;
-  oz2_host_consts(16, &hc, nullptr);
-  cudaStream_t st = g.stream;
+  if (ensure_workspace(oz2_a_layout(q).total) != 0) return -1;
   const bool timed = g.timing && g.ev_made;
-  B200_MARK(3);
-  B200_CHECK(launch_scan_rows(dA, M, K, A.amax, st));
-  B200_CHECK(launch_scales(A.amax, M, 52, A.mu, A.sa, A.sai, st));
-  B200_MARK(4);
-  SplitPlanes pa{M, K, q.Kp, q.K0, q.n_chunks, n_odd, A.a0, A.a_hi, A.a_odd, A.aodd, A.a_stride};
-  B200_CHECK(launch_split_a(dA, A.sa, pa, hc, st));
-  B200_MARK(5);
-  g.launches += 3;
-  GemmJob jobs[16];
-  fill_mod_job(&jobs[0], 0, 0, 0, 0);
-  for (int l = 1; l < 16; ++l) fill_mod_job(&jobs[l], l - 1, l - 1, l - 1, kModuli[l]);
-  B200_CHECK(cudaMemcpyAsync(A.jobs, jobs, sizeof(GemmJob) * 16, cudaMemcpyHostToDevice, st));
-  if (make_plane_map(&A.mA0, A.a0, q.K0, M, 1, static_cast<long long>(M) * q.K0, kBM)) return -1;
-  if (make_plane_map(&A.mA1, A.aodd, q.Kp, M, n_odd, A.a_stride, kBM)) return -1;
-  A.valid = true;
-  return 0;
+  g.bands_timed = 0;
+  return oz2_prepare_a_at(g.prepA, g.ws, q, dA, g.stream, timed ? &g.ev[3] : nullptr);
 }
 
+// Streams of one multiplication.  Serial: all three are the library stream.  In the band
+// pipeline the tie resolution and the reconstruction run on `post`, ordered behind the
+// products by the two events, so that they overlap the next band's products.
+struct MulLanes {
+  cudaStream_t gemm, post;
+  cudaEvent_t g0_done, g1_done;  // used only when post != gemm
+  cudaEvent_t* tev;              // optional: gemm-stream events [0..2], post-stream events [3..6]
+};
+
 // C = (prepared A) * (prepared B): the 16 modular products on the tensor cores and
-// the reconstruction.
-static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
+// the reconstruction.  ws / cap: the block A was prepared in.
+static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, double* dC,
+                           const EshkolB200GemmOpts& o, const MulLanes& ln) {
   const State::Prepared& P = g.prep;
-  const State::PreparedA& A = g.prepA;
   if (!P.valid || !A.valid) {
     fprintf(stderr, "[eshkol-b200] multiply needs both operands prepared\n");
     return -1;
@@ -432,17 +470,17 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   const size_t w_stride = static_cast<size_t>(A.Mp) * P.Np;
   const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
   const size_t o_tie = cv.take(w_stride / 32 * 8 * A.n_chunks), o_flip = cv.take(w_stride / 32 * 4);
-  if (cv.off > g.ws_bytes) {
+  if (cv.off > cap) {
     fprintf(stderr, "[eshkol-b200] result of %lld columns exceeds the room reserved when A was prepared\n", P.N);
     return -1;
   }
-  uint8_t* ws = g.ws;
   int16_t* w0 = reinterpret_cast<int16_t*>(ws + o_w0);
   int8_t* wodd = reinterpret_cast<int8_t*>(ws + o_wodd);
   uint32_t* tie_bits = reinterpret_cast<uint32_t*>(ws + o_tie);
   uint32_t* flip_bits = reinterpret_cast<uint32_t*>(ws + o_flip);
-  cudaStream_t st = g.stream;
-  const bool timed = g.timing && g.ev_made;
+  cudaStream_t st = ln.gemm, sp = ln.post;
+  const bool lanes = sp != st;
+  cudaEvent_t* tev = ln.tev;
 
   GemmParams p0 = make_gemm_params();
   p0.tie_bits = tie_bits;
@@ -466,18 +504,25 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   p1.out = reinterpret_cast<uint8_t*>(wodd);
   p1.out_plane_stride = static_cast<long long>(w_stride);
   const int tiles = A.tiles_m * P.tiles_n;
+  if (tev) B200_CHECK(cudaEventRecord(tev[0], st));
   if (o.use_simt_products) {
     SimtPlanes s0{A.a0, 0, static_cast<int>(A.K0), P.b0, 0, static_cast<int>(A.K0), static_cast<int>(M), static_cast<int>(P.N)};
     SimtPlanes s1{A.aodd, A.a_stride, static_cast<int>(A.Kp), P.bodd, P.bodd_stride,
                   static_cast<int>(A.Kp), static_cast<int>(M), static_cast<int>(P.N)};
     B200_CHECK(launch_modgemm_simt(kEpiMod256, s0, p0, st));
-    B200_CHECK(cudaMemsetAsync(flip_bits, 0, w_stride / 32 * 4, st));
-    B200_MARK(6);
+    if (lanes) { B200_CHECK(cudaEventRecord(ln.g0_done, st)); B200_CHECK(cudaStreamWaitEvent(sp, ln.g0_done, 0)); }
+    if (tev) B200_CHECK(cudaEventRecord(tev[3], sp));
+    B200_CHECK(cudaMemsetAsync(flip_bits, 0, w_stride / 32 * 4, sp));
+    if (tev) B200_CHECK(cudaEventRecord(tev[4], sp));
+    if (tev) B200_CHECK(cudaEventRecord(tev[1], st));
     B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
   } else {
     B200_CHECK(launch_modgemm(P.bn, kEpiMod256, A.mA0, P.mB0, p0, tiles, g.num_sms, st));
-    B200_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(P.N), st));
-    B200_MARK(6);
+    if (lanes) { B200_CHECK(cudaEventRecord(ln.g0_done, st)); B200_CHECK(cudaStreamWaitEvent(sp, ln.g0_done, 0)); }
+    if (tev) B200_CHECK(cudaEventRecord(tev[3], sp));
+    B200_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(P.N), sp));
+    if (tev) B200_CHECK(cudaEventRecord(tev[4], sp));
+    if (tev) B200_CHECK(cudaEventRecord(tev[1], st));
     if (g.pair_gemm && P.bn == 256) {
       B200_CHECK(launch_modgemm_pair(kEpiModI8, A.mA1, P.mB1_half, p1, static_cast<int>(A.Mp / (2 * kBM)),
                                      g.num_sms, st));
@@ -485,7 +530,8 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
       B200_CHECK(launch_modgemm(P.bn, kEpiModI8, A.mA1, P.mB1, p1, tiles * n_odd, g.num_sms, st));
     }
   }
-  B200_MARK(7);
+  if (tev) B200_CHECK(cudaEventRecord(tev[2], st));
+  if (lanes) { B200_CHECK(cudaEventRecord(ln.g1_done, st)); B200_CHECK(cudaStreamWaitEvent(sp, ln.g1_done, 0)); }
   CrtArgs ca;
   ca.w0 = w0; ca.flip = flip_bits; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = P.Np;
   ca.n_mod = 16; ca.M = M; ca.N = P.N;
@@ -494,10 +540,10 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   ca.bias_mode = o.bias ? o.bias_mode : 0; ca.bias = o.bias;
   ca.activation = o.activation;
   ca.pixels_per_image = o.pixels_per_image;
-  B200_CHECK(launch_crt(ca, P.consts, st));
-  B200_MARK(8);
+  if (tev) B200_CHECK(cudaEventRecord(tev[5], sp));
+  B200_CHECK(launch_crt(ca, P.consts, sp));
+  if (tev) B200_CHECK(cudaEventRecord(tev[6], sp));
   g.launches += 4;
-  g.ev_valid = timed;
 
   State::Last& L = g.last;
   L.valid = true; L.M = M; L.K = P.K; L.N = P.N; L.Kp = A.Kp; L.K0 = A.K0; L.Mp = A.Mp; L.Np = P.Np;
@@ -509,13 +555,110 @@ static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   return 0;
 }
 
+// Serial multiplication on the library stream.  Stage events: [6] behind the modulus-256
+// product and its tie resolution, [7] behind the odd products, [8] behind the reconstruction;
+// the lane marks that have no serial meaning land on a scratch event.
+static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
+  const bool timed = g.timing && g.ev_made;
+  cudaEvent_t tev[7] = {g.ev_scratch, g.ev[6], g.ev[7], g.ev_scratch, g.ev[6], g.ev_scratch, g.ev[8]};
+  MulLanes ln{g.stream, g.stream, nullptr, nullptr, timed ? tev : nullptr};
+  const int rc = oz2_multiply_at(g.prepA, g.ws, g.ws_bytes, dC, o, ln);
+  g.ev_valid = timed && rc == 0;
+  return rc;
+}
+
+static int make_band_lanes() {
+  if (g.lanes_made) return 0;
+  int least = 0, greatest = 0;
+  B200_CHECK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+  // the products run on the library stream (highest priority); the splits and the
+  // reconstruction fill the issue slots the tensor-core kernel leaves idle
+  B200_CHECK(cudaStreamCreateWithPriority(&g.s_prep, cudaStreamNonBlocking, least));
+  B200_CHECK(cudaStreamCreateWithPriority(&g.s_post, cudaStreamNonBlocking, least));
+  B200_CHECK(cudaEventCreateWithFlags(&g.eb_start, cudaEventDisableTiming));
+  B200_CHECK(cudaEventCreateWithFlags(&g.eb_done, cudaEventDisableTiming));
+  for (int i = 0; i < 2; ++i) {
+    B200_CHECK(cudaEventCreateWithFlags(&g.eb_a_ready[i], cudaEventDisableTiming));
+    B200_CHECK(cudaEventCreateWithFlags(&g.eb_g0[i], cudaEventDisableTiming));
+    B200_CHECK(cudaEventCreateWithFlags(&g.eb_g1[i], cudaEventDisableTiming));
+    B200_CHECK(cudaEventCreateWithFlags(&g.eb_w_free[i], cudaEventDisableTiming));
+  }
+  g.lanes_made = true;
+  return 0;
+}
+
+// C = A * (prepared B) over bands of rows, three streams, two workspace slots:
+//   prep:  scan / scale / split of band r+1
+//   gemm:  the 16 modular products of band r          (the library stream)
+//   post:  tie resolution and reconstruction of band r (and r-1)
+// Every row's result depends on that row of A and on B only, so the bits are those of the
+// serial product.  The library stream is ordered behind the last band when this returns.
+static int oz2_gemm_banded(const double* dA, double* dC, long long M, long long bm,
+                           const EshkolB200GemmOpts& o) {
+  const State::Prepared& P = g.prep;
+  const long long nb = (M + bm - 1) / bm;
+  const Oz2Geom qb = oz2_geometry(bm, P.K, P.N, P.bn);
+  const size_t slot = (oz2_a_layout(qb).total + 1023) & ~static_cast<size_t>(1023);
+  g.prepA.valid = false;
+  if (ensure_workspace(2 * slot) != 0) return -1;
+  if (make_band_lanes() != 0) return -1;
+  const bool timed = g.timing && g.ev_band_made && nb <= State::kMaxBands;
+  const long long ldc = (o.ldc > 0) ? o.ldc : P.N;
+  cudaStream_t st = g.stream;
+  B200_CHECK(cudaEventRecord(g.eb_start, st));
+  B200_CHECK(cudaStreamWaitEvent(g.s_prep, g.eb_start, 0));
+  B200_CHECK(cudaStreamWaitEvent(g.s_post, g.eb_start, 0));
+  int rc = 0;
+  for (long long r = 0; r < nb; ++r) {
+    const int s = static_cast<int>(r & 1);
+    const long long r0 = r * bm, rows = (r0 + bm <= M) ? bm : M - r0;
+    uint8_t* ws = g.ws + s * slot;
+    cudaEvent_t* tev = timed ? &g.ev_band[r * State::kBandEvents] : nullptr;
+    const Oz2Geom q = oz2_geometry(rows, P.K, P.N, P.bn);
+    // the slot's A planes are free once band r-2 is through its odd products (residue planes)
+    // and its tie resolution (flag planes); the reconstruction event covers the latter
+    if (r >= 2) {
+      B200_CHECK(cudaStreamWaitEvent(g.s_prep, g.eb_g1[s], 0));
+      B200_CHECK(cudaStreamWaitEvent(g.s_prep, g.eb_w_free[s], 0));
+    }
+    rc = oz2_prepare_a_at(g.bandA[s], ws, q, dA + r0 * P.K, g.s_prep, tev);
+    if (rc) break;
+    B200_CHECK(cudaEventRecord(g.eb_a_ready[s], g.s_prep));
+    B200_CHECK(cudaStreamWaitEvent(st, g.eb_a_ready[s], 0));
+    // ... and its product residues once band r-2 is reconstructed
+    if (r >= 2) B200_CHECK(cudaStreamWaitEvent(st, g.eb_w_free[s], 0));
+    EshkolB200GemmOpts ob = o;
+    if (ob.bias && ob.bias_mode == 1) ob.bias = o.bias + r0;
+    MulLanes ln{st, g.s_post, g.eb_g0[s], g.eb_g1[s], tev ? tev + 3 : nullptr};
+    rc = oz2_multiply_at(g.bandA[s], ws, slot, dC + r0 * ldc, ob, ln);
+    if (rc) break;
+    B200_CHECK(cudaEventRecord(g.eb_w_free[s], g.s_post));
+  }
+  // join: later work on the library stream sees the whole result
+  B200_CHECK(cudaEventRecord(g.eb_done, g.s_post));
+  B200_CHECK(cudaStreamWaitEvent(st, g.eb_done, 0));
+  B200_CHECK(cudaEventRecord(g.eb_done, g.s_prep));
+  B200_CHECK(cudaStreamWaitEvent(st, g.eb_done, 0));
+  g.bandA[0].valid = g.bandA[1].valid = false;
+  if (rc == 0 && timed) { g.bands_timed = static_cast<int>(nb); g.ev_valid = g.timing && g.ev_made; }
+  return rc;
+}
+
 // C[rows] = A[rows] * (prepared B) for one block of rows.  Bit-identical to the same
-// rows of a one-shot product.
-static int oz2_gemm_rows(const double* dA, double* dC, long long M, const EshkolB200GemmOpts& o) {
+// rows of a one-shot product.  allow_bands: large blocks go through the band pipeline.
+static int oz2_gemm_rows(const double* dA, double* dC, long long M, const EshkolB200GemmOpts& o,
+                         bool allow_bands) {
   const State::Prepared& P = g.prep;
   if (!P.valid) {
     fprintf(stderr, "[eshkol-b200] no prepared right-hand operand\n");
     return -1;
+  }
+  const long long bm = g.band_rows;
+  if (allow_bands && bm >= 256 && M >= 2 * bm && o.pixels_per_image == 0 && !o.use_simt_products) {
+    // bands of whole pair tiles; at most kMaxBands of them
+    long long rows = bm;
+    while ((M + rows - 1) / rows > State::kMaxBands) rows *= 2;
+    return oz2_gemm_banded(dA, dC, M, rows, o);
   }
   if (oz2_prepare_a(dA, M, P.K, P.N, P.bn)) return -1;
   const int rc = oz2_multiply(dC, o);
@@ -527,6 +670,7 @@ static int oz2_gemm_rows(const double* dA, double* dC, long long M, const Eshkol
 // operands (gpu_memory.mm:2510-2512), so the operands are scanned together.
 static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, long long M,
                                long long K, long long N, int n_mod, const EshkolB200GemmOpts& o) {
+  g.bands_timed = 0;
   if (oz2_check_shape(M, K, N, n_mod)) return -1;
   const int bn = (o.gemm_tile_n == 128) ? 128 : 256;
   const Oz2Geom q = oz2_geometry(M, K, N, bn);
@@ -661,7 +805,7 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
   if (n_mod != 16) return ozaki2_gemm_general(dA, dB, dC, M, K, N, n_mod, o);
   if (oz2_check_shape(M, K, N, 16)) return -1;
   if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256)) return -1;
-  const int rc = oz2_gemm_rows(dA, dC, M, o);
+  const int rc = oz2_gemm_rows(dA, dC, M, o, true);
   g.prep.valid = false;  // dB belongs to the caller and may change before the next call
   return rc;
 }
@@ -718,7 +862,7 @@ static int oz2_matmul_host(const double* hA, const double* hB, double* hC, long 
     B200_CHECK(cudaEventRecord(g.e_a_ready[s], g.s_in));
     B200_CHECK(cudaStreamWaitEvent(st, g.e_a_ready[s], 0));
     if (i >= 2) B200_CHECK(cudaStreamWaitEvent(st, g.e_c_free[s], 0));
-    rc = oz2_gemm_rows(dA[s], dC[s], rows, o);
+    rc = oz2_gemm_rows(dA[s], dC[s], rows, o, false);
     if (rc) break;
     B200_CHECK(cudaEventRecord(g.e_a_free[s], st));
     B200_CHECK(cudaEventRecord(g.e_c_ready[s], st));
@@ -754,10 +898,21 @@ int eshkol_b200_init(int device) {
   }
   g.device = device;
   g.num_sms = prop.multiProcessorCount;
-  B200_CHECK(cudaStreamCreateWithFlags(&g.stream, cudaStreamNonBlocking));
+  {
+    int least = 0, greatest = 0;
+    B200_CHECK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
+    B200_CHECK(cudaStreamCreateWithPriority(&g.stream, cudaStreamNonBlocking, greatest));
+  }
   // [0] kernel status word, [1] work counter of the persistent products kernel
   B200_CHECK(cudaMalloc(&g.d_status, 2 * sizeof(int)));
   B200_CHECK(cudaMemset(g.d_status, 0, 2 * sizeof(int)));
+  {
+    GemmJob jobs[16];
+    fill_mod_job(&jobs[0], 0, 0, 0, 0);
+    for (int l = 1; l < 16; ++l) fill_mod_job(&jobs[l], l - 1, l - 1, l - 1, kModuli[l]);
+    B200_CHECK(cudaMalloc(&g.d_jobs16, sizeof(jobs)));
+    B200_CHECK(cudaMemcpy(g.d_jobs16, jobs, sizeof(jobs), cudaMemcpyHostToDevice));
+  }
   void* fn = nullptr;
   cudaDriverEntryPointQueryResult qres;
   B200_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
@@ -771,6 +926,8 @@ int eshkol_b200_init(int device) {
   {
     const char* e = getenv("ESHKOL_B200_PAIR_GEMM");
     g.pair_gemm = e && e[0] == '1';
+    e = getenv("ESHKOL_B200_BAND_ROWS");
+    if (e && e[0]) eshkol_b200_set_row_bands(atoll(e));
   }
   B200_CHECK(split_set_attributes());
   B200_CHECK(tiers_set_attributes());
@@ -785,7 +942,21 @@ void eshkol_b200_shutdown(void) {
   if (g.ws) cudaFree(g.ws);
   if (g.aux) cudaFree(g.aux);
   if (g.d_status) cudaFree(g.d_status);
-  if (g.ev_made) for (int i = 0; i < 9; ++i) cudaEventDestroy(g.ev[i]);
+  if (g.ev_made) {
+    for (int i = 0; i < 9; ++i) cudaEventDestroy(g.ev[i]);
+    cudaEventDestroy(g.ev_scratch);
+  }
+  if (g.ev_band_made) for (cudaEvent_t e : g.ev_band) cudaEventDestroy(e);
+  if (g.d_jobs16) cudaFree(g.d_jobs16);
+  if (g.lanes_made) {
+    cudaStreamSynchronize(g.s_prep); cudaStreamSynchronize(g.s_post);
+    cudaStreamDestroy(g.s_prep); cudaStreamDestroy(g.s_post);
+    cudaEventDestroy(g.eb_start); cudaEventDestroy(g.eb_done);
+    for (int i = 0; i < 2; ++i) {
+      cudaEventDestroy(g.eb_a_ready[i]); cudaEventDestroy(g.eb_g0[i]);
+      cudaEventDestroy(g.eb_g1[i]); cudaEventDestroy(g.eb_w_free[i]);
+    }
+  }
   if (g.bside) cudaFree(g.bside);
   if (g.pipe_made) {
     cudaStreamDestroy(g.s_in); cudaStreamDestroy(g.s_out); cudaEventDestroy(g.e_b_ready);
@@ -866,7 +1037,7 @@ int eshkol_b200_gemm_prepared_f64_device(const double* dA, double* dC, uint64_t 
   EshkolB200GemmOpts o;
   memset(&o, 0, sizeof(o));
   if (opts) o = *opts;
-  return oz2_gemm_rows(dA, dC, static_cast<long long>(M), o);
+  return oz2_gemm_rows(dA, dC, static_cast<long long>(M), o, true);
 }
 
 int eshkol_b200_conv2d_f64_device(const double* d_in, int64_t batch, int64_t in_c, int64_t H,
@@ -940,12 +1111,23 @@ int eshkol_b200_sync_status(void) {
 
 void eshkol_b200_set_pair_gemm(int on) { g.pair_gemm = on != 0; }
 
+void eshkol_b200_set_row_bands(long long rows) {
+  // whole pair tiles (256 rows); 0 switches the band pipeline off
+  g.band_rows = rows <= 0 ? 0 : (rows + 255) / 256 * 256;
+}
+
 void eshkol_b200_set_phase_timing(int on) {
   if (!g.ready) return;
   if (on && !g.ev_made) {
     for (int i = 0; i < 9; ++i)
       if (cudaEventCreate(&g.ev[i]) != cudaSuccess) { cudaGetLastError(); return; }
+    if (cudaEventCreate(&g.ev_scratch) != cudaSuccess) { cudaGetLastError(); return; }
     g.ev_made = true;
+  }
+  if (on && !g.ev_band_made) {
+    for (cudaEvent_t& e : g.ev_band)
+      if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return; }
+    g.ev_band_made = true;
   }
   g.timing = on != 0;
   g.ev_valid = false;
@@ -956,8 +1138,26 @@ int eshkol_b200_get_phase_times(float* ms, int capacity) {
   if (cudaStreamSynchronize(g.stream) != cudaSuccess) { cudaGetLastError(); return -1; }
   // events 0-2 bracket the B side (scan + scales, split), events 3-8 the A side
   static const int from[7] = {0, 1, 3, 4, 5, 6, 7};
-  for (int i = 0; i < 7; ++i)
+  const int serial = g.bands_timed > 0 ? 2 : 7;
+  for (int i = 0; i < serial; ++i)
     if (cudaEventElapsedTime(&ms[i], g.ev[from[i]], g.ev[from[i] + 1]) != cudaSuccess) { cudaGetLastError(); return -1; }
+  if (g.bands_timed > 0) {
+    // band pipeline: each stage is the sum over the bands of its own kernels' time on its own
+    // stream; the stages overlap, so they add up to more than the product took
+    for (int i = 2; i < 7; ++i) ms[i] = 0.f;
+    static const int lo[6] = {0, 1, 3, 6, 4, 8}, hi[6] = {1, 2, 4, 7, 5, 9}, into[6] = {2, 3, 4, 4, 5, 6};
+    for (int r = 0; r < g.bands_timed; ++r) {
+      const cudaEvent_t* e = &g.ev_band[r * State::kBandEvents];
+      for (int k = 0; k < 6; ++k) {
+        float t = 0.f;
+        if (cudaEventElapsedTime(&t, e[lo[k]], e[hi[k]]) != cudaSuccess) { cudaGetLastError(); return -1; }
+        ms[into[k]] += t;
+      }
+    }
+    if (capacity >= 8) ms[7] = static_cast<float>(g.bands_timed);
+    return 7;
+  }
+  if (capacity >= 8) ms[7] = 0.f;
   return 7;
 }
 

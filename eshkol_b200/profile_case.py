@@ -30,6 +30,7 @@ def main() -> None:
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--tile-n", type=int, default=0, choices=[0, 128, 256])
     ap.add_argument("--pair", type=int, default=-1, help="1: two-SM products kernel, 0: one-SM")
+    ap.add_argument("--band-rows", type=int, default=-1, help="rows per band of the row-band pipeline, 0: off")
     ap.add_argument("--dist", default="normal", choices=["normal", "uniform", "wide"])
     args = ap.parse_args()
     M, K, N = args.m or args.n, args.k or args.n, args.n
@@ -45,6 +46,8 @@ def main() -> None:
     lib.eshkol_b200_set_phase_timing(1)
     if args.pair >= 0:
         lib.eshkol_b200_set_pair_gemm(args.pair)
+    if args.band_rows >= 0:
+        lib.eshkol_b200_set_row_bands(args.band_rows)
     opts = api.make_opts(TIERS[args.tier], args.param, tile_n=args.tile_n)
     stream = torch.cuda.ExternalStream(api.stream_handle(), device=dev)
     out = {}
@@ -62,6 +65,7 @@ def main() -> None:
             ph = (ctypes.c_float * 8)()
             if lib.eshkol_b200_get_phase_times(ph, 8) == 7:
                 out["stages_ms"] = dict(zip(STAGES, (round(float(x), 4) for x in ph[:7])))
+                out["bands"] = int(ph[7])
     print(json.dumps(out))
 
 

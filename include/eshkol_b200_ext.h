@@ -146,14 +146,28 @@ int eshkol_b200_sync_status(void);
  * tile).  Same results either way.  Initial value: environment ESHKOL_B200_PAIR_GEMM. */
 void eshkol_b200_set_pair_gemm(int on);
 
+/* Row-band pipeline of the one-shot exact-tier product (eshkol_b200_gemm_f64_device and
+ * eshkol_b200_gemm_prepared_f64_device): with at least two bands of `rows` rows of A, band
+ * r+1 is scanned and split while band r is multiplied and band r-1 is reconstructed, on
+ * three streams over two workspace slots.  Rows of the result depend on their own row of A
+ * and on B only, so the bits do not change.  rows is rounded up to a multiple of 256;
+ * 0 switches the pipeline off.  Initial value 0 (off), or environment ESHKOL_B200_BAND_ROWS:
+ * on a power-capped B200 the overlapped kernels slow the tensor-core products by about as
+ * much as they hide (8192^3: 7.85 ms serial, 7.78 ms in 4 bands; 16384^3: 59.6 vs 62.8 ms).
+ * The library stream is ordered behind the last band when the call returns. */
+void eshkol_b200_set_row_bands(long long rows);
+
 /* Per-stage timing of the Ozaki-II driver, the counterpart of the reference's
  * ESHKOL_OZAKI_PROFILE line (lib/backend/gpu/gpu_memory.mm:2479, 2658-2664).  When
  * switched on, CUDA events on the library stream bracket each stage of every
  * Ozaki-II GEMM.  get_phase_times waits for the stream and writes the durations
  * of the LAST 16-moduli GEMM in milliseconds: [0] column scan + scales of B,
  * [1] split B, [2] row scan + scales of A, [3] split A, [4] products modulo 256,
- * [5] products modulo the odd moduli, [6] reconstruction.  Returns 7, or -1 when
- * nothing was timed. */
+ * [5] products modulo the odd moduli, [6] reconstruction.  When the product ran through
+ * the row-band pipeline, each of [2]..[6] is the sum over the bands of that stage's kernels
+ * on their own stream (the stages overlap, so they add up to more than the product took)
+ * and, if capacity >= 8, [7] is the number of bands (0 for a serial product).  Returns 7,
+ * or -1 when nothing was timed. */
 void eshkol_b200_set_phase_timing(int on);
 int eshkol_b200_get_phase_times(float* ms, int capacity);
 

@@ -255,3 +255,47 @@ def test_two_sm_products_kernel_bit_exact(gpu_lib, shape):
     finally:
         gpu_lib.eshkol_b200_set_pair_gemm(0)
     assert gu.same_bits(got, ol.oz2_exact(A, B, 52))
+
+
+@pytest.mark.parametrize("shape,band", [((700, 600, 300), 256), ((1030, 2100, 520), 512), ((512, 130, 70), 256)])
+def test_row_band_pipeline_bit_exact(gpu_lib, shape, band):
+    """Bands of rows on three streams (split / products / reconstruction overlapped) give the
+    bits of the serial product and of the oracle, with a ragged last band."""
+    M, K, N = shape
+    A = inputs.full53(71, (M, K))
+    B = inputs.full53(72, (K, N))
+    bias = np.linspace(-1.0, 1.0, M)
+    gpu_lib.eshkol_b200_set_row_bands(0)
+    serial = gu.gemm(A, B)
+    serial_b = gu.gemm(A, B, activation=1, bias=bias, bias_mode=1)
+    gpu_lib.eshkol_b200_set_row_bands(band)
+    try:
+        first = gu.gemm(A, B)
+        second = gu.gemm(A, B)  # the slots and events are reused
+        banded_b = gu.gemm(A, B, activation=1, bias=bias, bias_mode=1)
+    finally:
+        gpu_lib.eshkol_b200_set_row_bands(0)
+    assert gu.same_bits(first, serial) and gu.same_bits(second, serial)
+    assert gu.same_bits(banded_b, serial_b)
+    assert gu.same_bits(first, ol.oz2_exact(A, B, 52))
+
+
+def test_row_band_pipeline_stage_times(gpu_lib):
+    """Stage times under the band pipeline are per-stage sums over the bands."""
+    import ctypes
+    A = inputs.uniform(73, (1024, 512))
+    B = inputs.uniform(74, (512, 512))
+    gpu_lib.eshkol_b200_set_row_bands(256)
+    gpu_lib.eshkol_b200_set_phase_timing(1)
+    try:
+        got = gu.gemm(A, B)
+        ph = (ctypes.c_float * 8)()
+        assert gpu_lib.eshkol_b200_get_phase_times(ph, 8) == 7
+        assert int(ph[7]) == 4 and all(ph[i] > 0.0 for i in range(7))
+        gpu_lib.eshkol_b200_set_row_bands(0)
+        again = gu.gemm(A, B)
+        assert gpu_lib.eshkol_b200_get_phase_times(ph, 8) == 7 and int(ph[7]) == 0
+    finally:
+        gpu_lib.eshkol_b200_set_phase_timing(0)
+        gpu_lib.eshkol_b200_set_row_bands(0)
+    assert gu.same_bits(got, again)
