@@ -168,9 +168,13 @@ def run_b200(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist = None
+    comm_sms = int(os.environ.get("ESHKOL_B200_COMM_SMS", "0"))  # measured: capping the collectives' CTAs costs more than it frees
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
+        if comm_sms > 0:
+            # the collectives run on the SMs the products kernels leave free (see ShardedGemm)
+            os.environ.setdefault("NCCL_MAX_CTAS", str(comm_sms))
         dist.init_process_group("nccl", device_id=dev)
     api.set_device(local)
     lib = eb.load_library()
@@ -190,8 +194,8 @@ def run_b200(args):
         from eshkol_b200.sharded import ShardedGemm
         # column panels of B overlap the broadcast and the gather with the products; worth it
         # once the collectives are a visible share of the step (4 ranks and more)
-        panels = int(os.environ.get("ESHKOL_B200_PANELS", "4" if world >= 4 else "1"))
-        sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=panels)
+        panels = int(os.environ.get("ESHKOL_B200_PANELS", "4"))
+        sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=panels, comm_sms=comm_sms)
         rows = sg.rows
         A = inputs.uniform(1, (rows, n), device=dev, start=sg.row0 * n)
         B = inputs.uniform(2, (n, n), device=dev) if rank == 0 else None
@@ -260,6 +264,23 @@ def run_b200(args):
             dist.destroy_process_group()
         return
 
+    # sharded run: rows another rank computed and this rank only received must carry the bits
+    # of the same rows multiplied here
+    verified = None
+    if sg is not None:
+        r_last, _ = sg.parts[world - 1]
+        probe = 128
+        A_probe = inputs.uniform(1, (probe, n), device=dev, start=r_last * n)
+        C_probe = torch.empty((probe, n), dtype=torch.float64, device=dev)
+        torch.cuda.synchronize()
+        api.gemm_device(A_probe.data_ptr(), B.data_ptr(), C_probe.data_ptr(), probe, n, n, opts)
+        if api.sync_status() != 0:
+            raise RuntimeError("kernel status non-zero")
+        if not torch.equal(C_probe.view(torch.int64), sg.C[r_last:r_last + probe].view(torch.int64)):
+            raise RuntimeError("gathered rows differ from the same rows multiplied on one GPU")
+        verified = probe
+        del A_probe, C_probe
+
     peaks = measured_peaks()
     roofline = None
     if phases:
@@ -317,7 +338,7 @@ def run_b200(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f64",
-        "data": "synthetic", "config": dict(workload_config(world), **({"b_panels": sg.panels} if sg else {})), "clocks": clocks,
+        "data": "synthetic", "config": dict(workload_config(world), **({"b_panels": sg.panels, "sms_left_to_collectives": comm_sms, "rows_checked_against_one_gpu": verified} if sg else {})), "clocks": clocks,
         "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu,
     }
     print(json.dumps(line), flush=True)

@@ -114,6 +114,7 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_elementwise_f64_device", ctypes.c_int, [vp, vp, vp, u64, ctypes.c_int])
     sig("eshkol_b200_sync_status", ctypes.c_int, [])
     sig("eshkol_b200_set_pair_gemm", None, [ctypes.c_int])
+    sig("eshkol_b200_set_sm_limit", None, [ctypes.c_int])
     sig("eshkol_b200_set_row_bands", None, [ctypes.c_longlong])
     sig("eshkol_b200_set_phase_timing", None, [ctypes.c_int])
     sig("eshkol_b200_get_phase_times", ctypes.c_int, [ctypes.POINTER(ctypes.c_float), ctypes.c_int])

@@ -25,6 +25,7 @@ struct State {
   bool ready = false;
   int device = -1;
   int num_sms = 0;
+  int sm_limit = 0;  // > 0: SMs the persistent products kernels may occupy (the rest stay free for a communication library's kernels)
   cudaStream_t stream = nullptr;
   uint8_t* ws = nullptr;
   size_t ws_bytes = 0;
@@ -162,7 +163,12 @@ uint8_t* aux_reserve(size_t bytes) {
 
 uint8_t* workspace_reserve(size_t bytes) { return ensure_workspace(bytes) == 0 ? g.ws : nullptr; }
 cudaStream_t lib_stream() { return g.stream; }
-int lib_num_sms() { return g.num_sms; }
+static inline int gemm_sms() {
+  int n = g.num_sms;
+  if (g.sm_limit > 0 && g.sm_limit < n) n = g.sm_limit;
+  return n < 2 ? 2 : (n & ~1);  // whole CTA pairs
+}
+int lib_num_sms() { return gemm_sms(); }
 int* lib_status_word() { return g.d_status; }
 void count_launches(int n) { g.launches += static_cast<unsigned long long>(n); }
 
@@ -517,7 +523,7 @@ static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, d
     if (tev) B200_CHECK(cudaEventRecord(tev[1], st));
     B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
   } else {
-    B200_CHECK(launch_modgemm(P.bn, kEpiMod256, A.mA0, P.mB0, p0, tiles, g.num_sms, st));
+    B200_CHECK(launch_modgemm(P.bn, kEpiMod256, A.mA0, P.mB0, p0, tiles, gemm_sms(), st));
     if (lanes) { B200_CHECK(cudaEventRecord(ln.g0_done, st)); B200_CHECK(cudaStreamWaitEvent(sp, ln.g0_done, 0)); }
     if (tev) B200_CHECK(cudaEventRecord(tev[3], sp));
     B200_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(P.N), sp));
@@ -525,9 +531,9 @@ static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, d
     if (tev) B200_CHECK(cudaEventRecord(tev[1], st));
     if (g.pair_gemm && P.bn == 256) {
       B200_CHECK(launch_modgemm_pair(kEpiModI8, A.mA1, P.mB1_half, p1, static_cast<int>(A.Mp / (2 * kBM)),
-                                     g.num_sms, st));
+                                     gemm_sms(), st));
     } else {
-      B200_CHECK(launch_modgemm(P.bn, kEpiModI8, A.mA1, P.mB1, p1, tiles * n_odd, g.num_sms, st));
+      B200_CHECK(launch_modgemm(P.bn, kEpiModI8, A.mA1, P.mB1, p1, tiles * n_odd, gemm_sms(), st));
     }
   }
   if (tev) B200_CHECK(cudaEventRecord(tev[2], st));
@@ -774,9 +780,9 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
     if (make_plane_map(&mB0, b0, q.K0, N, 1, static_cast<long long>(N) * q.K0, bn)) return -1;
     if (make_plane_map(&mA1, aodd, q.Kp, M, n_odd, static_cast<long long>(a_stride), kBM)) return -1;
     if (make_plane_map(&mB1, bodd, q.Kp, N, n_odd, static_cast<long long>(b_stride), bn)) return -1;
-    B200_CHECK(launch_modgemm(bn, kEpiMod256, mA0, mB0, p0, tiles, g.num_sms, st));
+    B200_CHECK(launch_modgemm(bn, kEpiMod256, mA0, mB0, p0, tiles, gemm_sms(), st));
     B200_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(N), st));
-    B200_CHECK(launch_modgemm(bn, kEpiModI8, mA1, mB1, p1, tiles * n_odd, g.num_sms, st));
+    B200_CHECK(launch_modgemm(bn, kEpiModI8, mA1, mB1, p1, tiles * n_odd, gemm_sms(), st));
   }
   CrtArgs ca;
   ca.w0 = w0; ca.flip = flip_bits; ca.w_odd = wodd; ca.w_odd_stride = static_cast<long long>(w_stride); ca.ldw = q.Np;
@@ -820,7 +826,22 @@ static int oz2_matmul_host(const double* hA, const double* hB, double* hC, long 
   if (oz2_check_shape(M, K, N, 16)) return -1;
   long long bm = 1024;
   if (M <= 2048) bm = M;  // too small to be worth splitting
-  const long long nblk = (M + bm - 1) / bm;
+  // Row blocks: whole blocks of bm rows, then a taper (half of what is left, rounded to a
+  // tile, until at most 256 rows remain) so that what is still to do once the last byte of A
+  // has crossed the link -- one block's products and its way back -- is a small block.
+  long long blk_r0[272], blk_rows[272];
+  int nblk = 0;
+  {
+    if (M / bm > 250) bm = round_up((M + 249) / 250, 256);
+    long long r0 = 0;
+    while (M - r0 > bm) { blk_r0[nblk] = r0; blk_rows[nblk++] = bm; r0 += bm; }
+    long long left = M - r0;
+    while (M > 2048 && left > 256) {
+      const long long t = round_up(left / 2, kBM);
+      blk_r0[nblk] = r0; blk_rows[nblk++] = t; r0 += t; left -= t;
+    }
+    if (left > 0) { blk_r0[nblk] = r0; blk_rows[nblk++] = left; }
+  }
   const size_t bytesB = static_cast<size_t>(K) * N * 8;
   const size_t bytesA = static_cast<size_t>(bm) * K * 8, bytesC = static_cast<size_t>(bm) * N * 8;
   const size_t need = ((bytesB + 1023) & ~size_t(1023)) + 2 * ((bytesA + 1023) & ~size_t(1023)) +
@@ -854,9 +875,9 @@ static int oz2_matmul_host(const double* hA, const double* hB, double* hC, long 
   B200_CHECK(cudaStreamWaitEvent(st, g.e_b_ready, 0));
   if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256)) return -1;
   int rc = 0;
-  for (long long i = 0; i < nblk && rc == 0; ++i) {
-    const int s = static_cast<int>(i & 1);
-    const long long r0 = i * bm, rows = (r0 + bm <= M) ? bm : M - r0;
+  for (int i = 0; i < nblk && rc == 0; ++i) {
+    const int s = i & 1;
+    const long long r0 = blk_r0[i], rows = blk_rows[i];
     if (i >= 2) B200_CHECK(cudaStreamWaitEvent(g.s_in, g.e_a_free[s], 0));
     B200_CHECK(cudaMemcpyAsync(dA[s], hA + r0 * K, static_cast<size_t>(rows) * K * 8, cudaMemcpyHostToDevice, g.s_in));
     B200_CHECK(cudaEventRecord(g.e_a_ready[s], g.s_in));
@@ -1110,6 +1131,8 @@ int eshkol_b200_sync_status(void) {
 }
 
 void eshkol_b200_set_pair_gemm(int on) { g.pair_gemm = on != 0; }
+
+void eshkol_b200_set_sm_limit(int sms) { g.sm_limit = sms > 0 ? sms : 0; }
 
 void eshkol_b200_set_row_bands(long long rows) {
   // whole pair tiles (256 rows); 0 switches the band pipeline off

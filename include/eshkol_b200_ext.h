@@ -146,6 +146,12 @@ int eshkol_b200_sync_status(void);
  * tile).  Same results either way.  Initial value: environment ESHKOL_B200_PAIR_GEMM. */
 void eshkol_b200_set_pair_gemm(int on);
 
+/* Number of SMs the persistent tensor-core products kernels occupy (one CTA each); 0 = all.
+ * The multi-GPU driver leaves a few SMs free so that the communication library's kernels,
+ * which cannot share an SM with a products CTA (shared memory), run beside the products
+ * instead of waiting for the gaps between them.  Odd values are rounded down. */
+void eshkol_b200_set_sm_limit(int sms);
+
 /* Row-band pipeline of the one-shot exact-tier product (eshkol_b200_gemm_f64_device and
  * eshkol_b200_gemm_prepared_f64_device): with at least two bands of `rows` rows of A, band
  * r+1 is scanned and split while band r is multiplied and band r-1 is reconstructed, on
