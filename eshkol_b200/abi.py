@@ -115,6 +115,8 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_sync_status", ctypes.c_int, [])
     sig("eshkol_b200_set_pair_gemm", None, [ctypes.c_int])
     sig("eshkol_b200_set_sm_limit", None, [ctypes.c_int])
+    sig("eshkol_b200_enable_peer_access", ctypes.c_int, [ctypes.c_int])
+    sig("eshkol_b200_copy_async", ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p])
     sig("eshkol_b200_set_row_bands", None, [ctypes.c_longlong])
     sig("eshkol_b200_set_phase_timing", None, [ctypes.c_int])
     sig("eshkol_b200_get_phase_times", ctypes.c_int, [ctypes.POINTER(ctypes.c_float), ctypes.c_int])

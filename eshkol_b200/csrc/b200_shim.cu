@@ -1132,6 +1132,30 @@ int eshkol_b200_sync_status(void) {
 
 void eshkol_b200_set_pair_gemm(int on) { g.pair_gemm = on != 0; }
 
+int eshkol_b200_enable_peer_access(int peer_device) {
+  if (!g.ready) return -1;
+  if (peer_device == g.device) return 0;
+  int can = 0;
+  if (cudaDeviceCanAccessPeer(&can, g.device, peer_device) != cudaSuccess || !can) { cudaGetLastError(); return -1; }
+  B200_CHECK(cudaSetDevice(g.device));
+  const cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+  if (e != cudaSuccess && e != cudaErrorPeerAccessAlreadyEnabled) {
+    fprintf(stderr, "[eshkol-b200] peer access to device %d: %s\n", peer_device, cudaGetErrorString(e));
+    cudaGetLastError();
+    return -1;
+  }
+  cudaGetLastError();
+  return 0;
+}
+
+int eshkol_b200_copy_async(void* dst, const void* src, size_t bytes, void* stream) {
+  if (!g.ready || !dst || !src) return -1;
+  if (bytes == 0) return 0;
+  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : g.stream;
+  B200_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, st));
+  return 0;
+}
+
 void eshkol_b200_set_sm_limit(int sms) { g.sm_limit = sms > 0 ? sms : 0; }
 
 void eshkol_b200_set_row_bands(long long rows) {

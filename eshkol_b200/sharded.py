@@ -104,7 +104,8 @@ class ShardedGemm:
     """
 
     def __init__(self, M: int, K: int, N: int, device, *, tier: int = 0, param: int = 0, src: int = 0,
-                 group=None, gemm: Optional[Callable] = None, panels: int = 1, comm_sms: int = 0):
+                 group=None, gemm: Optional[Callable] = None, panels: int = 1, comm_sms: int = 0,
+                 transport: str = "collectives"):
         self.M, self.K, self.N = M, K, N
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -125,6 +126,144 @@ class ShardedGemm:
         self.Cp = torch.empty((self.panels, self.world, self.max_rows, self.width), dtype=torch.float64,
                               device=self.device)
         self.C = torch.empty((M, N), dtype=torch.float64, device=self.device)
+        self.transport = "collectives"
+        if transport == "copy_engine" and self.world > 1 and self.backend.on_device:
+            self._open_peers()
+            self.transport = "copy_engine"
+        elif transport not in ("collectives", "copy_engine"):
+            raise ValueError(f"unknown transport {transport!r}")
+
+    # ------------------------------------------------------------ copy-engine transport
+    def _open_peers(self) -> None:
+        """Every rank opens every other rank's panel buffers (CUDA IPC) and hand-off events
+        (interprocess events).  Data then moves by copy-engine pulls over NVLink, ordered on
+        the device by those events; a gloo barrier only makes sure an event's record has been
+        *called* before a peer calls wait on it (the host runs far ahead of the device)."""
+        import datetime
+        from torch.multiprocessing.reductions import reduce_tensor
+        lib = self.backend.lib
+        self.ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=180))
+        my_dev = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        devs = [None] * self.world
+        dist.all_gather_object(devs, my_dev, group=self.ctl)
+        for q, d in enumerate(devs):
+            if q != self.rank and lib.eshkol_b200_enable_peer_access(d) != 0:
+                raise RuntimeError(f"no peer access from device {my_dev} to device {d}")
+
+        def share(t: torch.Tensor) -> list:
+            fn, args = reduce_tensor(t)
+            objs = [None] * self.world
+            dist.all_gather_object(objs, (fn, args), group=self.ctl)
+            return [t if q == self.rank else objs[q][0](*objs[q][1]) for q in range(self.world)]
+
+        self._peer_B = share(self.Bp)
+        self._peer_C = share(self.Cp)
+
+        def share_events(n: int) -> list:
+            mine = [torch.cuda.Event(enable_timing=False, interprocess=True) for _ in range(n)]
+            for e in mine:
+                e.record(torch.cuda.current_stream(self.device))
+            handles = [e.ipc_handle() for e in mine]
+            objs = [None] * self.world
+            dist.all_gather_object(objs, handles, group=self.ctl)
+            return [mine if q == self.rank else
+                    [torch.cuda.Event.from_ipc_handle(torch.device("cuda", devs[q]), h) for h in objs[q]]
+                    for q in range(self.world)]
+
+        P = self.panels
+        self._ev_packed = share_events(P)   # on the source rank: panel p packed
+        self._ev_slice = share_events(P)    # this rank's K-slice of panel p is in its Bp
+        self._ev_block = share_events(P)    # this rank's block of C, panel p, is computed
+        self._x1 = torch.cuda.Stream(self.device)
+        self._x2 = torch.cuda.Stream(self.device)
+        self._k_parts = row_partition(self.K, self.world)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.ctl)
+
+    def _pull(self, dst: torch.Tensor, src: torch.Tensor, stream) -> None:
+        """one copy-engine transfer of a contiguous block, enqueued on `stream`"""
+        if not (dst.is_contiguous() and src.is_contiguous()) or dst.numel() != src.numel():
+            raise ValueError("pull needs two contiguous blocks of one size")
+        rc = self.backend.lib.eshkol_b200_copy_async(dst.data_ptr(), src.data_ptr(),
+                                                     dst.numel() * dst.element_size(), stream.cuda_stream)
+        if rc != 0:
+            raise RuntimeError("copy_async failed")
+
+    def _step_copy_engine(self, A_rows: torch.Tensor, B_src: Optional[torch.Tensor]) -> torch.Tensor:
+        P, w, R, W = self.panels, self.width, self.rank, self.world
+        cur = torch.cuda.current_stream(self.device)
+        lib = self.backend.stream
+        if self._side is None:
+            self._side = torch.cuda.Stream(self.device)
+        x1, x2, xo = self._x1, self._x2, self._side
+        self._mark("start", cur)
+        for st in (x1, x2, xo):
+            st.wait_stream(cur)
+        if self.rows:
+            lib.wait_stream(cur)
+            self.backend.begin(A_rows, w)
+            self._mark("A prepared", lib)
+        # B: the source packs a panel; every rank pulls its own K-slice of it from the source
+        # (phase 1, the source's egress carries the panel once), then the other slices from
+        # the ranks that hold them (phase 2)
+        if R == self.src:
+            for p in range(P):
+                self.Bp[p].copy_(B_src[:, p * w:(p + 1) * w])
+                self._ev_packed[R][p].record(cur)
+                self._ev_slice[R][p].record(cur)
+        dist.barrier(group=self.ctl)
+        k0, kn = self._k_parts[R]
+        if R != self.src:
+            for p in range(P):
+                x1.wait_event(self._ev_packed[self.src][p])
+                self._pull(self.Bp[p, k0:k0 + kn], self._peer_B[self.src][p, k0:k0 + kn], x1)
+                self._ev_slice[R][p].record(x1)
+        dist.barrier(group=self.ctl)
+        arrived = []
+        for p in range(P):
+            if R != self.src:
+                for i in range(1, W):
+                    q = (R + i) % W
+                    q0, qn = self._k_parts[q]
+                    x2.wait_event(self._ev_slice[q][p])
+                    self._pull(self.Bp[p, q0:q0 + qn], self._peer_B[q][p, q0:q0 + qn], x2)
+                x2.wait_event(self._ev_slice[R][p])
+            else:
+                x2.wait_event(self._ev_packed[R][p])
+            ev = torch.cuda.Event()
+            ev.record(x2)
+            arrived.append(ev)
+            self._mark(f"B panel {p} arrived", x2)
+        for p in range(P):
+            if self.rows:
+                lib.wait_event(arrived[p])
+                self._mark(f"panel {p} products start", lib)
+                self.backend.panel(A_rows, self.Bp[p], self.Cp[p, R, : self.rows])
+                self._mark(f"panel {p} products done", lib)
+            self._ev_block[R][p].record(lib)
+        dist.barrier(group=self.ctl)
+        # C: pull every other rank's block of a panel once it is computed, then unpack the panel
+        for p in range(P):
+            for i in range(1, W):
+                q = (R + i) % W
+                rows_q = self.parts[q][1]
+                if rows_q == 0:
+                    continue
+                xo.wait_event(self._ev_block[q][p])
+                self._pull(self.Cp[p, q, :rows_q], self._peer_C[q][p, q, :rows_q], xo)
+            xo.wait_event(self._ev_block[R][p])
+            self._mark(f"panel {p} gathered", xo)
+            with torch.cuda.stream(xo):
+                self._unpack(p)
+        self._mark("unpacked", xo)
+        cur.wait_stream(xo)
+        cur.wait_stream(x1)
+        cur.wait_stream(x2)
+        self.backend.finish()
+        cur.synchronize()
+        # nobody overwrites a buffer a peer may still be reading
+        dist.barrier(group=self.ctl)
+        return self.C
 
     def _unpack(self, p: int) -> None:
         """gathered panel p, [rank][row][column in panel] -> its columns of the row-major C"""

@@ -146,6 +146,17 @@ int eshkol_b200_sync_status(void);
  * tile).  Same results either way.  Initial value: environment ESHKOL_B200_PAIR_GEMM. */
 void eshkol_b200_set_pair_gemm(int on);
 
+/* Copy-engine transfers for the multi-GPU driver (no counterpart in the reference, which is
+ * single-device).  enable_peer_access lets the library's device read and write peer_device's
+ * memory directly over NVLink (0 = enabled or already so, -1 = no peer path).  copy_async
+ * enqueues one cudaMemcpyAsync of `bytes` bytes on `stream` (a cudaStream_t; NULL = the
+ * library stream); dst and src are device pointers of this process, either of which may
+ * live on a peer device (e.g. another rank's buffer opened through CUDA IPC).  The copy
+ * engines move the data: no SM is used, so the transfers do not compete with the
+ * products kernels for shared memory. */
+int eshkol_b200_enable_peer_access(int peer_device);
+int eshkol_b200_copy_async(void* dst, const void* src, size_t bytes, void* stream);
+
 /* Number of SMs the persistent tensor-core products kernels occupy (one CTA each); 0 = all.
  * The multi-GPU driver leaves a few SMs free so that the communication library's kernels,
  * which cannot share an SM with a products CTA (shared memory), run beside the products
