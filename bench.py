@@ -319,6 +319,20 @@ def run_b200(args):
             "phases_ms": dict(zip(["scan_b", "split_b", "scan_a", "split_a", "products_mod256",
                                    "products_odd", "reconstruct"], phases)),
         }
+        # the memory-side stages against the measured copy bandwidth: algorithmic bytes per
+        # element are 8 read + 15 (odd planes) + 1024/1008 (modulus-256 plane) + 0.25 (flag
+        # bit-planes) written for a split, 15 + 2 + 0.125 read + 8 written for the reconstruction
+        kn = float(n) * Bdev.shape[1]
+        mk = float(rows) * n
+        mn = float(rows) * Bdev.shape[1]
+        split_bytes = 8.0 + 15.0 + 1024.0 / 1008.0 + 0.25
+        stages = [("scan_cols (B)", 8.0 * kn, phases[0]), ("split_b", split_bytes * kn, phases[1]),
+                  ("scan_rows (A)", 8.0 * mk, phases[2]), ("split_a", split_bytes * mk, phases[3]),
+                  ("crt (reconstruction)", (17.125 + 8.0) * mn, phases[6])]
+        roofline["hbm_stages"] = [
+            {"kernel": name, "bound": "hbm", "achieved": b / (ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"],
+             "unit": "GB/s", "frac": b / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "ms": ms}
+            for name, b, ms in stages if ms > 0]
         int8_peak = measure_int8_library_peak(torch, dev)
         if int8_peak:
             roofline["int8_cublaslt_tops_live"] = int8_peak

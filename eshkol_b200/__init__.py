@@ -20,6 +20,7 @@ from .api import (  # noqa: F401
     matmul,
     matmul_dispatch,
     batch_matmul_dispatch,
+    matmul_backward,
     conv2d,
     gemm_device,
     conv2d_device,

@@ -43,6 +43,8 @@ class GemmOpts(ctypes.Structure):
         ("use_simt_products", ctypes.c_int32),
         ("gemm_tile_n", ctypes.c_int32),
         ("ldc", ctypes.c_int64),
+        ("trans_a", ctypes.c_int32),
+        ("trans_b", ctypes.c_int32),
     ]
 
 
@@ -96,12 +98,14 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_matmul_dispatch", None, [vp, vp, vp, u64, u64, u64, i32])
     sig("eshkol_batch_matmul_dispatch", None, [vp, vp, vp, i64, i64, i64, i64, i32])
     sig("eshkol_gpu_conv2d_f64", ctypes.c_int, [vp, i64, i64, i64, i64, vp, i64, i64, i64, i64, i64, vp, i32])
+    sig("eshkol_gpu_matmul_backward_f64", ctypes.c_int, [vp, vp, vp, vp, vp, u64, u64, u64])
     sig("eshkol_b200_init", ctypes.c_int, [ctypes.c_int])
     sig("eshkol_b200_shutdown", None, [])
     sig("eshkol_b200_stream", vp, [])
     sig("eshkol_b200_gemm_f64_device", ctypes.c_int, [vp, vp, vp, u64, u64, u64, optp])
     sig("eshkol_b200_gemm_f64_static_scratch", ctypes.c_int, [vp, vp, vp, u64, u64, u64])
     sig("eshkol_b200_matmul_f64_host", ctypes.c_int, [vp, vp, vp, u64, u64, u64, optp])
+    sig("eshkol_b200_matmul_backward_f64_host", ctypes.c_int, [vp, vp, vp, vp, vp, u64, u64, u64, optp, optp])
     sig("eshkol_b200_prepare_b_f64_device", ctypes.c_int, [vp, u64, u64])
     sig("eshkol_b200_gemm_prepared_f64_device", ctypes.c_int, [vp, vp, u64, optp])
     sig("eshkol_b200_prepare_a_f64_device", ctypes.c_int, [vp, u64, u64, u64])

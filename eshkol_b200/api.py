@@ -41,6 +41,23 @@ def matmul_dispatch(A, B, dtype: int = 0) -> np.ndarray:
 matmul = matmul_dispatch
 
 
+def matmul_backward(G, A, B):
+    """(grad_A, grad_B) of C = A @ B for the upstream gradient G, through
+    eshkol_gpu_matmul_backward_f64 on host arrays; raises when the GPU path declines or fails."""
+    G, A, B = _f64(G), _f64(A), _f64(B)
+    M, K = A.shape
+    N = B.shape[1]
+    if G.shape != (M, N) or B.shape[0] != K:
+        raise ValueError("shapes do not match")
+    gA = np.empty((M, K), dtype=np.float64)
+    gB = np.empty((K, N), dtype=np.float64)
+    rc = load_library().eshkol_gpu_matmul_backward_f64(G.ctypes.data, A.ctypes.data, B.ctypes.data,
+                                                      gA.ctypes.data, gB.ctypes.data, M, K, N)
+    if rc != 0:
+        raise RuntimeError("eshkol_gpu_matmul_backward_f64 returned -1")
+    return gA, gB
+
+
 def batch_matmul_dispatch(a, b, dtype: int = 0) -> np.ndarray:
     a, b = _f64(a), _f64(b)
     batch, M, K = a.shape
@@ -79,7 +96,8 @@ def conv2d(inp, ker, stride: int = 1, pad: int = 0, activation: int = 0) -> np.n
 
 
 def make_opts(tier: int = 0, param: int = 0, activation: int = 0, bias_ptr: int = 0, bias_mode: int = 0,
-              use_simt: bool = False, tile_n: int = 0, ldc: int = 0) -> GemmOpts:
+              use_simt: bool = False, tile_n: int = 0, ldc: int = 0, trans_a: bool = False,
+              trans_b: bool = False) -> GemmOpts:
     o = GemmOpts()
     o.tier, o.param, o.activation = tier, param, activation
     o.bias_mode, o.bias = (bias_mode if bias_ptr else 0), (bias_ptr or None)
@@ -87,6 +105,7 @@ def make_opts(tier: int = 0, param: int = 0, activation: int = 0, bias_ptr: int 
     o.use_simt_products = 1 if use_simt else 0
     o.gemm_tile_n = tile_n
     o.ldc = ldc
+    o.trans_a, o.trans_b = (1 if trans_a else 0), (1 if trans_b else 0)
     return o
 
 

@@ -33,6 +33,8 @@ struct State {
   unsigned long long launches = 0;
   uint8_t* aux = nullptr;  // second scratch block (conv2d im2col operand)
   size_t aux_bytes = 0;
+  uint8_t* tbuf = nullptr;  // third scratch block: operands transposed for the tiers that need it
+  size_t tbuf_bytes = 0;
   PFN_cuTensorMapEncodeTiled_v12000 encode = nullptr;
   // optional per-stage timing of the Ozaki-II driver (CUDA events on the stream)
   bool timing = false;
@@ -159,6 +161,21 @@ uint8_t* aux_reserve(size_t bytes) {
   }
   g.aux_bytes = bytes;
   return g.aux;
+}
+
+static uint8_t* tbuf_reserve(size_t bytes) {
+  if (bytes <= g.tbuf_bytes) return g.tbuf;
+  if (cudaStreamSynchronize(g.stream) != cudaSuccess) return nullptr;
+  if (g.tbuf) cudaFree(g.tbuf);
+  g.tbuf = nullptr;
+  g.tbuf_bytes = 0;
+  if (cudaMalloc(&g.tbuf, bytes) != cudaSuccess) {
+    fprintf(stderr, "[eshkol-b200] scratch allocation of %zu bytes failed\n", bytes);
+    cudaGetLastError();
+    return nullptr;
+  }
+  g.tbuf_bytes = bytes;
+  return g.tbuf;
 }
 
 uint8_t* workspace_reserve(size_t bytes) { return ensure_workspace(bytes) == 0 ? g.ws : nullptr; }
@@ -316,7 +333,7 @@ static int oz2_check_shape(long long M, long long K, long long N, int n_mod) {
 // host pipeline, the row-sharded multi-GPU driver) without touching B again.  Only
 // with all 16 moduli, where the exponent E is 52 whatever the data; with fewer moduli
 // E depends on the maxima of both operands and the one-shot path below is used.
-static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
+static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, bool trans = false) {
   if (oz2_check_shape(1, K, N, 16)) return -1;
   const Oz2Geom q = oz2_geometry(1, K, N, bn);
   const int n_odd = 15;
@@ -357,11 +374,15 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn) {
   const bool timed = g.timing && g.ev_made;
   g.ev_valid = false;
   B200_MARK(0);
-  B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(P.bmax), st));
+  // trans: B is stored N x K (each column of the operand is a contiguous row), which is the
+  // layout the row scan and the non-transposing split of a left-hand operand read
+  if (trans) B200_CHECK(launch_scan_rows(dB, N, K, P.bmax, st));
+  else B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(P.bmax), st));
   B200_CHECK(launch_scales(P.bmax, N, 52, P.nu, P.sb, P.sbi, st));
   B200_MARK(1);
   SplitPlanes pb{N, K, q.Kp, q.K0, q.n_chunks, n_odd, P.b0, P.b_hi, P.b_odd, P.bodd, P.bodd_stride};
-  B200_CHECK(launch_split_b(dB, P.sb, N, pb, P.consts, st));
+  if (trans) B200_CHECK(launch_split_a(dB, P.sb, pb, P.consts, st));
+  else B200_CHECK(launch_split_b(dB, P.sb, N, pb, P.consts, st));
   B200_MARK(2);
   g.launches += 3;
   if (make_plane_map(&P.mB0, P.b0, q.K0, N, 1, static_cast<long long>(N) * q.K0, bn)) return -1;
@@ -399,7 +420,7 @@ static ALayout oz2_a_layout(const Oz2Geom& q) {
 // scan, scale and split one block of rows on stream st into the planes behind ws.
 // tev (optional): three events recorded before the scan, after the scales, after the split.
 static int oz2_prepare_a_at(State::PreparedA& A, uint8_t* ws, const Oz2Geom& q, const double* dA,
-                            cudaStream_t st, cudaEvent_t* tev) {
+                            cudaStream_t st, cudaEvent_t* tev, bool trans = false) {
   const int n_odd = 15;
   const ALayout L = oz2_a_layout(q);
   const long long M = q.M;
@@ -419,11 +440,14 @@ static int oz2_prepare_a_at(State::PreparedA& A, uint8_t* ws, const Oz2Geom& q, 
   Oz2DeviceConsts hc;
   oz2_host_consts(16, &hc, nullptr);
   if (tev) B200_CHECK(cudaEventRecord(tev[0], st));
-  B200_CHECK(launch_scan_rows(dA, M, q.K, A.amax, st));
+  // trans: A is stored K x M, the layout of a right-hand operand: column scan, transposing split
+  if (trans) B200_CHECK(launch_scan_cols(dA, q.K, M, reinterpret_cast<unsigned long long*>(A.amax), st));
+  else B200_CHECK(launch_scan_rows(dA, M, q.K, A.amax, st));
   B200_CHECK(launch_scales(A.amax, M, 52, A.mu, A.sa, A.sai, st));
   if (tev) B200_CHECK(cudaEventRecord(tev[1], st));
   SplitPlanes pa{M, q.K, q.Kp, q.K0, q.n_chunks, n_odd, A.a0, A.a_hi, A.a_odd, A.aodd, A.a_stride};
-  B200_CHECK(launch_split_a(dA, A.sa, pa, hc, st));
+  if (trans) B200_CHECK(launch_split_b(dA, A.sa, M, pa, hc, st));
+  else B200_CHECK(launch_split_a(dA, A.sa, pa, hc, st));
   if (tev) B200_CHECK(cudaEventRecord(tev[2], st));
   g.launches += 3;
   if (make_plane_map(&A.mA0, A.a0, q.K0, M, 1, static_cast<long long>(M) * q.K0, kBM)) return -1;
@@ -436,14 +460,15 @@ static int oz2_prepare_a_at(State::PreparedA& A, uint8_t* ws, const Oz2Geom& q, 
 // of rows of A, kept at the front of the workspace; room for the product residues of
 // a result up to n_cols_hint columns wide is reserved behind them so that the
 // following multiplications never move the planes.
-static int oz2_prepare_a(const double* dA, long long M, long long K, long long n_cols_hint, int bn) {
+static int oz2_prepare_a(const double* dA, long long M, long long K, long long n_cols_hint, int bn,
+                         bool trans = false) {
   if (oz2_check_shape(M, K, n_cols_hint, 16)) return -1;
   const Oz2Geom q = oz2_geometry(M, K, n_cols_hint, bn);
   g.prepA.valid = false;
   if (ensure_workspace(oz2_a_layout(q).total) != 0) return -1;
   const bool timed = g.timing && g.ev_made;
   g.bands_timed = 0;
-  return oz2_prepare_a_at(g.prepA, g.ws, q, dA, g.stream, timed ? &g.ev[3] : nullptr);
+  return oz2_prepare_a_at(g.prepA, g.ws, q, dA, g.stream, timed ? &g.ev[3] : nullptr, trans);
 }
 
 // Streams of one multiplication.  Serial: all three are the library stream.  In the band
@@ -660,13 +685,14 @@ static int oz2_gemm_rows(const double* dA, double* dC, long long M, const Eshkol
     return -1;
   }
   const long long bm = g.band_rows;
-  if (allow_bands && bm >= 256 && M >= 2 * bm && o.pixels_per_image == 0 && !o.use_simt_products) {
+  if (allow_bands && bm >= 256 && M >= 2 * bm && o.pixels_per_image == 0 && !o.use_simt_products &&
+      !o.trans_a) {
     // bands of whole pair tiles; at most kMaxBands of them
     long long rows = bm;
     while ((M + rows - 1) / rows > State::kMaxBands) rows *= 2;
     return oz2_gemm_banded(dA, dC, M, rows, o);
   }
-  if (oz2_prepare_a(dA, M, P.K, P.N, P.bn)) return -1;
+  if (oz2_prepare_a(dA, M, P.K, P.N, P.bn, o.trans_a != 0)) return -1;
   const int rc = oz2_multiply(dC, o);
   g.prepA.valid = false;  // dA belongs to the caller
   return rc;
@@ -810,7 +836,7 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
                        long long N, int n_mod, const EshkolB200GemmOpts& o) {
   if (n_mod != 16) return ozaki2_gemm_general(dA, dB, dC, M, K, N, n_mod, o);
   if (oz2_check_shape(M, K, N, 16)) return -1;
-  if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256)) return -1;
+  if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256, o.trans_b != 0)) return -1;
   const int rc = oz2_gemm_rows(dA, dC, M, o, true);
   g.prep.valid = false;  // dB belongs to the caller and may change before the next call
   return rc;
@@ -962,6 +988,7 @@ void eshkol_b200_shutdown(void) {
   cudaStreamSynchronize(g.stream);
   if (g.ws) cudaFree(g.ws);
   if (g.aux) cudaFree(g.aux);
+  if (g.tbuf) cudaFree(g.tbuf);
   if (g.d_status) cudaFree(g.d_status);
   if (g.ev_made) {
     for (int i = 0; i < 9; ++i) cudaEventDestroy(g.ev[i]);
@@ -1003,6 +1030,24 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC, 
   memset(&o, 0, sizeof(o));
   if (opts) o = *opts;
   const long long m = static_cast<long long>(M), k = static_cast<long long>(K), n = static_cast<long long>(N);
+  if ((o.trans_a || o.trans_b) &&
+      !(o.tier == ESHKOL_B200_TIER_OZAKI2 && (o.param == 0 || o.param == 16) && !o.use_simt_products)) {
+    // only the 16-moduli exact tier reads transposed storage directly
+    const size_t ba = o.trans_a ? ((static_cast<size_t>(m) * k * 8 + 1023) & ~size_t(1023)) : 0;
+    const size_t bb = o.trans_b ? static_cast<size_t>(k) * n * 8 : 0;
+    uint8_t* t = tbuf_reserve(ba + bb);
+    if (!t) return -1;
+    if (o.trans_a) {
+      B200_CHECK(launch_transpose(dA, k, m, reinterpret_cast<double*>(t), g.stream));
+      dA = reinterpret_cast<const double*>(t);
+    }
+    if (o.trans_b) {
+      B200_CHECK(launch_transpose(dB, n, k, reinterpret_cast<double*>(t + ba), g.stream));
+      dB = reinterpret_cast<const double*>(t + ba);
+    }
+    g.launches += (o.trans_a ? 1 : 0) + (o.trans_b ? 1 : 0);
+    o.trans_a = o.trans_b = 0;
+  }
   switch (o.tier) {
     case ESHKOL_B200_TIER_OZAKI2:
       return ozaki2_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 16, o);
@@ -1031,6 +1076,45 @@ int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, 
   if (o.tier != ESHKOL_B200_TIER_OZAKI2 || (o.param != 0 && o.param != 16)) return -2;
   return oz2_matmul_host(hA, hB, hC, static_cast<long long>(M), static_cast<long long>(K),
                          static_cast<long long>(N), o);
+}
+
+int eshkol_b200_matmul_backward_f64_host(const double* grad_out, const double* A, const double* B,
+                                         double* grad_A, double* grad_B, uint64_t M, uint64_t K,
+                                         uint64_t N, const EshkolB200GemmOpts* opts_grad_a,
+                                         const EshkolB200GemmOpts* opts_grad_b) {
+  if (!g.ready) {
+    fprintf(stderr, "[eshkol-b200] matmul backward called before eshkol_b200_init succeeded\n");
+    return -1;
+  }
+  if (!grad_out || !A || !B || !grad_A || !grad_B || M == 0 || K == 0 || N == 0) return -1;
+  EshkolB200GemmOpts oa, ob;
+  memset(&oa, 0, sizeof(oa));
+  memset(&ob, 0, sizeof(ob));
+  if (opts_grad_a) { oa.tier = opts_grad_a->tier; oa.param = opts_grad_a->param; }
+  if (opts_grad_b) { ob.tier = opts_grad_b->tier; ob.param = opts_grad_b->param; }
+  const size_t bg = (M * N * 8 + 1023) & ~size_t(1023), ba = (M * K * 8 + 1023) & ~size_t(1023),
+               bb = (K * N * 8 + 1023) & ~size_t(1023);
+  uint8_t* base = aux_reserve(bg + 2 * ba + 2 * bb);
+  if (!base) return -1;
+  double* dG = reinterpret_cast<double*>(base);
+  double* dA = reinterpret_cast<double*>(base + bg);
+  double* dB = reinterpret_cast<double*>(base + bg + ba);
+  double* dGA = reinterpret_cast<double*>(base + bg + ba + bb);
+  double* dGB = reinterpret_cast<double*>(base + bg + 2 * ba + bb);
+  cudaStream_t st = g.stream;
+  B200_CHECK(cudaMemcpyAsync(dG, grad_out, M * N * 8, cudaMemcpyHostToDevice, st));
+  B200_CHECK(cudaMemcpyAsync(dB, B, K * N * 8, cudaMemcpyHostToDevice, st));
+  // grad_A[M x K] = G[M x N] * B^T: inner dimension N, B stored (columns of the operand) x (inner)
+  oa.trans_a = 0; oa.trans_b = 1;
+  if (eshkol_b200_gemm_f64_device(dG, dB, dGA, M, N, K, &oa) != 0) return -1;
+  B200_CHECK(cudaMemcpyAsync(grad_A, dGA, M * K * 8, cudaMemcpyDeviceToHost, st));
+  B200_CHECK(cudaMemcpyAsync(dA, A, M * K * 8, cudaMemcpyHostToDevice, st));
+  // grad_B[K x N] = A^T * G: inner dimension M, A stored (inner) x (rows of the operand)
+  ob.trans_a = 1; ob.trans_b = 0;
+  if (eshkol_b200_gemm_f64_device(dA, dG, dGB, K, M, N, &ob) != 0) return -1;
+  B200_CHECK(cudaMemcpyAsync(grad_B, dGB, K * N * 8, cudaMemcpyDeviceToHost, st));
+  B200_CHECK(cudaStreamSynchronize(st));
+  return 0;
 }
 
 int eshkol_b200_prepare_b_f64_device(const double* dB, uint64_t K, uint64_t N) {

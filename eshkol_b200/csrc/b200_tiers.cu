@@ -461,6 +461,35 @@ __global__ void __launch_bounds__(256) elementwise_kernel(const double* __restri
 
 }  // namespace
 
+namespace {
+// 32 x 32 tiles through padded shared memory: both sides coalesced
+__global__ void __launch_bounds__(256) transpose_kernel(const double* __restrict__ src, long long rows,
+                                                        long long cols, double* __restrict__ dst) {
+  __shared__ double tile[32][33];
+  const long long c0 = static_cast<long long>(blockIdx.x) * 32, r0 = static_cast<long long>(blockIdx.y) * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const long long r = r0 + ty + 8 * k, c = c0 + tx;
+    if (r < rows && c < cols) tile[ty + 8 * k][tx] = src[r * cols + c];
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const long long c = c0 + ty + 8 * k, r = r0 + tx;
+    if (r < rows && c < cols) dst[c * rows + r] = tile[tx][ty + 8 * k];
+  }
+}
+}  // namespace
+
+cudaError_t launch_transpose(const double* src, long long rows, long long cols, double* dst, cudaStream_t st) {
+  if (rows <= 0 || cols <= 0) return cudaSuccess;
+  const long long gx = (cols + 31) / 32, gy = (rows + 31) / 32;
+  if (gy > 65535) return cudaErrorInvalidValue;
+  transpose_kernel<<<dim3(static_cast<unsigned>(gx), static_cast<unsigned>(gy)), 256, 0, st>>>(src, rows, cols, dst);
+  return cudaGetLastError();
+}
+
 cudaError_t launch_elementwise(const double* a, const double* b, double* out, long long n, int op,
                                cudaStream_t st) {
   long long blocks = (n + 255) / 256;

@@ -32,6 +32,8 @@ int conv2d_lowered(const double* d_in, long long batch, long long in_c, long lon
                    const double* d_ker, long long out_c, long long kH, long long kW,
                    long long stride, long long pad, double* d_out, const EshkolB200GemmOpts& o);
 cudaError_t tiers_set_attributes();
+// dst[cols x rows] = transpose of src[rows x cols] (row-major f64)
+cudaError_t launch_transpose(const double* src, long long rows, long long cols, double* dst, cudaStream_t st);
 cudaError_t launch_elementwise(const double* a, const double* b, double* out, long long n, int op,
                                cudaStream_t st);
 

@@ -487,3 +487,28 @@ int eshkol_gpu_conv2d_f64(const double* in, int64_t batch, int64_t in_c, int64_t
   if (rc) fprintf(stderr, "[GPU] eshkol_gpu_conv2d_f64: the B200 path FAILED\n");
   return rc;
 }
+
+int eshkol_gpu_matmul_backward_f64(const double* grad_out, const double* A, const double* B,
+                                   double* grad_A, double* grad_B, uint64_t M, uint64_t K, uint64_t N) {
+  if (!grad_out || !A || !B || !grad_A || !grad_B || M == 0 || K == 0 || N == 0) return -1;
+  if (g_backend == ESHKOL_GPU_NONE) eshkol_gpu_init();
+  if (g_backend != ESHKOL_GPU_CUDA) return -1;
+  const size_t out_a = (size_t)(M * K), out_b = (size_t)(K * N);
+  if (!eshkol_gpu_should_use(out_a > out_b ? out_a : out_b)) return -1; /* blas_backend.cpp:957-958 */
+  /* each gradient is a product of its own shape and gets the tier that shape would get */
+  const TierChoice ca = choose_tier(M, N, K), cb = choose_tier(K, M, N);
+  EshkolB200GemmOpts oa, ob;
+  memset(&oa, 0, sizeof(oa));
+  memset(&ob, 0, sizeof(ob));
+  oa.tier = ca.tier; oa.param = ca.param;
+  ob.tier = cb.tier; ob.param = cb.param;
+  GPU_LOG("matmul backward M=%llu K=%llu N=%llu -> grad_A tier %d:%d, grad_B tier %d:%d (%s)",
+          (unsigned long long)M, (unsigned long long)K, (unsigned long long)N, ca.tier, ca.param,
+          cb.tier, cb.param, ca.why);
+  if (eshkol_b200_matmul_backward_f64_host(grad_out, A, B, grad_A, grad_B, M, K, N, &oa, &ob) != 0 ||
+      eshkol_b200_sync_status() != 0) {
+    fprintf(stderr, "[GPU] eshkol_gpu_matmul_backward_f64: the B200 path FAILED\n");
+    return -1;
+  }
+  return 0;
+}

@@ -51,6 +51,8 @@ typedef struct EshkolB200GemmOpts {
   int32_t use_simt_products;/* tests only: integer products on CUDA cores instead of tcgen05 */
   int32_t gemm_tile_n;      /* 0 = default (256), or 128 */
   int64_t ldc;              /* elements between rows of C; 0 = N (C may be a column panel of a wider matrix) */
+  int32_t trans_a;          /* 1: A is stored K x M row-major (the product uses its transpose) */
+  int32_t trans_b;          /* 1: B is stored N x K row-major (the product uses its transpose) */
 } EshkolB200GemmOpts;
 
 /* Selects `device`, creates the stream and queries the SM count.  Idempotent.
@@ -61,11 +63,29 @@ void eshkol_b200_shutdown(void);
 /* The CUDA stream (cudaStream_t) every call of this library enqueues on. */
 void* eshkol_b200_stream(void);
 
-/* C[M x N] = A[M x K] * B[K x N], row-major f64, all three in device memory.
- * Asynchronous.  opts may be NULL (exact tier, no epilogue). */
+/* C[M x N] = op(A)[M x K] * op(B)[K x N], row-major f64, all three in device memory.
+ * Asynchronous.  opts may be NULL (exact tier, no epilogue, no transposes).  With
+ * opts->trans_a / trans_b an operand is read in its transposed storage: the exact tier
+ * (16 moduli) reads it directly -- a transposed A goes through the column scan and the
+ * transposing split that B normally takes, a transposed B through the row scan and split
+ * of A -- and the result carries the bits of the product of the explicitly transposed
+ * matrices; the other tiers transpose into library scratch first.  This is what the
+ * gradients of a product need (grad_A = G * B^T, grad_B = A^T * G) without the host-side
+ * transposes of lib/backend/blas_backend.cpp:969-977. */
 int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC,
                                 uint64_t M, uint64_t K, uint64_t N,
                                 const EshkolB200GemmOpts* opts);
+
+/* Both gradients of C = A * B from host memory (the GPU branch of
+ * eshkol_matmul_backward_f64, lib/backend/blas_backend.cpp:924-1012, without its host
+ * transposes): grad_A[M x K] = grad_out[M x N] * B^T, grad_B[K x N] = A^T * grad_out, each
+ * with the bits of eshkol_b200_gemm_f64_device on the explicitly transposed operand.
+ * Synchronous; returns 0 or -1.  opts_grad_a / opts_grad_b select the tier of each product as
+ * for the forward one (NULL = exact tier); only their tier and param are used. */
+int eshkol_b200_matmul_backward_f64_host(const double* grad_out, const double* A, const double* B,
+                                         double* grad_A, double* grad_B, uint64_t M, uint64_t K,
+                                         uint64_t N, const EshkolB200GemmOpts* opts_grad_a,
+                                         const EshkolB200GemmOpts* opts_grad_b);
 
 /* Exact tier (16 moduli) with the right-hand operand prepared once: prepare_b scans
  * and splits B (K x N, device memory) into library-owned residue planes; each

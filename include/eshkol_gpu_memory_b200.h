@@ -168,6 +168,18 @@ int eshkol_gpu_conv2d_f64(const double* in, int64_t batch, int64_t in_c, int64_t
                           const double* ker, int64_t out_c, int64_t kH, int64_t kW,
                           int64_t stride, int64_t pad, double* out, int32_t activation);
 
+/* Both gradients of C = A * B on host arrays: grad_A[M x K] = grad_out * B^T and
+ * grad_B[K x N] = A^T * grad_out.  The GPU branch of eshkol_matmul_backward_f64
+ * (lib/backend/blas_backend.cpp:955-1012) in one call: that branch transposes A and B on the
+ * host and wraps six buffers around two eshkol_gpu_matmul_f64 calls; here the operands are
+ * uploaded once and read transposed on the device.  Each gradient carries the bits the
+ * reference's two calls would produce in the same tier.  The tier follows the environment as
+ * for the forward product, with each gradient's own shape.  Returns 0, or -1 when the GPU path
+ * is unavailable or failed (the caller then takes its BLAS branch, as it does today); below the
+ * element threshold of eshkol_gpu_should_use it returns -1 without touching the GPU. */
+int eshkol_gpu_matmul_backward_f64(const double* grad_out, const double* A, const double* B,
+                                   double* grad_A, double* grad_B, uint64_t M, uint64_t K, uint64_t N);
+
 #ifdef __cplusplus
 }
 #endif

@@ -7,20 +7,22 @@ import eshkol_b200 as eb
 from eshkol_b200 import api
 
 
-def gemm(A, B, tier=eb.TIER_OZAKI2, param=0, simt=False, tile_n=0, activation=0, bias=None, bias_mode=0):
-    """C = A @ B on the GPU via eshkol_b200_gemm_f64_device; numpy in, numpy out."""
+def gemm(A, B, tier=eb.TIER_OZAKI2, param=0, simt=False, tile_n=0, activation=0, bias=None, bias_mode=0,
+         trans_a=False, trans_b=False):
+    """C = op(A) @ op(B) on the GPU via eshkol_b200_gemm_f64_device; numpy in, numpy out.
+    With trans_a / trans_b the array passed is the transposed storage (K x M, N x K)."""
     import torch
     dA = torch.from_numpy(np.ascontiguousarray(A, dtype=np.float64)).cuda()
     dB = torch.from_numpy(np.ascontiguousarray(B, dtype=np.float64)).cuda()
-    M, K = dA.shape
-    N = dB.shape[1]
+    M, K = (dA.shape[1], dA.shape[0]) if trans_a else dA.shape
+    N = dB.shape[0] if trans_b else dB.shape[1]
     dC = torch.full((M, N), float("nan"), dtype=torch.float64, device="cuda")
     dbias = None
     if bias is not None:
         dbias = torch.from_numpy(np.ascontiguousarray(bias, dtype=np.float64)).cuda()
     torch.cuda.synchronize()
     opts = api.make_opts(tier, param, activation, dbias.data_ptr() if dbias is not None else 0, bias_mode,
-                         simt, tile_n)
+                         simt, tile_n, 0, trans_a, trans_b)
     api.gemm_device(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), M, K, N, opts)
     st = api.sync_status()
     assert st == 0, f"kernel status {st}"

@@ -147,6 +147,23 @@ def ref_matmul(A, B, blas: bool = False):
     return C
 
 
+def ref_matmul_backward(G, A, B, blas: bool = True):
+    """The reference's own eshkol_matmul_backward_f64 (lib/backend/blas_backend.cpp:924), CPU build."""
+    L = ref_lib("libref_matmul_blas.so" if blas else "libref_matmul_simd.so")
+    if L is None or not hasattr(L, "eshkol_matmul_backward_f64"):
+        return None
+    G = np.ascontiguousarray(G, dtype=np.float64)
+    A = np.ascontiguousarray(A, dtype=np.float64)
+    B = np.ascontiguousarray(B, dtype=np.float64)
+    gA = np.zeros_like(A)
+    gB = np.zeros_like(B)
+    u64 = ctypes.c_uint64
+    L.eshkol_matmul_backward_f64.argtypes = [_dp, _dp, _dp, _dp, _dp, u64, u64, u64]
+    L.eshkol_matmul_backward_f64.restype = None
+    L.eshkol_matmul_backward_f64(_p(G), _p(A), _p(B), _p(gA), _p(gB), A.shape[0], A.shape[1], B.shape[1])
+    return gA, gB
+
+
 def ref_conv2d(inp, ker, stride=1, pad=0):
     L = ref_lib("libref_conv.so")
     if L is None:

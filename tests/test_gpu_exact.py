@@ -299,3 +299,79 @@ def test_row_band_pipeline_stage_times(gpu_lib):
         gpu_lib.eshkol_b200_set_phase_timing(0)
         gpu_lib.eshkol_b200_set_row_bands(0)
     assert gu.same_bits(got, again)
+
+
+def test_sharded_configuration_depth_sampled_rows(gpu_lib):
+    """K = 32768 (33 extraction chunks), the depth of the multi-GPU configuration: a few rows
+    of A against 2048 columns of B, bit for bit against the oracle."""
+    K = 32768
+    A = inputs.uniform(1, (4, K), start=12345 * K)
+    B = inputs.uniform(2, (K, 2048))
+    assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, 52))
+
+
+def test_largest_exact_depth(gpu_lib):
+    """K = 131071 is the last depth whose int32 accumulation of 127^2-bounded products is exact
+    and the last the exact tier accepts; one more is refused."""
+    K = 131071
+    A = inputs.full53(81, (3, K))
+    B = inputs.full53(82, (K, 40))
+    assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, 52))
+    import torch
+    dA = torch.zeros((1, K + 1), dtype=torch.float64, device="cuda")
+    dB = torch.zeros((K + 1, 1), dtype=torch.float64, device="cuda")
+    dC = torch.zeros((1, 1), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    rc = gpu_lib.eshkol_b200_gemm_f64_device(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 1, K + 1, 1,
+                                             api.make_opts(eb.TIER_OZAKI2, 16))
+    assert rc == -1
+
+
+@pytest.mark.parametrize("shape", [(130, 300, 70), (257, 1100, 129), (64, 64, 64)])
+def test_transposed_operands_read_in_place(gpu_lib, shape):
+    """trans_a / trans_b: the exact tier reads the transposed storage directly (column scan and
+    transposing split for A, row scan and plain split for B); bits of the explicit transposes."""
+    M, K, N = shape
+    A = inputs.full53(91, (M, K))
+    B = inputs.full53(92, (K, N))
+    want = ol.oz2_exact(A, B, 52)
+    At = np.ascontiguousarray(A.T)
+    Bt = np.ascontiguousarray(B.T)
+    assert gu.same_bits(gu.gemm(At, B, trans_a=True), want)
+    assert gu.same_bits(gu.gemm(A, Bt, trans_b=True), want)
+    assert gu.same_bits(gu.gemm(At, Bt, trans_a=True, trans_b=True), want)
+
+
+@pytest.mark.parametrize("tier,param", [(eb.TIER_OZAKI1, 4), (eb.TIER_OZAKI2_FAST, 12), (eb.TIER_DGEMM, 0),
+                                        (eb.TIER_OZAKI2, 9)])
+def test_transposed_operands_other_tiers(gpu_lib, tier, param):
+    A = inputs.uniform(93, (100, 260))
+    B = inputs.uniform(94, (260, 150))
+    want = gu.gemm(A, B, tier=tier, param=param)
+    got = gu.gemm(np.ascontiguousarray(A.T), np.ascontiguousarray(B.T), tier=tier, param=param,
+                  trans_a=True, trans_b=True)
+    assert gu.same_bits(got, want)
+
+
+def test_matmul_backward_both_gradients(gpu_lib):
+    """eshkol_gpu_matmul_backward_f64: grad_A = G B^T and grad_B = A^T G with the bits of the exact
+    products of the explicitly transposed operands, and the reference's CPU backward to the tier's accuracy."""
+    M, K, N = 300, 520, 260
+    G = inputs.normal(95, (M, N))
+    A = inputs.uniform(96, (M, K))
+    B = inputs.wide(97, (K, N), span=9, lo=-4)
+    gpu_lib.eshkol_gpu_set_threshold(1)
+    try:
+        gA, gB = eb.matmul_backward(G, A, B)
+    finally:
+        gpu_lib.eshkol_gpu_set_threshold(100000)
+    assert gu.same_bits(gA, ol.oz2_exact(G, np.ascontiguousarray(B.T), 52))
+    assert gu.same_bits(gB, ol.oz2_exact(np.ascontiguousarray(A.T), G, 52))
+    ref = ol.ref_matmul_backward(G, A, B)
+    if ref is not None:
+        # the tier's own error is bounded by about 2^-25 of sum |g||b|; allow 2^-22
+        assert np.all(np.abs(gA - ref[0]) <= (np.abs(G) @ np.abs(B.T)) * 2.0 ** -22)
+        assert np.all(np.abs(gB - ref[1]) <= (np.abs(A.T) @ np.abs(G)) * 2.0 ** -22)
+    # below the element threshold the call declines and the caller keeps its CPU branch
+    with pytest.raises(RuntimeError):
+        eb.matmul_backward(G[:4, :4], A[:4, :4], np.ascontiguousarray(B[:4, :4]))

@@ -138,3 +138,21 @@ def test_reference_cpu_matmul_agrees_with_oracle_to_rounding():
     assert np.median(err) < 1e-14
     assert np.mean(err < 1e-12) > 0.98
     assert np.max(err / np.maximum(np.abs(ref), 1e-9)) < 1e-6
+
+
+def test_reference_backward_is_two_products_of_transposes():
+    """eshkol_matmul_backward_f64 (blas_backend.cpp:924) compiled from the reference: grad_A and
+    grad_B equal G B^T and A^T G; the oracle's exact products of the transposed operands agree
+    with it to the tier's accuracy.  This is what the GPU backward entry is compared with."""
+    rng = np.random.default_rng(5)
+    G, A, B = rng.standard_normal((37, 29)), rng.standard_normal((37, 41)), rng.standard_normal((41, 29))
+    ref = ol.ref_matmul_backward(G, A, B)
+    if ref is None:
+        pytest.skip("reference CPU library not built")
+    gA, gB = ref
+    np.testing.assert_allclose(gA, G @ B.T, rtol=1e-12, atol=1e-12)
+    np.testing.assert_allclose(gB, A.T @ G, rtol=1e-12, atol=1e-12)
+    # the exact tier's own error (its split CRT weights round in about 0.7 % of the cells, near
+    # 2^-25 of the row-by-column magnitude) bounds the agreement, as for the forward product
+    np.testing.assert_allclose(ol.oz2_exact(G, np.ascontiguousarray(B.T), 52), gA, rtol=1e-6, atol=5e-6)
+    np.testing.assert_allclose(ol.oz2_exact(np.ascontiguousarray(A.T), G, 52), gB, rtol=1e-6, atol=5e-6)
