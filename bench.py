@@ -201,7 +201,7 @@ def run_b200(args):
         rows = sg.rows
         A = inputs.uniform(1, (rows, n), device=dev, start=sg.row0 * n)
         B = inputs.uniform(2, (n, n), device=dev) if rank == 0 else None
-        C_local = sg.Cp[0, rank, :rows]
+        C_local = torch.empty((rows, sg.width), dtype=torch.float64, device=dev)  # the stage-timed product's output
     torch.cuda.synchronize()
 
     def step():

@@ -121,6 +121,17 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_set_sm_limit", None, [ctypes.c_int])
     sig("eshkol_b200_enable_peer_access", ctypes.c_int, [ctypes.c_int])
     sig("eshkol_b200_copy_async", ctypes.c_int, [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p])
+    hp = ctypes.c_char_p
+    sig("eshkol_b200_ipc_export_mem", ctypes.c_int, [vp, hp])
+    sig("eshkol_b200_ipc_import_mem", ctypes.c_int, [hp, ctypes.POINTER(vp)])
+    sig("eshkol_b200_ipc_close_mem", ctypes.c_int, [vp])
+    sig("eshkol_b200_ipc_event_create", ctypes.c_int, [ctypes.POINTER(vp), hp])
+    sig("eshkol_b200_ipc_event_import", ctypes.c_int, [hp, ctypes.POINTER(vp)])
+    sig("eshkol_b200_event_record", ctypes.c_int, [vp, vp])
+    sig("eshkol_b200_event_wait", ctypes.c_int, [vp, vp])
+    sig("eshkol_b200_event_destroy", ctypes.c_int, [vp])
+    sig("eshkol_b200_copy2d_async", ctypes.c_int, [ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_size_t,
+                                                   ctypes.c_size_t, ctypes.c_size_t, ctypes.c_void_p])
     sig("eshkol_b200_set_row_bands", None, [ctypes.c_longlong])
     sig("eshkol_b200_set_phase_timing", None, [ctypes.c_int])
     sig("eshkol_b200_get_phase_times", ctypes.c_int, [ctypes.POINTER(ctypes.c_float), ctypes.c_int])

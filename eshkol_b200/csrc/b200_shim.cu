@@ -948,7 +948,9 @@ int eshkol_b200_init(int device) {
   {
     int least = 0, greatest = 0;
     B200_CHECK(cudaDeviceGetStreamPriorityRange(&least, &greatest));
-    B200_CHECK(cudaStreamCreateWithPriority(&g.stream, cudaStreamNonBlocking, greatest));
+    const char* pe = getenv("ESHKOL_B200_STREAM_PRIORITY");  // "default": do not raise the library stream
+    const bool raise = !(pe && !strcmp(pe, "default"));
+    B200_CHECK(cudaStreamCreateWithPriority(&g.stream, cudaStreamNonBlocking, raise ? greatest : least));
   }
   // [0] kernel status word, [1] work counter of the persistent products kernel
   B200_CHECK(cudaMalloc(&g.d_status, 2 * sizeof(int)));
@@ -1235,8 +1237,86 @@ int eshkol_b200_enable_peer_access(int peer_device) {
 int eshkol_b200_copy_async(void* dst, const void* src, size_t bytes, void* stream) {
   if (!g.ready || !dst || !src) return -1;
   if (bytes == 0) return 0;
-  cudaStream_t st = stream ? static_cast<cudaStream_t>(stream) : g.stream;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
   B200_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, st));
+  return 0;
+}
+
+// ---- interprocess handles (one process per GPU): memory and events of a peer rank ----
+int eshkol_b200_ipc_export_mem(void* device_ptr, unsigned char handle[64]) {
+  if (!g.ready || !device_ptr || !handle) return -1;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+  cudaIpcMemHandle_t h;
+  B200_CHECK(cudaIpcGetMemHandle(&h, device_ptr));
+  memcpy(handle, &h, 64);
+  return 0;
+}
+
+int eshkol_b200_ipc_import_mem(const unsigned char handle[64], void** device_ptr) {
+  if (!g.ready || !device_ptr || !handle) return -1;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  B200_CHECK(cudaSetDevice(g.device));
+  // opened in this rank's own context; peer access to the owning device is enabled on demand
+  B200_CHECK(cudaIpcOpenMemHandle(device_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+
+int eshkol_b200_ipc_close_mem(void* device_ptr) {
+  if (!g.ready || !device_ptr) return -1;
+  B200_CHECK(cudaIpcCloseMemHandle(device_ptr));
+  return 0;
+}
+
+int eshkol_b200_ipc_event_create(void** event, unsigned char handle[64]) {
+  if (!g.ready || !event || !handle) return -1;
+  static_assert(sizeof(cudaIpcEventHandle_t) == 64, "handle size");
+  cudaEvent_t ev = nullptr;
+  B200_CHECK(cudaSetDevice(g.device));
+  B200_CHECK(cudaEventCreateWithFlags(&ev, cudaEventDisableTiming | cudaEventInterprocess));
+  cudaIpcEventHandle_t h;
+  B200_CHECK(cudaIpcGetEventHandle(&h, ev));
+  memcpy(handle, &h, 64);
+  *event = ev;
+  return 0;
+}
+
+int eshkol_b200_ipc_event_import(const unsigned char handle[64], void** event) {
+  if (!g.ready || !event || !handle) return -1;
+  cudaIpcEventHandle_t h;
+  memcpy(&h, handle, 64);
+  cudaEvent_t ev = nullptr;
+  B200_CHECK(cudaSetDevice(g.device));
+  B200_CHECK(cudaIpcOpenEventHandle(&ev, h));
+  *event = ev;
+  return 0;
+}
+
+int eshkol_b200_event_record(void* event, void* stream) {
+  if (!g.ready || !event) return -1;
+  B200_CHECK(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+
+int eshkol_b200_event_wait(void* event, void* stream) {
+  if (!g.ready || !event) return -1;
+  B200_CHECK(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream),
+                                 static_cast<cudaEvent_t>(event), 0));
+  return 0;
+}
+
+int eshkol_b200_event_destroy(void* event) {
+  if (!g.ready || !event) return -1;
+  B200_CHECK(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  return 0;
+}
+
+int eshkol_b200_copy2d_async(void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                             size_t width_bytes, size_t rows, void* stream) {
+  if (!g.ready || !dst || !src) return -1;
+  if (width_bytes == 0 || rows == 0) return 0;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  B200_CHECK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, rows, cudaMemcpyDefault, st));
   return 0;
 }
 

@@ -10,6 +10,7 @@ has no multi-device code; this is the sharding BASELINE's 32768^3 configuration 
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Callable, Optional
 
 import torch
@@ -57,12 +58,14 @@ class _DeviceBackend:
                         "prepare_a")
 
     def panel(self, a: torch.Tensor, b: torch.Tensor, c: torch.Tensor) -> None:
+        """c: rows x panel-width view, contiguous or a column panel of a wider row-major matrix"""
+        ldc = 0 if c.is_contiguous() else c.stride(0)
+        opts = self.api.make_opts(self.tier, self.param, ldc=ldc)
         if self.prepared:
             self._check(self.lib.eshkol_b200_prepare_b_f64_device(b.data_ptr(), b.shape[0], b.shape[1]), "prepare_b")
-            self._check(self.lib.eshkol_b200_multiply_prepared_f64_device(c.data_ptr(), None), "multiply")
+            self._check(self.lib.eshkol_b200_multiply_prepared_f64_device(c.data_ptr(), ctypes.byref(opts)), "multiply")
         else:
-            self.api.gemm_device(a.data_ptr(), b.data_ptr(), c.data_ptr(), a.shape[0], a.shape[1], b.shape[1],
-                                 self.api.make_opts(self.tier, self.param))
+            self.api.gemm_device(a.data_ptr(), b.data_ptr(), c.data_ptr(), a.shape[0], a.shape[1], b.shape[1], opts)
 
     def finish(self) -> None:
         st = self.api.sync_status()
@@ -120,74 +123,133 @@ class ShardedGemm:
         self.trace = None  # set to [] to collect (label, CUDA event) marks of the next step
         self.panels = panels if (panels > 0 and N % panels == 0) else 1
         self.width = N // self.panels
-        # panel-major copy of B: panel p is the contiguous K x width block of columns p*width ...
-        self.Bp = torch.empty((self.panels, K, self.width), dtype=torch.float64, device=self.device)
-        # gathered blocks: [panel][rank][row][column in panel]; padding rows are never read back
-        self.Cp = torch.empty((self.panels, self.world, self.max_rows, self.width), dtype=torch.float64,
-                              device=self.device)
-        self.C = torch.empty((M, N), dtype=torch.float64, device=self.device)
+        if transport not in ("collectives", "copy_engine"):
+            raise ValueError(f"unknown transport {transport!r}")
         self.transport = "collectives"
+        self.Cp = None
         if transport == "copy_engine" and self.world > 1 and self.backend.on_device:
+            # the panel buffer of B and C itself are library allocations the peers open; products
+            # write their block of C in place and the peers pull it from there
             self._open_peers()
             self.transport = "copy_engine"
-        elif transport not in ("collectives", "copy_engine"):
-            raise ValueError(f"unknown transport {transport!r}")
+        else:
+            # panel-major copy of B: panel p is the contiguous K x width block of columns p*width ...
+            self.Bp = torch.empty((self.panels, K, self.width), dtype=torch.float64, device=self.device)
+            self.C = torch.empty((M, N), dtype=torch.float64, device=self.device)
+            # gathered blocks: [panel][rank][row][column in panel]; padding rows are never read back
+            self.Cp = torch.empty((self.panels, self.world, self.max_rows, self.width), dtype=torch.float64,
+                                  device=self.device)
 
     # ------------------------------------------------------------ copy-engine transport
+    class _DeviceBlock:
+        """A cudaMalloc block owned by the library, visible to torch as a tensor."""
+
+        def __init__(self, lib, shape, device):
+            self.lib = lib
+            n = 1
+            for d in shape:
+                n *= d
+            ptr = ctypes.c_void_p()
+            if lib.eshkol_b200_mem_alloc(0, n * 8, ctypes.byref(ptr)) != 0:
+                raise RuntimeError(f"allocation of {n * 8} bytes failed")
+            self.ptr = ptr.value
+            self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f8", "data": (self.ptr, False),
+                                             "version": 2, "strides": None}
+            self.tensor = torch.as_tensor(self, device=device)
+
+        def handle(self) -> bytes:
+            buf = ctypes.create_string_buffer(64)
+            if self.lib.eshkol_b200_ipc_export_mem(self.ptr, buf) != 0:
+                raise RuntimeError("ipc_export_mem failed")
+            return buf.raw
+
     def _open_peers(self) -> None:
-        """Every rank opens every other rank's panel buffers (CUDA IPC) and hand-off events
-        (interprocess events).  Data then moves by copy-engine pulls over NVLink, ordered on
-        the device by those events; a gloo barrier only makes sure an event's record has been
-        *called* before a peer calls wait on it (the host runs far ahead of the device)."""
+        """Every rank opens every other rank's B-panel buffer and C (CUDA IPC memory handles,
+        opened in the rank's own context) and its hand-off events (interprocess events).  Data
+        then moves by copy-engine pulls over NVLink, ordered on the device by those events; a
+        gloo barrier only makes sure an event's record has been *called* before a peer calls
+        wait on it (the host runs far ahead of the device)."""
         import datetime
-        from torch.multiprocessing.reductions import reduce_tensor
         lib = self.backend.lib
         self.ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=180))
-        my_dev = self.device.index if self.device.index is not None else torch.cuda.current_device()
-        devs = [None] * self.world
-        dist.all_gather_object(devs, my_dev, group=self.ctl)
-        for q, d in enumerate(devs):
-            if q != self.rank and lib.eshkol_b200_enable_peer_access(d) != 0:
-                raise RuntimeError(f"no peer access from device {my_dev} to device {d}")
+        W, R, P = self.world, self.rank, self.panels
 
-        def share(t: torch.Tensor) -> list:
-            fn, args = reduce_tensor(t)
-            objs = [None] * self.world
-            dist.all_gather_object(objs, (fn, args), group=self.ctl)
-            return [t if q == self.rank else objs[q][0](*objs[q][1]) for q in range(self.world)]
+        def exchange(obj):
+            objs = [None] * W
+            dist.all_gather_object(objs, obj, group=self.ctl)
+            return objs
 
-        self._peer_B = share(self.Bp)
-        self._peer_C = share(self.Cp)
+        def import_mem(handle: bytes) -> int:
+            out = ctypes.c_void_p()
+            if lib.eshkol_b200_ipc_import_mem(handle, ctypes.byref(out)) != 0:
+                raise RuntimeError("ipc_import_mem failed (no peer access between the GPUs?)")
+            return out.value
 
-        def share_events(n: int) -> list:
-            mine = [torch.cuda.Event(enable_timing=False, interprocess=True) for _ in range(n)]
-            for e in mine:
-                e.record(torch.cuda.current_stream(self.device))
-            handles = [e.ipc_handle() for e in mine]
-            objs = [None] * self.world
-            dist.all_gather_object(objs, handles, group=self.ctl)
-            return [mine if q == self.rank else
-                    [torch.cuda.Event.from_ipc_handle(torch.device("cuda", devs[q]), h) for h in objs[q]]
-                    for q in range(self.world)]
+        self._blk_B = self._DeviceBlock(lib, (P, self.K, self.width), self.device)
+        self._blk_C = self._DeviceBlock(lib, (self.M, self.N), self.device)
+        self.Bp, self.C = self._blk_B.tensor, self._blk_C.tensor
+        hs = exchange((self._blk_B.handle(), self._blk_C.handle()))
+        # base addresses of every rank's Bp and C in this process (own rank: the local pointer)
+        self._addr_B = [self._blk_B.ptr if q == R else import_mem(hs[q][0]) for q in range(W)]
+        self._addr_C = [self._blk_C.ptr if q == R else import_mem(hs[q][1]) for q in range(W)]
 
-        P = self.panels
-        self._ev_packed = share_events(P)   # on the source rank: panel p packed
-        self._ev_slice = share_events(P)    # this rank's K-slice of panel p is in its Bp
-        self._ev_block = share_events(P)    # this rank's block of C, panel p, is computed
+        def make_events(n: int):
+            mine, handles = [], []
+            for _ in range(n):
+                ev, buf = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+                if lib.eshkol_b200_ipc_event_create(ctypes.byref(ev), buf) != 0:
+                    raise RuntimeError("ipc_event_create failed")
+                mine.append(ev.value)
+                handles.append(buf.raw)
+            theirs = exchange(handles)
+            table = []
+            for q in range(W):
+                if q == R:
+                    table.append(mine)
+                    continue
+                row = []
+                for h in theirs[q]:
+                    ev = ctypes.c_void_p()
+                    if lib.eshkol_b200_ipc_event_import(h, ctypes.byref(ev)) != 0:
+                        raise RuntimeError("ipc_event_import failed")
+                    row.append(ev.value)
+                table.append(row)
+            return table
+
+        self._ev_packed = make_events(P)   # on the source rank: panel p packed
+        self._ev_slice = make_events(P)    # this rank's K-slice of panel p is in its Bp
+        self._ev_block = make_events(P)    # this rank's block of C, panel p, is computed
         self._x1 = torch.cuda.Stream(self.device)
         self._x2 = torch.cuda.Stream(self.device)
-        self._k_parts = row_partition(self.K, self.world)
+        self._k_parts = row_partition(self.K, W)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.ctl)
 
-    def _pull(self, dst: torch.Tensor, src: torch.Tensor, stream) -> None:
-        """one copy-engine transfer of a contiguous block, enqueued on `stream`"""
-        if not (dst.is_contiguous() and src.is_contiguous()) or dst.numel() != src.numel():
-            raise ValueError("pull needs two contiguous blocks of one size")
-        rc = self.backend.lib.eshkol_b200_copy_async(dst.data_ptr(), src.data_ptr(),
-                                                     dst.numel() * dst.element_size(), stream.cuda_stream)
+    def _record(self, ev: int, stream) -> None:
+        if self.backend.lib.eshkol_b200_event_record(ev, stream.cuda_stream) != 0:
+            raise RuntimeError("event_record failed")
+
+    def _wait(self, ev: int, stream) -> None:
+        if self.backend.lib.eshkol_b200_event_wait(ev, stream.cuda_stream) != 0:
+            raise RuntimeError("event_wait failed")
+
+    def _pull_b_slice(self, q_from: int, p: int, k0: int, kn: int, stream) -> None:
+        """rows [k0, k0+kn) of panel p: rank q_from's Bp -> this rank's Bp (contiguous, one copy)"""
+        off = (p * self.K + k0) * self.width * 8
+        rc = self.backend.lib.eshkol_b200_copy_async(self._addr_B[self.rank] + off, self._addr_B[q_from] + off,
+                                                     kn * self.width * 8, stream.cuda_stream)
         if rc != 0:
             raise RuntimeError("copy_async failed")
+
+    def _pull_c_block(self, q: int, p: int, stream) -> None:
+        """rank q's rows of the panel-p columns of C: its C -> the same place in this rank's C"""
+        q0, rows_q = self.parts[q]
+        off = (q0 * self.N + p * self.width) * 8
+        rc = self.backend.lib.eshkol_b200_copy2d_async(self._addr_C[self.rank] + off, self.N * 8,
+                                                       self._addr_C[q] + off, self.N * 8, self.width * 8, rows_q,
+                                                       stream.cuda_stream)
+        if rc != 0:
+            raise RuntimeError("copy2d_async failed")
 
     def _step_copy_engine(self, A_rows: torch.Tensor, B_src: Optional[torch.Tensor]) -> torch.Tensor:
         P, w, R, W = self.panels, self.width, self.rank, self.world
@@ -207,17 +269,28 @@ class ShardedGemm:
         # (phase 1, the source's egress carries the panel once), then the other slices from
         # the ranks that hold them (phase 2)
         if R == self.src:
+            if not (B_src.is_contiguous() and B_src.shape == (self.K, self.N)):
+                raise ValueError("B must be a contiguous K x N matrix")
+            # packed by the copy engines (about 0.9 TB/s on an idle GPU): an elementwise kernel of
+            # another stream would wait for the gaps between the products kernels
+            st = x1
             for p in range(P):
-                self.Bp[p].copy_(B_src[:, p * w:(p + 1) * w])
-                self._ev_packed[R][p].record(cur)
-                self._ev_slice[R][p].record(cur)
+                rc = self.backend.lib.eshkol_b200_copy2d_async(
+                    self._addr_B[R] + p * self.K * w * 8, w * 8, B_src.data_ptr() + p * w * 8, self.N * 8,
+                    w * 8, self.K, st.cuda_stream)
+                if rc != 0:
+                    raise RuntimeError("copy2d_async failed")
+                self._mark(f"packed {p}", st)
+                self._record(self._ev_packed[R][p], st)
+                self._record(self._ev_slice[R][p], st)
         dist.barrier(group=self.ctl)
         k0, kn = self._k_parts[R]
         if R != self.src:
             for p in range(P):
-                x1.wait_event(self._ev_packed[self.src][p])
-                self._pull(self.Bp[p, k0:k0 + kn], self._peer_B[self.src][p, k0:k0 + kn], x1)
-                self._ev_slice[R][p].record(x1)
+                self._wait(self._ev_packed[self.src][p], x1)
+                self._pull_b_slice(self.src, p, k0, kn, x1)
+                self._mark(f"own slice {p}", x1)
+                self._record(self._ev_slice[R][p], x1)
         dist.barrier(group=self.ctl)
         arrived = []
         for p in range(P):
@@ -225,11 +298,11 @@ class ShardedGemm:
                 for i in range(1, W):
                     q = (R + i) % W
                     q0, qn = self._k_parts[q]
-                    x2.wait_event(self._ev_slice[q][p])
-                    self._pull(self.Bp[p, q0:q0 + qn], self._peer_B[q][p, q0:q0 + qn], x2)
-                x2.wait_event(self._ev_slice[R][p])
+                    self._wait(self._ev_slice[q][p], x2)
+                    self._pull_b_slice(q, p, q0, qn, x2)
+                self._wait(self._ev_slice[R][p], x2)
             else:
-                x2.wait_event(self._ev_packed[R][p])
+                self._wait(self._ev_packed[R][p], x2)
             ev = torch.cuda.Event()
             ev.record(x2)
             arrived.append(ev)
@@ -238,24 +311,20 @@ class ShardedGemm:
             if self.rows:
                 lib.wait_event(arrived[p])
                 self._mark(f"panel {p} products start", lib)
-                self.backend.panel(A_rows, self.Bp[p], self.Cp[p, R, : self.rows])
+                self.backend.panel(A_rows, self.Bp[p], self.C[self.row0:self.row0 + self.rows, p * w:(p + 1) * w])
                 self._mark(f"panel {p} products done", lib)
-            self._ev_block[R][p].record(lib)
+            self._record(self._ev_block[R][p], lib)
         dist.barrier(group=self.ctl)
-        # C: pull every other rank's block of a panel once it is computed, then unpack the panel
+        # C: pull every other rank's block of a panel, straight into its place in C, once computed
         for p in range(P):
             for i in range(1, W):
                 q = (R + i) % W
-                rows_q = self.parts[q][1]
-                if rows_q == 0:
+                if self.parts[q][1] == 0:
                     continue
-                xo.wait_event(self._ev_block[q][p])
-                self._pull(self.Cp[p, q, :rows_q], self._peer_C[q][p, q, :rows_q], xo)
-            xo.wait_event(self._ev_block[R][p])
+                self._wait(self._ev_block[q][p], xo)
+                self._pull_c_block(q, p, xo)
             self._mark(f"panel {p} gathered", xo)
-            with torch.cuda.stream(xo):
-                self._unpack(p)
-        self._mark("unpacked", xo)
+        cur.wait_stream(lib)
         cur.wait_stream(xo)
         cur.wait_stream(x1)
         cur.wait_stream(x2)
@@ -308,6 +377,8 @@ class ShardedGemm:
         side = self._side
         if self.rank == self.src and B_src is None:
             raise ValueError("the source rank must pass B")
+        if self.transport == "copy_engine":
+            return self._step_copy_engine(A_rows, B_src)
         self._mark("start", cur)
         if dev:
             side.wait_stream(cur)  # whoever read C after the last step did so on torch's stream
