@@ -17,6 +17,7 @@ enum GemmEpilogue : int {
   kEpiModI8 = 0,     // centred residue mod an odd modulus -> int8 plane
   kEpiRawI32 = 1,    // raw int32 accumulator -> int32 plane
   kEpiMod256 = 2,    // per-chunk reduction mod 256 with the reference's tie rule -> int16 plane
+  kEpiF16 = 3,       // f16 operands, f32 accumulator; rounded to f16 and widened -> f64 matrix
 };
 
 // One accumulation: sum over segments of A_plane[seg] * B_plane[seg]^T.
@@ -49,6 +50,8 @@ struct GemmParams {
   int n_chunks;
   // kEpiMod256: per chunk, row and 32 columns, (tie mask, bit-8 mask) of the byte sums
   uint32_t* tie_bits;
+  // kEpiF16: the output is the caller's matrix, not a padded plane: rows / columns that exist
+  int out_rows, out_cols;
 };
 
 // Launchers (b200_modgemm.cu).  bn is 128 or 256.
@@ -85,6 +88,7 @@ inline GemmParams make_gemm_params() {
   p.a_hi = p.a_odd = p.b_odd = p.b_hi = nullptr;
   p.n_chunks = 0;
   p.tie_bits = nullptr;
+  p.out_rows = p.out_cols = 0;
   return p;
 }
 cudaError_t launch_modgemm_simt(int epi, const SimtPlanes& pl, const GemmParams& prm,

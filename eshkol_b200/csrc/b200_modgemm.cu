@@ -13,6 +13,8 @@
 // Replaces, on the reference's side, the per-modulus Metal GEMM
 // (lib/backend/gpu/metal_softfloat.h:3907-4100) and the per-pair cublasGemmEx
 // calls (lib/backend/gpu/gpu_memory_cuda.cpp:413-436).
+#include <cuda_fp16.h>
+
 #include "b200_common.cuh"
 #include "b200_internal.h"
 #include "b200_residue.cuh"
@@ -161,7 +163,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   } else if (warp == 1) {
     // -------------------------------------------------------------- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_s8(kBM, BN);
+      constexpr uint32_t idesc = (EPI == kEpiF16) ? umma_idesc_f16(kBM, BN) : umma_idesc_s8(kBM, BN);
       int stage = 0;
       uint32_t phase = 0, unit = 0;
       bool ok = true;
@@ -200,8 +202,10 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const uint64_t db = umma_desc_k128(tile_base + kStages * kABytes + stage * kBBytes);
 #pragma unroll
             for (int k = 0; k < kBK / kUmmaK; ++k) {
-              // +32 bytes along K inside the swizzle atom = +2 in the encoded address
-              umma_i8(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+              // +32 bytes along K inside the swizzle atom = +2 in the encoded address (32 int8
+              // or 16 f16 elements: one instruction's K either way)
+              if (EPI == kEpiF16) umma_f16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+              else umma_i8(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
             }
             umma_commit(&empty_bar[stage]);
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -312,7 +316,18 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           uint32_t v[32];
           tmem_ld32(tmem_base + lane_addr + buf * BN + cc * 32, v);
           tmem_ld_wait();
-          if (EPI == kEpiModI8) {
+          if (EPI == kEpiF16) {
+            // f32 accumulator -> f16 (round to nearest even) -> f64, as a GEMM with f16 output
+            // widened by the caller would give; the matrix is the caller's: guard its edges
+            double* dst = reinterpret_cast<double*>(out_plane) + elem0 + cc * 32;
+            const int col0 = it.tn * BN + cc * 32;
+            if (row < prm.out_rows) {
+#pragma unroll
+              for (int e = 0; e < 32; ++e)
+                if (col0 + e < prm.out_cols)
+                  dst[e] = static_cast<double>(__half2float(__float2half_rn(__uint_as_float(v[e]))));
+            }
+          } else if (EPI == kEpiModI8) {
             uint32_t o[8];
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
@@ -489,6 +504,8 @@ cudaError_t modgemm_set_attributes() {
   B200_SET(256, kEpiModI8)
   B200_SET(256, kEpiRawI32)
   B200_SET(256, kEpiMod256)
+  B200_SET(256, kEpiF16)
+  B200_SET(128, kEpiF16)
   B200_SET(128, kEpiModI8)
   B200_SET(128, kEpiRawI32)
   B200_SET(128, kEpiMod256)
@@ -503,7 +520,9 @@ cudaError_t launch_modgemm(int bn, int epi, const CUtensorMap& tmA, const CUtens
     if (epi == kEpiModI8) return launch_one<256, kEpiModI8>(tmA, tmB, prm, total_work, num_sms, stream);
     if (epi == kEpiRawI32) return launch_one<256, kEpiRawI32>(tmA, tmB, prm, total_work, num_sms, stream);
     if (epi == kEpiMod256) return launch_one<256, kEpiMod256>(tmA, tmB, prm, total_work, num_sms, stream);
+    if (epi == kEpiF16) return launch_one<256, kEpiF16>(tmA, tmB, prm, total_work, num_sms, stream);
   } else if (bn == 128) {
+    if (epi == kEpiF16) return launch_one<128, kEpiF16>(tmA, tmB, prm, total_work, num_sms, stream);
     if (epi == kEpiModI8) return launch_one<128, kEpiModI8>(tmA, tmB, prm, total_work, num_sms, stream);
     if (epi == kEpiRawI32) return launch_one<128, kEpiRawI32>(tmA, tmB, prm, total_work, num_sms, stream);
     if (epi == kEpiMod256) return launch_one<128, kEpiMod256>(tmA, tmB, prm, total_work, num_sms, stream);

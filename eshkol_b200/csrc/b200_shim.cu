@@ -1080,6 +1080,29 @@ int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, 
                          static_cast<long long>(N), o);
 }
 
+int eshkol_b200_gemm_f16_device(const double* dA, const double* dB, double* dC, uint64_t batch,
+                                uint64_t M, uint64_t K, uint64_t N) {
+  if (!g.ready) {
+    fprintf(stderr, "[eshkol-b200] gemm called before eshkol_b200_init succeeded\n");
+    return -1;
+  }
+  if (!dA || !dB || !dC) return -1;
+  g.last.valid = false;
+  g.prepA.valid = false;
+  return f16_gemm(dA, dB, dC, static_cast<long long>(batch), static_cast<long long>(M),
+                  static_cast<long long>(K), static_cast<long long>(N));
+}
+
+int eshkol_b200_gemm_f32_device(const float* dA, const float* dB, float* dC, uint64_t M, uint64_t K,
+                                uint64_t N) {
+  if (!g.ready) {
+    fprintf(stderr, "[eshkol-b200] gemm called before eshkol_b200_init succeeded\n");
+    return -1;
+  }
+  if (!dA || !dB || !dC) return -1;
+  return f32_gemm(dA, dB, dC, static_cast<long long>(M), static_cast<long long>(K), static_cast<long long>(N));
+}
+
 int eshkol_b200_matmul_backward_f64_host(const double* grad_out, const double* A, const double* B,
                                          double* grad_A, double* grad_B, uint64_t M, uint64_t K,
                                          uint64_t N, const EshkolB200GemmOpts* opts_grad_a,

@@ -24,6 +24,9 @@
 #include "b200_residue.cuh"
 #include "b200_tiers.h"
 
+#include <cuda_fp16.h>
+#include <vector>
+
 namespace b200 {
 
 #define TIER_CHECK(call)                                                               \
@@ -460,6 +463,139 @@ __global__ void __launch_bounds__(256) elementwise_kernel(const double* __restri
 }
 
 }  // namespace
+
+// ------------------------------------------------------------ f16 tier (dtype fast path)
+namespace {
+// f64 -> f32 -> f16, two roundings to nearest even as the reference's host loop does
+// (lib/backend/gpu/gpu_memory_cuda.cpp:691-692: __float2half((float)x))
+__device__ __forceinline__ __half to_half_like_reference(double x) {
+  return __float2half_rn(static_cast<float>(x));
+}
+
+// rows x K f64 row-major -> rows x Kp halves (zero padding up to the 64-element k-block)
+__global__ void __launch_bounds__(256) f16_rows_kernel(const double* __restrict__ A, long long K, long long Kp,
+                                                       __half* __restrict__ out) {
+  const long long i = blockIdx.x;
+  const long long k2 = (static_cast<long long>(blockIdx.y) * 256 + threadIdx.x) * 2;
+  if (k2 >= Kp) return;
+  const double* a = A + i * K;
+  const __half h0 = (k2 < K) ? to_half_like_reference(a[k2]) : __float2half_rn(0.f);
+  const __half h1 = (k2 + 1 < K) ? to_half_like_reference(a[k2 + 1]) : __float2half_rn(0.f);
+  *reinterpret_cast<__half2*>(out + i * Kp + k2) = __halves2half2(h0, h1);
+}
+
+// K x N f64 row-major -> N x Kp halves (transposed: the products kernel wants both operands K-major)
+__global__ void __launch_bounds__(256) f16_cols_kernel(const double* __restrict__ B, long long K, long long N,
+                                                       long long Kp, __half* __restrict__ out) {
+  __shared__ __half tile[64][66];  // [k][j], pitch 66 halves: conflict-free column reads
+  const long long j0 = static_cast<long long>(blockIdx.x) * 64, k0 = static_cast<long long>(blockIdx.y) * 64;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;  // 64 x 4
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    const long long k = k0 + ty + 4 * r, j = j0 + tx;
+    tile[ty + 4 * r][tx] = (k < K && j < N) ? to_half_like_reference(B[k * N + j]) : __float2half_rn(0.f);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < 16; ++r) {
+    const long long j = j0 + ty + 4 * r, k = k0 + tx;
+    if (j < N && k < Kp) out[j * Kp + k] = tile[tx][ty + 4 * r];
+  }
+}
+
+__global__ void __launch_bounds__(256) widen_f32_kernel(const float* __restrict__ in, long long n, double* __restrict__ out) {
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (i < n) out[i] = static_cast<double>(in[i]);
+}
+__global__ void __launch_bounds__(256) narrow_f32_kernel(const double* __restrict__ in, long long n, float* __restrict__ out) {
+  const long long i = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (i < n) out[i] = static_cast<float>(in[i]);
+}
+}  // namespace
+
+// C[b] = half(A[b]) * half(B[b]) for b < batch, f32 accumulation on the tensor cores, the
+// result rounded to f16 and widened: what cublasGemmEx(16F, 16F, 16F out, COMPUTE_32F) followed
+// by the host widening gives in the reference (gpu_memory_cuda.cpp:677-784), up to the order
+// of the f32 accumulation.  One launch covers the whole batch (one job per matrix).
+int f16_gemm(const double* dA, const double* dB, double* dC, long long batch, long long M, long long K,
+             long long N) {
+  if (batch <= 0 || M <= 0 || K <= 0 || N <= 0) return -1;
+  const int bn = 256;
+  const long long Kp = round_up_ll(K, 64);  // halves; 128-byte k-blocks
+  const int tiles_m = static_cast<int>((M + kBM - 1) / kBM), tiles_n = static_cast<int>((N + bn - 1) / bn);
+  if (static_cast<long long>(tiles_m) * tiles_n * batch > 0x7fffffffLL || M > 0x7fffff00LL || N > 0x7fffff00LL)
+    return -1;
+  Carver cv;
+  const size_t a_stride = static_cast<size_t>(M) * Kp * 2, b_stride = static_cast<size_t>(N) * Kp * 2;
+  const size_t o_jobs = cv.take(sizeof(GemmJob) * batch);
+  const size_t o_a = cv.take(a_stride * batch), o_b = cv.take(b_stride * batch);
+  uint8_t* ws = workspace_reserve(cv.off);
+  if (!ws) return -1;
+  GemmJob* d_jobs = reinterpret_cast<GemmJob*>(ws + o_jobs);
+  __half* ap = reinterpret_cast<__half*>(ws + o_a);
+  __half* bp = reinterpret_cast<__half*>(ws + o_b);
+  cudaStream_t st = lib_stream();
+  if ((Kp / 2 + 255) / 256 > 65535 || (Kp + 63) / 64 > 65535) return -1;
+  for (long long b = 0; b < batch; ++b) {
+    const dim3 ga(static_cast<unsigned>(M), static_cast<unsigned>((Kp / 2 + 255) / 256));
+    f16_rows_kernel<<<ga, 256, 0, st>>>(dA + b * M * K, K, Kp, ap + b * M * Kp);
+    const dim3 gb(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((Kp + 63) / 64));
+    f16_cols_kernel<<<gb, 256, 0, st>>>(dB + b * K * N, K, N, Kp, bp + b * N * Kp);
+  }
+  TIER_CHECK(cudaGetLastError());
+  std::vector<GemmJob> jobs(static_cast<size_t>(batch));
+  for (long long b = 0; b < batch; ++b) {
+    memset(&jobs[b], 0, sizeof(GemmJob));
+    jobs[b].n_seg = 1;
+    jobs[b].a_plane[0] = static_cast<int>(b); jobs[b].b_plane[0] = static_cast<int>(b);
+    jobs[b].out_plane = static_cast<int>(b);
+  }
+  TIER_CHECK(cudaMemcpyAsync(d_jobs, jobs.data(), sizeof(GemmJob) * jobs.size(), cudaMemcpyHostToDevice, st));
+  TIER_CHECK(cudaStreamSynchronize(st));  // the job table above is host memory of this frame
+  GemmParams prm = make_gemm_params();
+  prm.tiles_m = tiles_m; prm.tiles_n = tiles_n; prm.n_jobs = static_cast<int>(batch);
+  prm.kb_per_seg = static_cast<int>(Kp * 2 / kBK);
+  prm.kb_per_unit = 1 << 28;
+  prm.group_m = 16;
+  prm.jobs = d_jobs;
+  prm.out = reinterpret_cast<uint8_t*>(dC);
+  prm.out_plane_stride = M * N * 8;
+  prm.ldo = static_cast<int>(N);
+  prm.out_rows = static_cast<int>(M); prm.out_cols = static_cast<int>(N);
+  prm.status = lib_status_word();
+  prm.work_counter = lib_status_word() + 1;
+  CUtensorMap mA, mB;
+  if (make_plane_map(&mA, ap, Kp * 2, M, batch, static_cast<long long>(a_stride), kBM)) return -1;
+  if (make_plane_map(&mB, bp, Kp * 2, N, batch, static_cast<long long>(b_stride), bn)) return -1;
+  TIER_CHECK(launch_modgemm(bn, kEpiF16, mA, mB, prm, static_cast<int>(tiles_m * tiles_n * batch), lib_num_sms(), st));
+  count_launches(static_cast<int>(2 * batch + 1));
+  return 0;
+}
+
+// f32 storage in and out (the reference runs cublasSgemm, gpu_memory_cuda.cpp:653-669): widened,
+// multiplied in the exact tier, narrowed with one rounding -- at least as accurate as an f32 GEMM.
+int f32_gemm(const float* dA, const float* dB, float* dC, long long M, long long K, long long N) {
+  if (M <= 0 || K <= 0 || N <= 0) return -1;
+  const size_t ba = (static_cast<size_t>(M) * K * 8 + 1023) & ~size_t(1023),
+               bb = (static_cast<size_t>(K) * N * 8 + 1023) & ~size_t(1023);
+  uint8_t* t = aux_reserve(ba + bb + static_cast<size_t>(M) * N * 8);
+  if (!t) return -1;
+  double* wA = reinterpret_cast<double*>(t);
+  double* wB = reinterpret_cast<double*>(t + ba);
+  double* wC = reinterpret_cast<double*>(t + ba + bb);
+  cudaStream_t st = lib_stream();
+  widen_f32_kernel<<<static_cast<unsigned>((M * K + 255) / 256), 256, 0, st>>>(dA, M * K, wA);
+  widen_f32_kernel<<<static_cast<unsigned>((K * N + 255) / 256), 256, 0, st>>>(dB, K * N, wB);
+  TIER_CHECK(cudaGetLastError());
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  o.tier = (K <= 131071) ? ESHKOL_B200_TIER_OZAKI2 : ESHKOL_B200_TIER_DGEMM;
+  if (eshkol_b200_gemm_f64_device(wA, wB, wC, M, K, N, &o) != 0) return -1;
+  narrow_f32_kernel<<<static_cast<unsigned>((M * N + 255) / 256), 256, 0, st>>>(wC, M * N, dC);
+  TIER_CHECK(cudaGetLastError());
+  count_launches(3);
+  return 0;
+}
 
 namespace {
 // 32 x 32 tiles through padded shared memory: both sides coalesced

@@ -31,6 +31,9 @@ int native_dgemm(const double* dA, const double* dB, double* dC, long long M, lo
 int conv2d_lowered(const double* d_in, long long batch, long long in_c, long long H, long long W,
                    const double* d_ker, long long out_c, long long kH, long long kW,
                    long long stride, long long pad, double* d_out, const EshkolB200GemmOpts& o);
+int f16_gemm(const double* dA, const double* dB, double* dC, long long batch, long long M, long long K,
+             long long N);
+int f32_gemm(const float* dA, const float* dB, float* dC, long long M, long long K, long long N);
 cudaError_t tiers_set_attributes();
 // dst[cols x rows] = transpose of src[rows x cols] (row-major f64)
 cudaError_t launch_transpose(const double* src, long long rows, long long cols, double* dst, cudaStream_t st);

@@ -312,9 +312,38 @@ int eshkol_gpu_matmul_f64(EshkolGPUBuffer* A, EshkolGPUBuffer* B, EshkolGPUBuffe
 
 int eshkol_gpu_matmul_f32(EshkolGPUBuffer* A, EshkolGPUBuffer* B, EshkolGPUBuffer* C,
                           uint64_t M, uint64_t K, uint64_t N) {
-  (void)A; (void)B; (void)C; (void)M; (void)K; (void)N;
-  /* f32 buffers never reach this backend from the f64 tensor runtime; not built */
-  return -1;
+  /* gpu_memory_cuda.cpp:653-669 (cublasSgemm on f32 buffers) */
+  if (!A || !B || !C) return -1;
+  if (g_backend != ESHKOL_GPU_CUDA) {
+    fprintf(stderr, "[GPU] eshkol_gpu_matmul_f32: no B200 backend is active\n");
+    return -1;
+  }
+  if (!A->device_ptr || !B->device_ptr || !C->device_ptr) return -1;
+  if (A->size_bytes < M * K * 4 || B->size_bytes < K * N * 4 || C->size_bytes < M * N * 4) return -1;
+  if (eshkol_b200_gemm_f32_device((const float*)A->device_ptr, (const float*)B->device_ptr,
+                                  (float*)C->device_ptr, M, K, N))
+    return -1;
+  if (C->flags & FLAG_WRAPPED) C->flags |= FLAG_DIRTY;
+  return eshkol_b200_sync_status() == 0 ? 0 : -1;
+}
+
+/* f16 / bf16-tagged operands (dtype 2 / 3, f64 storage): the tensor-core half-precision product,
+ * whatever the size (gpu_memory_cuda.cpp:1122-1131, :1170-1175).  0 on success. */
+static int gpu_matmul_f16_host(const double* a, const double* b, double* c, uint64_t batch, uint64_t M,
+                               uint64_t K, uint64_t N) {
+  const size_t ab = (size_t)(batch * M * K) * 8, bb = (size_t)(batch * K * N) * 8, cb = (size_t)(batch * M * N) * 8;
+  void *da = NULL, *db = NULL, *dc = NULL;
+  int rc = -1;
+  if (eshkol_b200_mem_alloc(0, ab, &da) == 0 && eshkol_b200_mem_alloc(0, bb, &db) == 0 &&
+      eshkol_b200_mem_alloc(0, cb, &dc) == 0 && eshkol_b200_copy_h2d(da, a, ab) == 0 &&
+      eshkol_b200_copy_h2d(db, b, bb) == 0 &&
+      eshkol_b200_gemm_f16_device((const double*)da, (const double*)db, (double*)dc, batch, M, K, N) == 0 &&
+      eshkol_b200_copy_d2h(c, dc, cb) == 0 && eshkol_b200_sync_status() == 0)
+    rc = 0;
+  if (da) eshkol_b200_mem_free(0, da);
+  if (db) eshkol_b200_mem_free(0, db);
+  if (dc) eshkol_b200_mem_free(0, dc);
+  return rc;
 }
 
 void eshkol_gpu_set_threshold(size_t threshold) { g_gpu_threshold = threshold; }
@@ -410,9 +439,16 @@ static int gpu_matmul_host(const double* A, const double* B, double* C, uint64_t
 
 void eshkol_matmul_dispatch(const double* A, const double* B, double* C, uint64_t M, uint64_t K,
                             uint64_t N, int32_t dtype) {
-  (void)dtype; /* f16 / bf16 tags keep f64 storage; the environment picks the tier */
   if (!A || !B || !C || M == 0 || K == 0 || N == 0) return;
   if (g_backend == ESHKOL_GPU_NONE) eshkol_gpu_init(); /* gpu_memory_cuda.cpp:1117-1119 */
+  if ((dtype == 2 || dtype == 3) && g_backend == ESHKOL_GPU_CUDA) {
+    /* the half-precision fast path bypasses the element threshold (gpu_memory_cuda.cpp:1122-1131);
+     * if it fails the f64 path below still produces C, as in the reference */
+    GPU_LOG("matmul %llux%llu @ %llux%llu -> f16 tensor-core path (dtype %d)", (unsigned long long)M,
+            (unsigned long long)K, (unsigned long long)K, (unsigned long long)N, (int)dtype);
+    if (gpu_matmul_f16_host(A, B, C, 1, M, K, N) == 0) return;
+    fprintf(stderr, "[GPU] eshkol_matmul_dispatch: the f16 path failed; continuing in f64\n");
+  }
   const size_t n_out = (size_t)(M * N);
   if (!eshkol_gpu_should_use(n_out) && eshkol_matmul_f64) {
     eshkol_matmul_f64(A, B, C, M, K, N); /* small shapes stay on the CPU: policy, not a fallback */
@@ -445,6 +481,12 @@ void eshkol_batch_matmul_dispatch(const double* a, const double* b, double* c, i
                                   int64_t M, int64_t K, int64_t N, int32_t dtype) {
   if (!a || !b || !c || batch <= 0 || M <= 0 || K <= 0 || N <= 0) return;
   if (g_backend == ESHKOL_GPU_NONE) eshkol_gpu_init();
+  if ((dtype == 2 || dtype == 3) && g_backend == ESHKOL_GPU_CUDA) {
+    /* one launch for the whole batch (gpu_memory_cuda.cpp:1170-1175) */
+    if (gpu_matmul_f16_host(a, b, c, (uint64_t)batch, (uint64_t)M, (uint64_t)K, (uint64_t)N) == 0) return;
+    fprintf(stderr, "[GPU] eshkol_batch_matmul_dispatch: the f16 path failed; continuing in f64\n");
+    dtype = 0;
+  }
   if (!eshkol_gpu_should_use((size_t)(M * N)) && eshkol_batch_matmul_f64) {
     eshkol_batch_matmul_f64(a, b, c, batch, M, K, N);
     return;

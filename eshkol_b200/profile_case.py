@@ -25,7 +25,8 @@ def main() -> None:
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--m", type=int, default=0)
     ap.add_argument("--k", type=int, default=0)
-    ap.add_argument("--tier", default="exact", choices=sorted(TIERS))
+    ap.add_argument("--tier", default="exact", choices=sorted(TIERS) + ["f16"],
+                    help="f16: the half-precision dtype path (f64 storage, f16 operands, f32 accumulation)")
     ap.add_argument("--param", type=int, default=0)
     ap.add_argument("--reps", type=int, default=3)
     ap.add_argument("--tile-n", type=int, default=0, choices=[0, 128, 256])
@@ -48,13 +49,17 @@ def main() -> None:
         lib.eshkol_b200_set_pair_gemm(args.pair)
     if args.band_rows >= 0:
         lib.eshkol_b200_set_row_bands(args.band_rows)
-    opts = api.make_opts(TIERS[args.tier], args.param, tile_n=args.tile_n)
+    opts = api.make_opts(TIERS.get(args.tier, 0), args.param, tile_n=args.tile_n)
     stream = torch.cuda.ExternalStream(api.stream_handle(), device=dev)
     out = {}
     for rep in range(args.reps):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        api.gemm_device(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, K, N, opts)
+        if args.tier == "f16":
+            if lib.eshkol_b200_gemm_f16_device(A.data_ptr(), B.data_ptr(), C.data_ptr(), 1, M, K, N) != 0:
+                raise RuntimeError("gemm_f16 failed")
+        else:
+            api.gemm_device(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, K, N, opts)
         e1.record(stream)
         if api.sync_status() != 0:
             raise RuntimeError("kernel status non-zero")

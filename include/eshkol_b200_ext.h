@@ -76,6 +76,24 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC,
                                 uint64_t M, uint64_t K, uint64_t N,
                                 const EshkolB200GemmOpts* opts);
 
+/* The dtype fast path (f16 / bf16-tagged tensors keep f64 storage): for b < batch,
+ * C[b][M x N] = f16(A[b]) * f16(B[b]) with f32 accumulation on the tensor cores
+ * (tcgen05.mma kind::f16), the result rounded to f16 and widened back to f64 -- the arithmetic of
+ * cuda_matmul_f16_from_f64 / cuda_batch_matmul_f16_from_f64
+ * (lib/backend/gpu/gpu_memory_cuda.cpp:677-784) up to the order of the f32 accumulation, with
+ * the f64 -> f32 -> f16 conversion (two roundings, as the reference's host loop) done on the
+ * device.  Matrices of a batch are contiguous; one kernel launch multiplies the whole batch.
+ * Device pointers; asynchronous.  Returns 0 / -1. */
+int eshkol_b200_gemm_f16_device(const double* dA, const double* dB, double* dC, uint64_t batch,
+                                uint64_t M, uint64_t K, uint64_t N);
+
+/* C = A * B on f32 matrices in device memory (the role of cuda_matmul_f32,
+ * gpu_memory_cuda.cpp:653-669): widened to f64, multiplied in the exact tier, narrowed with one
+ * rounding, so every element is the correctly rounded f32 of the exact-tier product.
+ * Asynchronous.  Returns 0 / -1. */
+int eshkol_b200_gemm_f32_device(const float* dA, const float* dB, float* dC, uint64_t M, uint64_t K,
+                                uint64_t N);
+
 /* Both gradients of C = A * B from host memory (the GPU branch of
  * eshkol_matmul_backward_f64, lib/backend/blas_backend.cpp:924-1012, without its host
  * transposes): grad_A[M x K] = grad_out[M x N] * B^T, grad_B[K x N] = A^T * grad_out, each

@@ -192,3 +192,89 @@ def test_k_beyond_int32_bound_is_refused_loudly(gpu_lib):
     torch.cuda.synchronize()
     rc = gpu_lib.eshkol_b200_gemm_f64_device(a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, 131072, 1, None)
     assert rc == -1
+
+
+def _f16_reference(A, B):
+    """The reference's dtype fast path restated on the CPU (lib/backend/gpu/gpu_memory_cuda.cpp:677-733):
+    operands rounded f64 -> f32 -> f16, product with wide accumulation, result rounded to f16.
+    Returns (half-rounded exact product, sum |a||b| of the rounded operands)."""
+    a = np.asarray(A, dtype=np.float64).astype(np.float32).astype(np.float16).astype(np.float64)
+    b = np.asarray(B, dtype=np.float64).astype(np.float32).astype(np.float16).astype(np.float64)
+    exact = a @ b  # products of halves are exact in f64; the f64 sum is exact to 2^-53 relative
+    return exact, np.abs(a) @ np.abs(b)
+
+
+def _check_f16(got, exact, mag, K):
+    # f32 accumulation in an unspecified order: |acc - exact| <= K * 2^-24 * sum|a||b| (first order);
+    # the final rounding to f16 adds half an f16 ulp of the accumulated value: 2^-11 relative
+    # (2^-25 absolute in the subnormal range)
+    acc_err = K * 2.0 ** -24 * mag
+    bound = acc_err + 2.0 ** -11 * (np.abs(exact) + acc_err) + 2.0 ** -25
+    assert np.all(np.isfinite(got))
+    assert np.all(np.abs(got - exact) <= bound)
+    # every output is an f16 value
+    assert np.array_equal(got, got.astype(np.float16).astype(np.float64))
+
+
+@pytest.mark.parametrize("shape", [(128, 64, 256), (300, 200, 130), (1, 1, 1), (513, 1000, 77), (1024, 4096, 512)])
+def test_f16_fast_path_device(gpu_lib, shape):
+    import torch
+    M, K, N = shape
+    A = inputs.uniform(301, (M, K))
+    B = inputs.uniform(302, (K, N))
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.full((M, N), float("nan"), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    assert gpu_lib.eshkol_b200_gemm_f16_device(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 1, M, K, N) == 0
+    assert api.sync_status() == 0
+    exact, mag = _f16_reference(A, B)
+    _check_f16(dC.cpu().numpy(), exact, mag, K)
+
+
+def test_f16_small_integers_are_exact(gpu_lib):
+    """Integers whose products and sums fit f16 / f32 exactly: the half-precision product has
+    no rounding anywhere, so the result equals the integer product."""
+    rng = np.random.default_rng(11)
+    A = rng.integers(-4, 5, (200, 96)).astype(np.float64)
+    B = rng.integers(-4, 5, (96, 144)).astype(np.float64)
+    C = eb.matmul_dispatch(A, B, dtype=2)
+    assert np.array_equal(C, A @ B)
+
+
+def test_f16_dtype_dispatch_and_batch(gpu_lib):
+    """dtype 2 / 3 on the dispatchers take the half-precision path whatever the size; the
+    batched dispatcher multiplies all matrices in one launch."""
+    A = inputs.uniform(303, (40, 50))
+    B = inputs.uniform(304, (50, 30))
+    for dtype in (2, 3):
+        C = eb.matmul_dispatch(A, B, dtype=dtype)
+        exact, mag = _f16_reference(A, B)
+        _check_f16(C, exact, mag, 50)
+    batch = 5
+    a = inputs.uniform(305, (batch, 70, 90))
+    b = inputs.uniform(306, (batch, 90, 33))
+    launches0 = api.launch_count()
+    c = eb.batch_matmul_dispatch(a, b, dtype=2)
+    assert api.launch_count() - launches0 == 2 * batch + 1  # conversions per matrix, one product launch
+    for i in range(batch):
+        exact, mag = _f16_reference(a[i], b[i])
+        _check_f16(c[i], exact, mag, 90)
+
+
+def test_f32_buffers(gpu_lib):
+    """eshkol_gpu_matmul_f32 on f32 device buffers: correctly rounded f32 of the exact-tier product."""
+    import ctypes
+    import torch
+    M, K, N = 150, 333, 90
+    A = inputs.uniform(307, (M, K)).astype(np.float32)
+    B = inputs.uniform(308, (K, N)).astype(np.float32)
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+    torch.cuda.synchronize()
+    assert gpu_lib.eshkol_b200_gemm_f32_device(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), M, K, N) == 0
+    assert api.sync_status() == 0
+    want = ol.oz2_exact(A.astype(np.float64), B.astype(np.float64), 52).astype(np.float32)
+    assert np.array_equal(dC.cpu().numpy(), want)
+    # and within an f32 GEMM's own error of the f64 product
+    ref = A.astype(np.float64) @ B.astype(np.float64)
+    assert np.all(np.abs(dC.cpu().numpy() - ref) <= 2.0 ** -23 * (np.abs(A).astype(np.float64) @ np.abs(B)))
