@@ -221,6 +221,7 @@ class ShardedGemm:
         self._ev_block = make_events(P)    # this rank's block of C, panel p, is computed
         self._x1 = torch.cuda.Stream(self.device)
         self._x2 = torch.cuda.Stream(self.device)
+        self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(min(4, max(1, W - 1)))]
         self._k_parts = row_partition(self.K, W)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.ctl)
@@ -259,7 +260,7 @@ class ShardedGemm:
             self._side = torch.cuda.Stream(self.device)
         x1, x2, xo = self._x1, self._x2, self._side
         self._mark("start", cur)
-        for st in (x1, x2, xo):
+        for st in (x1, x2, xo, *self._pull_streams):
             st.wait_stream(cur)
         if self.rows:
             lib.wait_stream(cur)
@@ -315,14 +316,20 @@ class ShardedGemm:
                 self._mark(f"panel {p} products done", lib)
             self._record(self._ev_block[R][p], lib)
         dist.barrier(group=self.ctl)
-        # C: pull every other rank's block of a panel, straight into its place in C, once computed
+        # C: pull every other rank's block of a panel, straight into its place in C, once computed;
+        # the pulls of a panel are spread over a few streams so that several copy engines work
+        # at once (one 2-D pull alone runs far below the link rate)
+        pool = self._pull_streams
         for p in range(P):
             for i in range(1, W):
                 q = (R + i) % W
                 if self.parts[q][1] == 0:
                     continue
-                self._wait(self._ev_block[q][p], xo)
-                self._pull_c_block(q, p, xo)
+                st = pool[i % len(pool)]
+                self._wait(self._ev_block[q][p], st)
+                self._pull_c_block(q, p, st)
+            for st in pool:
+                xo.wait_stream(st)
             self._mark(f"panel {p} gathered", xo)
         cur.wait_stream(lib)
         cur.wait_stream(xo)
