@@ -95,10 +95,16 @@ class ShardedGemm:
     """Buffers and schedule of one sharded product C = A @ B with A row-sharded.
 
     B travels in `panels` column panels (contiguous K x N/panels blocks packed on the
-    source rank): all broadcasts are enqueued at once, each panel is multiplied as soon
-    as it has arrived, and its block of C is all-gathered while the next panel is being
-    multiplied, so only the first broadcast and the last gather are exposed.  All
-    buffers are allocated once; step() allocates nothing.
+    source rank): every panel's transfer is enqueued at once, each panel is multiplied as soon
+    as it has arrived, and its block of C travels to the other ranks while the next panel is
+    being multiplied, so only the first panel's way out and the last one's way back are
+    exposed.  All buffers are allocated once; step() allocates nothing.
+
+    transport: "collectives" moves the panels with torch.distributed (broadcast, all-gather:
+    NCCL on GPUs, gloo in the CPU tests); "copy_engine" (GPUs only) with the library's copy
+    engine entry points over CUDA IPC, which run beside the products kernels where a
+    collective's kernel has to wait for the gaps between them.  If the peers' memory cannot
+    be opened the constructor says so and falls back to the collectives on every rank.
 
     comm_sms: SMs the products kernels leave free for the collectives.  A products CTA fills
     its SM's shared memory, so a collective's kernel launched beside them would otherwise
@@ -130,9 +136,20 @@ class ShardedGemm:
         if transport == "copy_engine" and self.world > 1 and self.backend.on_device:
             # the panel buffer of B and C itself are library allocations the peers open; products
             # write their block of C in place and the peers pull it from there
-            self._open_peers()
-            self.transport = "copy_engine"
-        else:
+            import datetime
+            import sys
+            self.ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=180))
+            try:
+                self._open_peers()
+                opened = 1
+            except RuntimeError as exc:
+                sys.stderr.write(f"[eshkol-b200] rank {self.rank}: copy-engine transport unavailable ({exc})\n")
+                opened = 0
+            agreed = torch.tensor([opened], dtype=torch.int32)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=self.ctl)
+            if int(agreed.item()) == 1:
+                self.transport = "copy_engine"
+        if self.transport != "copy_engine":
             # panel-major copy of B: panel p is the contiguous K x width block of columns p*width ...
             self.Bp = torch.empty((self.panels, K, self.width), dtype=torch.float64, device=self.device)
             self.C = torch.empty((M, N), dtype=torch.float64, device=self.device)
@@ -168,11 +185,22 @@ class ShardedGemm:
         opened in the rank's own context) and its hand-off events (interprocess events).  Data
         then moves by copy-engine pulls over NVLink, ordered on the device by those events; a
         gloo barrier only makes sure an event's record has been *called* before a peer calls
-        wait on it (the host runs far ahead of the device)."""
-        import datetime
+        wait on it (the host runs far ahead of the device).
+
+        Every rank takes part in every exchange whatever failed locally (a rank that stopped
+        half-way would leave the others waiting); the first failure is raised at the end."""
         lib = self.backend.lib
-        self.ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=180))
         W, R, P = self.world, self.rank, self.panels
+        failure = []
+
+        def attempt(fn, *args):
+            if failure:
+                return None
+            try:
+                return fn(*args)
+            except RuntimeError as exc:
+                failure.append(str(exc))
+                return None
 
         def exchange(obj):
             objs = [None] * W
@@ -181,50 +209,71 @@ class ShardedGemm:
 
         def import_mem(handle: bytes) -> int:
             out = ctypes.c_void_p()
-            if lib.eshkol_b200_ipc_import_mem(handle, ctypes.byref(out)) != 0:
-                raise RuntimeError("ipc_import_mem failed (no peer access between the GPUs?)")
+            if handle is None or lib.eshkol_b200_ipc_import_mem(handle, ctypes.byref(out)) != 0:
+                raise RuntimeError("a peer's memory could not be opened (no peer access between the GPUs?)")
             return out.value
 
-        self._blk_B = self._DeviceBlock(lib, (P, self.K, self.width), self.device)
-        self._blk_C = self._DeviceBlock(lib, (self.M, self.N), self.device)
-        self.Bp, self.C = self._blk_B.tensor, self._blk_C.tensor
-        hs = exchange((self._blk_B.handle(), self._blk_C.handle()))
-        # base addresses of every rank's Bp and C in this process (own rank: the local pointer)
-        self._addr_B = [self._blk_B.ptr if q == R else import_mem(hs[q][0]) for q in range(W)]
-        self._addr_C = [self._blk_C.ptr if q == R else import_mem(hs[q][1]) for q in range(W)]
+        def make_blocks():
+            self._blk_B = self._DeviceBlock(lib, (P, self.K, self.width), self.device)
+            self._blk_C = self._DeviceBlock(lib, (self.M, self.N), self.device)
+            return (self._blk_B.handle(), self._blk_C.handle())
 
-        def make_events(n: int):
-            mine, handles = [], []
+        mine = attempt(make_blocks)
+        hs = exchange(mine)
+        # base addresses of every rank's Bp and C in this process (own rank: the local pointer)
+        self._addr_B = [None] * W
+        self._addr_C = [None] * W
+        for q in range(W):
+            if q == R:
+                if mine is not None:
+                    self._addr_B[q], self._addr_C[q] = self._blk_B.ptr, self._blk_C.ptr
+            elif hs[q] is None:
+                failure.append(f"rank {q} exported nothing")
+            else:
+                self._addr_B[q] = attempt(import_mem, hs[q][0])
+                self._addr_C[q] = attempt(import_mem, hs[q][1])
+
+        def create_events(n: int):
+            evs, handles = [], []
             for _ in range(n):
                 ev, buf = ctypes.c_void_p(), ctypes.create_string_buffer(64)
                 if lib.eshkol_b200_ipc_event_create(ctypes.byref(ev), buf) != 0:
-                    raise RuntimeError("ipc_event_create failed")
-                mine.append(ev.value)
+                    raise RuntimeError("an interprocess event could not be created")
+                evs.append(ev.value)
                 handles.append(buf.raw)
-            theirs = exchange(handles)
+            return evs, handles
+
+        def import_event(h: bytes) -> int:
+            ev = ctypes.c_void_p()
+            if lib.eshkol_b200_ipc_event_import(h, ctypes.byref(ev)) != 0:
+                raise RuntimeError("a peer's event could not be opened")
+            return ev.value
+
+        def make_events(n: int):
+            made = attempt(create_events, n)
+            theirs = exchange(None if made is None else made[1])
             table = []
             for q in range(W):
                 if q == R:
-                    table.append(mine)
-                    continue
-                row = []
-                for h in theirs[q]:
-                    ev = ctypes.c_void_p()
-                    if lib.eshkol_b200_ipc_event_import(h, ctypes.byref(ev)) != 0:
-                        raise RuntimeError("ipc_event_import failed")
-                    row.append(ev.value)
-                table.append(row)
+                    table.append(None if made is None else made[0])
+                elif theirs[q] is None:
+                    failure.append(f"rank {q} exported no events")
+                    table.append(None)
+                else:
+                    table.append([attempt(import_event, h) for h in theirs[q]])
             return table
 
         self._ev_packed = make_events(P)   # on the source rank: panel p packed
         self._ev_slice = make_events(P)    # this rank's K-slice of panel p is in its Bp
         self._ev_block = make_events(P)    # this rank's block of C, panel p, is computed
+        if failure:
+            raise RuntimeError(failure[0])
+        self.Bp, self.C = self._blk_B.tensor, self._blk_C.tensor
         self._x1 = torch.cuda.Stream(self.device)
         self._x2 = torch.cuda.Stream(self.device)
         self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(min(4, max(1, W - 1)))]
         self._k_parts = row_partition(self.K, W)
         torch.cuda.synchronize(self.device)
-        dist.barrier(group=self.ctl)
 
     def _record(self, ev: int, stream) -> None:
         if self.backend.lib.eshkol_b200_event_record(ev, stream.cuda_stream) != 0:

@@ -278,3 +278,32 @@ def test_f32_buffers(gpu_lib):
     # and within an f32 GEMM's own error of the f64 product
     ref = A.astype(np.float64) @ B.astype(np.float64)
     assert np.all(np.abs(dC.cpu().numpy() - ref) <= 2.0 ** -23 * (np.abs(A).astype(np.float64) @ np.abs(B)))
+
+
+def test_copy_engine_entry_points_on_one_gpu(gpu_lib):
+    """copy_async / copy2d_async / interprocess events, as far as one process can exercise them:
+    the copies land, a recorded event orders a second stream, the handles have 64 bytes."""
+    import torch
+    lib = gpu_lib
+    src = torch.arange(6 * 1024, dtype=torch.float64, device="cuda").reshape(6, 1024)
+    dst = torch.zeros((6, 1024), dtype=torch.float64, device="cuda")
+    pan = torch.zeros((6, 256), dtype=torch.float64, device="cuda")
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    ev, buf = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+    assert lib.eshkol_b200_ipc_event_create(ctypes.byref(ev), buf) == 0 and len(buf.raw) == 64
+    assert lib.eshkol_b200_copy_async(dst.data_ptr(), src.data_ptr(), src.numel() * 8, s1.cuda_stream) == 0
+    assert lib.eshkol_b200_event_record(ev, s1.cuda_stream) == 0
+    assert lib.eshkol_b200_event_wait(ev, s2.cuda_stream) == 0
+    # columns 512..767 of the copy, as a contiguous panel, on the stream that waited
+    assert lib.eshkol_b200_copy2d_async(pan.data_ptr(), 256 * 8, dst.data_ptr() + 512 * 8, 1024 * 8,
+                                        256 * 8, 6, s2.cuda_stream) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dst, src) and torch.equal(pan, src[:, 512:768])
+    assert lib.eshkol_b200_event_destroy(ev) == 0
+    blk = ctypes.c_void_p()
+    assert lib.eshkol_b200_mem_alloc(0, 1 << 20, ctypes.byref(blk)) == 0
+    hbuf = ctypes.create_string_buffer(64)
+    assert lib.eshkol_b200_ipc_export_mem(blk, hbuf) == 0 and any(hbuf.raw)
+    lib.eshkol_b200_mem_free(0, blk)
+    assert lib.eshkol_b200_enable_peer_access(torch.cuda.current_device()) == 0  # own device: nothing to do
