@@ -322,10 +322,27 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             double* dst = reinterpret_cast<double*>(out_plane) + elem0 + cc * 32;
             const int col0 = it.tn * BN + cc * 32;
             if (row < prm.out_rows) {
+              if (col0 + 32 <= prm.out_cols && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+                // whole 32-byte sectors: four doubles per store
 #pragma unroll
-              for (int e = 0; e < 32; ++e)
-                if (col0 + e < prm.out_cols)
-                  dst[e] = static_cast<double>(__half2float(__float2half_rn(__uint_as_float(v[e]))));
+                for (int g = 0; g < 8; ++g) {
+                  double d[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e)
+                    d[e] = static_cast<double>(__half2float(__float2half_rn(__uint_as_float(v[g * 4 + e]))));
+                  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + g * 4),
+                               "f"(__int_as_float(__double2loint(d[0]))), "f"(__int_as_float(__double2hiint(d[0]))),
+                               "f"(__int_as_float(__double2loint(d[1]))), "f"(__int_as_float(__double2hiint(d[1]))),
+                               "f"(__int_as_float(__double2loint(d[2]))), "f"(__int_as_float(__double2hiint(d[2]))),
+                               "f"(__int_as_float(__double2loint(d[3]))), "f"(__int_as_float(__double2hiint(d[3])))
+                               : "memory");
+                }
+              } else {
+#pragma unroll
+                for (int e = 0; e < 32; ++e)
+                  if (col0 + e < prm.out_cols)
+                    dst[e] = static_cast<double>(__half2float(__float2half_rn(__uint_as_float(v[e]))));
+              }
             }
           } else if (EPI == kEpiModI8) {
             uint32_t o[8];

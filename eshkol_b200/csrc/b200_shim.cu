@@ -1080,6 +1080,34 @@ int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, 
                          static_cast<long long>(N), o);
 }
 
+int eshkol_b200_conv2d_backward_kernel_f64_device(const double* d_grad_out, const double* d_input,
+                                                  double* d_grad_kernel, uint64_t in_h, uint64_t in_w,
+                                                  uint64_t k_h, uint64_t k_w, uint64_t out_h, uint64_t out_w,
+                                                  uint64_t stride_h, uint64_t stride_w, uint64_t channels_in,
+                                                  uint64_t channels_out, uint64_t batch,
+                                                  const EshkolB200GemmOpts* opts) {
+  if (!g.ready || !d_grad_out || !d_input || !d_grad_kernel) return -1;
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  if (opts) { o.tier = opts->tier; o.param = opts->param; }
+  return conv2d_backward_kernel(d_grad_out, d_input, d_grad_kernel, in_h, in_w, k_h, k_w, out_h, out_w, stride_h,
+                                stride_w, channels_in, channels_out, batch, o);
+}
+
+int eshkol_b200_conv2d_backward_input_f64_device(const double* d_grad_out, const double* d_weights,
+                                                 double* d_grad_input, uint64_t in_h, uint64_t in_w,
+                                                 uint64_t k_h, uint64_t k_w, uint64_t out_h, uint64_t out_w,
+                                                 uint64_t stride_h, uint64_t stride_w, uint64_t channels_in,
+                                                 uint64_t channels_out, uint64_t batch,
+                                                 const EshkolB200GemmOpts* opts) {
+  if (!g.ready || !d_grad_out || !d_weights || !d_grad_input) return -1;
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  if (opts) { o.tier = opts->tier; o.param = opts->param; }
+  return conv2d_backward_input(d_grad_out, d_weights, d_grad_input, in_h, in_w, k_h, k_w, out_h, out_w, stride_h,
+                               stride_w, channels_in, channels_out, batch, o);
+}
+
 int eshkol_b200_gemm_f16_device(const double* dA, const double* dB, double* dC, uint64_t batch,
                                 uint64_t M, uint64_t K, uint64_t N) {
   if (!g.ready) {

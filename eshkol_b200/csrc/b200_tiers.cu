@@ -902,4 +902,119 @@ int conv2d_lowered(const double* d_in, long long batch, long long in_c, long lon
                                      static_cast<uint64_t>(Kc), static_cast<uint64_t>(ncol), &o);
 }
 
+// ------------------------------------------------------------ conv2d backward
+namespace {
+// G[b][c][pix] (NCHW) -> Gm[c][b*pix + pix]: rows of the GEMM operand are channels
+__global__ void __launch_bounds__(256) nchw_to_channel_rows_kernel(const double* __restrict__ g, long long batch,
+                                                                   long long C, long long pix,
+                                                                   double* __restrict__ out) {
+  const long long n = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  const long long c = blockIdx.y;
+  if (n >= batch * pix) return;
+  const long long b = n / pix, p = n - b * pix;
+  out[c * batch * pix + n] = __ldg(g + (b * C + c) * pix + p);
+}
+
+// col[kk][n], kk = (ci*kH + kh)*kW + kw, n = (b*oH + oh)*oW + ow; no padding, separate strides
+__global__ void __launch_bounds__(256) im2col_strides_kernel(const double* __restrict__ in, long long batch,
+                                                             long long C, long long H, long long W, long long kH,
+                                                             long long kW, long long sH, long long sW,
+                                                             long long oH, long long oW, double* __restrict__ col) {
+  const long long ncol = batch * oH * oW;
+  const long long n = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  const long long kk = blockIdx.y;
+  if (n >= ncol) return;
+  const long long kw = kk % kW, kh = (kk / kW) % kH, ci = kk / (kW * kH);
+  const long long ow = n % oW, oh = (n / oW) % oH, b = n / (oW * oH);
+  const long long ih = oh * sH + kh, iw = ow * sW + kw;
+  col[kk * ncol + n] = (ih < H && iw < W) ? __ldg(in + ((b * C + ci) * H + ih) * W + iw) : 0.0;
+}
+
+// gX[b][ci][ih][iw] = sum over kh, kw (kh outer, as the reference's loop) of Z[(ci,kh,kw)][(b,oh,ow)]
+// for the output pixels (oh, ow) = ((ih-kh)/sH, (iw-kw)/sW) that exist: a gather, no atomics
+__global__ void __launch_bounds__(256) col2im_gather_kernel(const double* __restrict__ Z, long long batch,
+                                                            long long C, long long H, long long W, long long kH,
+                                                            long long kW, long long sH, long long sW, long long oH,
+                                                            long long oW, double* __restrict__ gx) {
+  const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (idx >= batch * C * H * W) return;
+  const long long iw = idx % W, ih = (idx / W) % H, ci = (idx / (W * H)) % C, b = idx / (W * H * C);
+  const long long ncol = batch * oH * oW;
+  double sum = 0.0;
+  for (long long kh = 0; kh < kH; ++kh) {
+    const long long oh_c = ih - kh;
+    if (oh_c < 0 || oh_c % sH != 0 || oh_c / sH >= oH) continue;
+    for (long long kw = 0; kw < kW; ++kw) {
+      const long long ow_c = iw - kw;
+      if (ow_c < 0 || ow_c % sW != 0 || ow_c / sW >= oW) continue;
+      sum = __dadd_rn(sum, __ldg(Z + ((ci * kH + kh) * kW + kw) * ncol + (b * oH + oh_c / sH) * oW + ow_c / sW));
+    }
+  }
+  gx[idx] = sum;
+}
+}  // namespace
+
+// grad_kernel[co][ci][kh][kw] = sum over (b, oh, ow) of G[b][co][oh][ow] * X[b][ci][oh*sH+kh][ow*sW+kw]
+// (lib/backend/gpu/gpu_cuda_kernels.cu:451-486) as one GEMM: (co x b*pix) times im2col(X)^T, the
+// im2col matrix read in its own (kk x b*pix) storage.
+int conv2d_backward_kernel(const double* d_gout, const double* d_in, double* d_gker, long long H, long long W,
+                           long long kH, long long kW, long long oH, long long oW, long long sH, long long sW,
+                           long long C_in, long long C_out, long long batch, const EshkolB200GemmOpts& o_in) {
+  if (H <= 0 || W <= 0 || kH <= 0 || kW <= 0 || oH <= 0 || oW <= 0 || sH <= 0 || sW <= 0 || C_in <= 0 ||
+      C_out <= 0 || batch <= 0)
+    return -1;
+  const long long Kc = C_in * kH * kW, ncol = batch * oH * oW;
+  if (Kc > 65535 || C_out > 65535) return -1;
+  const size_t bg = (static_cast<size_t>(C_out) * ncol * 8 + 1023) & ~size_t(1023);
+  uint8_t* base = aux_reserve(bg + static_cast<size_t>(Kc) * ncol * 8);
+  if (!base) return -1;
+  double* gm = reinterpret_cast<double*>(base);
+  double* col = reinterpret_cast<double*>(base + bg);
+  cudaStream_t st = lib_stream();
+  const unsigned gx = static_cast<unsigned>((ncol + 255) / 256);
+  nchw_to_channel_rows_kernel<<<dim3(gx, static_cast<unsigned>(C_out)), 256, 0, st>>>(d_gout, batch, C_out, oH * oW, gm);
+  im2col_strides_kernel<<<dim3(gx, static_cast<unsigned>(Kc)), 256, 0, st>>>(d_in, batch, C_in, H, W, kH, kW, sH, sW,
+                                                                             oH, oW, col);
+  TIER_CHECK(cudaGetLastError());
+  count_launches(2);
+  EshkolB200GemmOpts o = o_in;
+  o.trans_a = 0; o.trans_b = 1;
+  o.bias = nullptr; o.bias_mode = 0; o.activation = 0; o.pixels_per_image = 0; o.ldc = 0;
+  return eshkol_b200_gemm_f64_device(gm, col, d_gker, static_cast<uint64_t>(C_out), static_cast<uint64_t>(ncol),
+                                     static_cast<uint64_t>(Kc), &o);
+}
+
+// grad_input (gpu_cuda_kernels.cu:413-449): Z = W^T (kk x co) * G (co x b*pix) as one GEMM with W read
+// in its own (co x kk) storage, then the gather above.
+int conv2d_backward_input(const double* d_gout, const double* d_ker, double* d_gin, long long H, long long W,
+                          long long kH, long long kW, long long oH, long long oW, long long sH, long long sW,
+                          long long C_in, long long C_out, long long batch, const EshkolB200GemmOpts& o_in) {
+  if (H <= 0 || W <= 0 || kH <= 0 || kW <= 0 || oH <= 0 || oW <= 0 || sH <= 0 || sW <= 0 || C_in <= 0 ||
+      C_out <= 0 || batch <= 0)
+    return -1;
+  const long long Kc = C_in * kH * kW, ncol = batch * oH * oW;
+  if (C_out > 65535) return -1;
+  const size_t bg = (static_cast<size_t>(C_out) * ncol * 8 + 1023) & ~size_t(1023);
+  uint8_t* base = aux_reserve(bg + static_cast<size_t>(Kc) * ncol * 8);
+  if (!base) return -1;
+  double* gm = reinterpret_cast<double*>(base);
+  double* Z = reinterpret_cast<double*>(base + bg);
+  cudaStream_t st = lib_stream();
+  nchw_to_channel_rows_kernel<<<dim3(static_cast<unsigned>((ncol + 255) / 256), static_cast<unsigned>(C_out)), 256, 0,
+                                st>>>(d_gout, batch, C_out, oH * oW, gm);
+  TIER_CHECK(cudaGetLastError());
+  EshkolB200GemmOpts o = o_in;
+  o.trans_a = 1; o.trans_b = 0;
+  o.bias = nullptr; o.bias_mode = 0; o.activation = 0; o.pixels_per_image = 0; o.ldc = 0;
+  if (eshkol_b200_gemm_f64_device(d_ker, gm, Z, static_cast<uint64_t>(Kc), static_cast<uint64_t>(C_out),
+                                  static_cast<uint64_t>(ncol), &o) != 0)
+    return -1;
+  const long long total = batch * C_in * H * W;
+  col2im_gather_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(Z, batch, C_in, H, W, kH, kW, sH,
+                                                                                   sW, oH, oW, d_gin);
+  TIER_CHECK(cudaGetLastError());
+  count_launches(2);
+  return 0;
+}
+
 }  // namespace b200

@@ -31,6 +31,12 @@ int native_dgemm(const double* dA, const double* dB, double* dC, long long M, lo
 int conv2d_lowered(const double* d_in, long long batch, long long in_c, long long H, long long W,
                    const double* d_ker, long long out_c, long long kH, long long kW,
                    long long stride, long long pad, double* d_out, const EshkolB200GemmOpts& o);
+int conv2d_backward_kernel(const double* d_gout, const double* d_in, double* d_gker, long long H, long long W,
+                           long long kH, long long kW, long long oH, long long oW, long long sH, long long sW,
+                           long long C_in, long long C_out, long long batch, const EshkolB200GemmOpts& o);
+int conv2d_backward_input(const double* d_gout, const double* d_ker, double* d_gin, long long H, long long W,
+                          long long kH, long long kW, long long oH, long long oW, long long sH, long long sW,
+                          long long C_in, long long C_out, long long batch, const EshkolB200GemmOpts& o);
 int f16_gemm(const double* dA, const double* dB, double* dC, long long batch, long long M, long long K,
              long long N);
 int f32_gemm(const float* dA, const float* dB, float* dC, long long M, long long K, long long N);

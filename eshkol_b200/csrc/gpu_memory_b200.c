@@ -383,17 +383,45 @@ int eshkol_gpu_normalize_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t
   (void)in; (void)out; (void)num_slices; (void)slice_len; (void)gamma; (void)beta; (void)epsilon;
   return -1;
 }
-int eshkol_gpu_conv2d_backward_input_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
-    uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t d4, uint64_t d5, uint64_t d6,
-    uint64_t d7, uint64_t d8, uint64_t d9, uint64_t d10) {
-  (void)a; (void)b; (void)c; (void)d0; (void)d1; (void)d2; (void)d3; (void)d4; (void)d5; (void)d6;
-  (void)d7; (void)d8; (void)d9; (void)d10; return -1;
+/* tier of one GEMM of a conv2d gradient: what the forward product of that shape would get */
+static void conv_grad_opts(uint64_t M, uint64_t K, uint64_t N, EshkolB200GemmOpts* o) {
+  TierChoice c = choose_tier(M, K, N);
+  if (c.tier != ESHKOL_B200_TIER_DGEMM && K > 131071) { c.tier = ESHKOL_B200_TIER_DGEMM; c.param = 0; }
+  memset(o, 0, sizeof(*o));
+  o->tier = c.tier; o->param = c.param;
 }
-int eshkol_gpu_conv2d_backward_kernel_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
-    uint64_t d0, uint64_t d1, uint64_t d2, uint64_t d3, uint64_t d4, uint64_t d5, uint64_t d6,
-    uint64_t d7, uint64_t d8, uint64_t d9, uint64_t d10) {
-  (void)a; (void)b; (void)c; (void)d0; (void)d1; (void)d2; (void)d3; (void)d4; (void)d5; (void)d6;
-  (void)d7; (void)d8; (void)d9; (void)d10; return -1;
+
+int eshkol_gpu_conv2d_backward_input_f64(EshkolGPUBuffer* grad_out, EshkolGPUBuffer* kernel_weights,
+    EshkolGPUBuffer* grad_input, uint64_t in_h, uint64_t in_w, uint64_t k_h, uint64_t k_w, uint64_t out_h,
+    uint64_t out_w, uint64_t stride_h, uint64_t stride_w, uint64_t channels_in, uint64_t channels_out,
+    uint64_t batch_size) {
+  /* gpu_memory.h:404; kernel lib/backend/gpu/gpu_cuda_kernels.cu:413-449 */
+  if (!grad_out || !kernel_weights || !grad_input || g_backend != ESHKOL_GPU_CUDA) return -1;
+  if (!grad_out->device_ptr || !kernel_weights->device_ptr || !grad_input->device_ptr) return -1;
+  EshkolB200GemmOpts o;
+  conv_grad_opts(channels_in * k_h * k_w, channels_out, batch_size * out_h * out_w, &o);
+  if (eshkol_b200_conv2d_backward_input_f64_device((const double*)grad_out->device_ptr,
+          (const double*)kernel_weights->device_ptr, (double*)grad_input->device_ptr, in_h, in_w, k_h, k_w,
+          out_h, out_w, stride_h, stride_w, channels_in, channels_out, batch_size, &o))
+    return -1;
+  if (grad_input->flags & FLAG_WRAPPED) grad_input->flags |= FLAG_DIRTY;
+  return eshkol_b200_sync_status() == 0 ? 0 : -1;
+}
+int eshkol_gpu_conv2d_backward_kernel_f64(EshkolGPUBuffer* grad_out, EshkolGPUBuffer* saved_input,
+    EshkolGPUBuffer* grad_kernel, uint64_t in_h, uint64_t in_w, uint64_t k_h, uint64_t k_w, uint64_t out_h,
+    uint64_t out_w, uint64_t stride_h, uint64_t stride_w, uint64_t channels_in, uint64_t channels_out,
+    uint64_t batch_size) {
+  /* gpu_memory.h:415; kernel lib/backend/gpu/gpu_cuda_kernels.cu:451-486 */
+  if (!grad_out || !saved_input || !grad_kernel || g_backend != ESHKOL_GPU_CUDA) return -1;
+  if (!grad_out->device_ptr || !saved_input->device_ptr || !grad_kernel->device_ptr) return -1;
+  EshkolB200GemmOpts o;
+  conv_grad_opts(channels_out, batch_size * out_h * out_w, channels_in * k_h * k_w, &o);
+  if (eshkol_b200_conv2d_backward_kernel_f64_device((const double*)grad_out->device_ptr,
+          (const double*)saved_input->device_ptr, (double*)grad_kernel->device_ptr, in_h, in_w, k_h, k_w,
+          out_h, out_w, stride_h, stride_w, channels_in, channels_out, batch_size, &o))
+    return -1;
+  if (grad_kernel->flags & FLAG_WRAPPED) grad_kernel->flags |= FLAG_DIRTY;
+  return eshkol_b200_sync_status() == 0 ? 0 : -1;
 }
 int eshkol_gpu_batchnorm_backward_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
     EshkolGPUBuffer* d, EshkolGPUBuffer* e, EshkolGPUBuffer* f, EshkolGPUBuffer* g2,

@@ -6,7 +6,7 @@ K <= 131071), so a row shard computed alone carries the same bits as the same ro
 of the full product.  Rank r owns a contiguous block of rows of A and of C; B is
 broadcast from one rank and the blocks of C are all-gathered, both with
 torch.distributed (NCCL over NVLink on GPUs, gloo in the CPU tests).  The reference
-has no multi-device code; this is the sharding BASELINE's 32768^3 configuration asks for.
+has no multi-device code; this is the sharding the 32768^3 row-sharded configuration asks for.
 """
 from __future__ import annotations
 

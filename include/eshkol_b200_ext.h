@@ -76,6 +76,26 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC,
                                 uint64_t M, uint64_t K, uint64_t N,
                                 const EshkolB200GemmOpts* opts);
 
+/* conv2d backward on device tensors (NCHW, no padding, strides sH / sW), the two kernels of
+ * lib/backend/gpu/gpu_cuda_kernels.cu:413-486 as GEMMs in the tier opts selects:
+ *   grad_kernel[co][ci][kh][kw] = (grad_out as co x batch*pixels) * im2col(input)^T
+ *   grad_input = gather over (kh, kw) of  weights^T (ci*kh*kw x co) * (grad_out as co x batch*pixels)
+ * Both transposed operands are read in place.  In the exact tier every GEMM element is the
+ * exact-tier sum where the reference adds products one by one in f64, so results agree to the
+ * reference's own rounding error, not bit for bit.  Asynchronous; 0 / -1. */
+int eshkol_b200_conv2d_backward_kernel_f64_device(const double* d_grad_out, const double* d_input,
+                                                  double* d_grad_kernel, uint64_t in_h, uint64_t in_w,
+                                                  uint64_t k_h, uint64_t k_w, uint64_t out_h, uint64_t out_w,
+                                                  uint64_t stride_h, uint64_t stride_w, uint64_t channels_in,
+                                                  uint64_t channels_out, uint64_t batch,
+                                                  const EshkolB200GemmOpts* opts);
+int eshkol_b200_conv2d_backward_input_f64_device(const double* d_grad_out, const double* d_weights,
+                                                 double* d_grad_input, uint64_t in_h, uint64_t in_w,
+                                                 uint64_t k_h, uint64_t k_w, uint64_t out_h, uint64_t out_w,
+                                                 uint64_t stride_h, uint64_t stride_w, uint64_t channels_in,
+                                                 uint64_t channels_out, uint64_t batch,
+                                                 const EshkolB200GemmOpts* opts);
+
 /* The dtype fast path (f16 / bf16-tagged tensors keep f64 storage): for b < batch,
  * C[b][M x N] = f16(A[b]) * f16(B[b]) with f32 accumulation on the tensor cores
  * (tcgen05.mma kind::f16), the result rounded to f16 and widened back to f64 -- the arithmetic of

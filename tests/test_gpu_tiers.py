@@ -110,7 +110,7 @@ def test_conv_bits_match_oracle_on_the_lowered_operands(gpu_lib, cfg):
     low = ol.oz2_exact(ker.reshape(oc, -1), col, 52).reshape(oc, b, oH, oW).transpose(1, 0, 2, 3)
     assert gu.same_bits(got, np.where(low > 0.0, low, 0.0))
     # against the direct loop: every cell to rounding except the few that carry the
-    # exact tier's own 2^-25-relative CRT rounding (parity status)
+    # exact tier's own 2^-25-relative CRT rounding (its split weights sl1 round in about 0.7 % of the cells)
     direct = fx.conv2d_numpy(inp, ker, stride, pad)
     direct = np.where(direct > 0.0, direct, 0.0)
     err = np.abs(got - direct)
@@ -307,3 +307,51 @@ def test_copy_engine_entry_points_on_one_gpu(gpu_lib):
     assert lib.eshkol_b200_ipc_export_mem(blk, hbuf) == 0 and any(hbuf.raw)
     lib.eshkol_b200_mem_free(0, blk)
     assert lib.eshkol_b200_enable_peer_access(torch.cuda.current_device()) == 0  # own device: nothing to do
+
+
+def _conv_backward_reference(G, X, Wt, sH, sW):
+    """The loops of the reference's two backward kernels (lib/backend/gpu/gpu_cuda_kernels.cu:413-486),
+    in longdouble so that the comparison measures the GPU result, not this restatement."""
+    G, X, Wt = (np.asarray(t, dtype=np.longdouble) for t in (G, X, Wt))
+    batch, C_out, oH, oW = G.shape
+    _, C_in, H, W = X.shape
+    _, _, kH, kW = Wt.shape
+    gX = np.zeros((batch, C_in, H, W), dtype=np.longdouble)
+    gK = np.zeros((C_out, C_in, kH, kW), dtype=np.longdouble)
+    for kh in range(kH):
+        for kw in range(kW):
+            xs = X[:, :, kh:kh + (oH - 1) * sH + 1:sH, kw:kw + (oW - 1) * sW + 1:sW]  # b, ci, oh, ow
+            gK[:, :, kh, kw] = np.einsum("bohw,bihw->oi", G, xs)
+            gX[:, :, kh:kh + (oH - 1) * sH + 1:sH, kw:kw + (oW - 1) * sW + 1:sW] += np.einsum(
+                "bohw,oi->bihw", G, Wt[:, :, kh, kw])
+    return gX, gK
+
+
+@pytest.mark.parametrize("cfg", [(2, 3, 9, 10, 4, 3, 3, 1, 1), (3, 5, 12, 11, 6, 3, 2, 2, 1), (1, 2, 8, 8, 3, 1, 1, 2, 2)])
+def test_conv2d_backward_both_gradients(gpu_lib, cfg):
+    import torch
+    batch, C_in, H, W, C_out, kH, kW, sH, sW = cfg
+    oH, oW = (H - kH) // sH + 1, (W - kW) // sW + 1
+    X = inputs.uniform(401, (batch, C_in, H, W))
+    Wt = inputs.uniform(402, (C_out, C_in, kH, kW))
+    G = inputs.normal(403, (batch, C_out, oH, oW))
+    dX, dW, dG = (torch.from_numpy(t).cuda() for t in (X, Wt, G))
+    gX = torch.full_like(dX, float("nan"))
+    gK = torch.full_like(dW, float("nan"))
+    torch.cuda.synchronize()
+    opts = api.make_opts(eb.TIER_OZAKI2, 16)
+    dims = (H, W, kH, kW, oH, oW, sH, sW, C_in, C_out, batch)
+    assert gpu_lib.eshkol_b200_conv2d_backward_kernel_f64_device(dG.data_ptr(), dX.data_ptr(), gK.data_ptr(),
+                                                                *dims, ctypes.byref(opts)) == 0
+    assert gpu_lib.eshkol_b200_conv2d_backward_input_f64_device(dG.data_ptr(), dW.data_ptr(), gX.data_ptr(),
+                                                               *dims, ctypes.byref(opts)) == 0
+    assert api.sync_status() == 0
+    wantX, wantK = _conv_backward_reference(G, X, Wt, sH, sW)
+    # the exact tier's own error: about 2^-25 of the magnitude sum (its CRT weights round); allow 2^-22
+    magK = float(np.abs(G).sum()) * float(np.abs(X).max())
+    magX = float(np.abs(G).max()) * float(np.abs(Wt).sum())
+    assert np.all(np.abs(gK.cpu().numpy() - wantK.astype(np.float64)) <= magK * 2.0 ** -22)
+    assert np.all(np.abs(gX.cpu().numpy() - wantX.astype(np.float64)) <= magX * 2.0 ** -22)
+    # tight on the typical element: relative error of the whole tensors
+    assert normwise(gK.cpu().numpy(), wantK.astype(np.float64)) < 1e-7
+    assert normwise(gX.cpu().numpy(), wantX.astype(np.float64)) < 1e-7
