@@ -105,6 +105,7 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_gemm_f64_device", ctypes.c_int, [vp, vp, vp, u64, u64, u64, optp])
     sig("eshkol_b200_gemm_f64_static_scratch", ctypes.c_int, [vp, vp, vp, u64, u64, u64])
     sig("eshkol_b200_matmul_f64_host", ctypes.c_int, [vp, vp, vp, u64, u64, u64, optp])
+    sig("eshkol_b200_feed_forward_f64_device", ctypes.c_int, [vp, vp, vp, vp, vp, vp, u64, u64, u64, optp])
     sig("eshkol_b200_conv2d_backward_kernel_f64_device", ctypes.c_int, [vp, vp, vp] + [u64] * 11 + [optp])
     sig("eshkol_b200_conv2d_backward_input_f64_device", ctypes.c_int, [vp, vp, vp] + [u64] * 11 + [optp])
     sig("eshkol_b200_gemm_f16_device", ctypes.c_int, [vp, vp, vp, u64, u64, u64, u64])

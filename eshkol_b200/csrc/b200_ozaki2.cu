@@ -379,7 +379,7 @@ __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
     double v = __dmul_rn(__dmul_rn(__dadd_rn(c1, c2), mu_inv), a.inv_scale_b[j]);
     if (a.bias_mode == 1) v = __dadd_rn(v, a.bias[i]);
     else if (a.bias_mode == 2) v = __dadd_rn(v, a.bias[j]);
-    if (a.activation == 1) v = (v > 0.0) ? v : 0.0;  // gpu_cuda_kernels.cu:37
+    v = apply_activation(v, a.activation);
     out[e] = v;
   }
   if (a.pixels_per_image > 0) {

@@ -40,7 +40,7 @@ struct CrtArgs {
   long long ldc;
   int bias_mode;              // 0 none, 1 per row, 2 per column
   const double* bias;
-  int activation;             // 0 none, 1 ReLU
+  int activation;             // 0 none, 1 ReLU, 2 tanh-form GELU
   long long pixels_per_image; // > 0: scatter columns to [image][row][pixel] (conv2d NCHW)
 };
 

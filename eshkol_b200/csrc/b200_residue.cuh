@@ -69,4 +69,20 @@ __device__ __forceinline__ uint32_t chunk_flag_parity(const uint16_t* a_hi, cons
   return acc & 1u;
 }
 
+// Epilogue activations: 0 none, 1 ReLU (x > 0 ? x : 0, lib/backend/gpu/gpu_cuda_kernels.cu:37),
+// 2 the tanh-form GELU of the reference's feed-forward, written as its generated code computes
+// it (lib/backend/tensor_transformer_codegen.cpp:2469-2577): tanh through exp(2u), each
+// operation rounded on its own.  Like that code it returns NaN once exp(2u) overflows (u > 354).
+__device__ __forceinline__ double apply_activation(double x, int activation) {
+  if (activation == 1) return (x > 0.0) ? x : 0.0;
+  if (activation == 2) {
+    const double x3 = __dmul_rn(x, __dmul_rn(x, x));
+    const double u = __dmul_rn(0.7978845608028654, __dadd_rn(x, __dmul_rn(0.044715, x3)));
+    const double e = exp(__dmul_rn(2.0, u));
+    const double t = __ddiv_rn(__dsub_rn(e, 1.0), __dadd_rn(e, 1.0));
+    return __dmul_rn(0.5, __dmul_rn(x, __dadd_rn(1.0, t)));
+  }
+  return x;
+}
+
 }  // namespace b200

@@ -1080,6 +1080,25 @@ int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, 
                          static_cast<long long>(N), o);
 }
 
+int eshkol_b200_feed_forward_f64_device(const double* d_x, const double* d_w1, const double* d_b1,
+                                        const double* d_w2, const double* d_b2, double* d_out,
+                                        uint64_t rows, uint64_t d_model, uint64_t d_ff,
+                                        const EshkolB200GemmOpts* opts) {
+  if (!g.ready || !d_x || !d_w1 || !d_w2 || !d_out || rows == 0 || d_model == 0 || d_ff == 0) return -1;
+  uint8_t* hid = aux_reserve(static_cast<size_t>(rows) * d_ff * 8);
+  if (!hid) return -1;
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  if (opts) { o.tier = opts->tier; o.param = opts->param; }
+  EshkolB200GemmOpts o1 = o;
+  o1.activation = 2;
+  o1.bias = d_b1; o1.bias_mode = d_b1 ? 2 : 0;
+  if (eshkol_b200_gemm_f64_device(d_x, d_w1, reinterpret_cast<double*>(hid), rows, d_model, d_ff, &o1) != 0) return -1;
+  EshkolB200GemmOpts o2 = o;
+  o2.bias = d_b2; o2.bias_mode = d_b2 ? 2 : 0;
+  return eshkol_b200_gemm_f64_device(reinterpret_cast<const double*>(hid), d_w2, d_out, rows, d_ff, d_model, &o2);
+}
+
 int eshkol_b200_conv2d_backward_kernel_f64_device(const double* d_grad_out, const double* d_input,
                                                   double* d_grad_kernel, uint64_t in_h, uint64_t in_w,
                                                   uint64_t k_h, uint64_t k_w, uint64_t out_h, uint64_t out_w,

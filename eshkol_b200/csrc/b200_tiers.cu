@@ -64,7 +64,7 @@ struct Epilogue {
 __device__ __forceinline__ void store_out(const Epilogue& ep, long long i, long long j, double c) {
   if (ep.bias_mode == 1) c = __dadd_rn(c, ep.bias[i]);
   else if (ep.bias_mode == 2) c = __dadd_rn(c, ep.bias[j]);
-  if (ep.activation == 1) c = (c > 0.0) ? c : 0.0;
+  c = apply_activation(c, ep.activation);
   long long o;
   if (ep.pixels_per_image > 0) {
     const long long img = j / ep.pixels_per_image, pix = j - img * ep.pixels_per_image;

@@ -44,7 +44,8 @@ typedef enum {
 typedef struct EshkolB200GemmOpts {
   int32_t tier;             /* EshkolB200Tier */
   int32_t param;            /* tier parameter, 0 = tier default */
-  int32_t activation;       /* 0 none, 1 ReLU (x > 0 ? x : 0) fused into the last pass */
+  int32_t activation;       /* fused into the last pass: 0 none, 1 ReLU (x > 0 ? x : 0), 2 the tanh-form GELU of
+                               the reference's feed-forward (tensor_transformer_codegen.cpp:2469-2577) */
   int32_t bias_mode;        /* 0 none, 1 bias[row], 2 bias[column], added before the activation */
   const double* bias;       /* device pointer, M or N doubles */
   int64_t pixels_per_image; /* > 0: C is written as [N/pixels][M][pixels] (conv2d NCHW) */
@@ -75,6 +76,18 @@ void* eshkol_b200_stream(void);
 int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC,
                                 uint64_t M, uint64_t K, uint64_t N,
                                 const EshkolB200GemmOpts* opts);
+
+/* feed-forward block on device tensors, the arithmetic of the loops the reference generates inline
+ * for (feed-forward x W1 b1 W2 b2) (lib/backend/tensor_transformer_codegen.cpp:2557-2664):
+ *   out[rows x d_model] = gelu(x[rows x d_model] * W1[d_model x d_ff] + b1) * W2[d_ff x d_model] + b2
+ * as two GEMMs of the tier opts selects with bias and activation fused into their last pass; the
+ * hidden activations stay in library scratch.  The GEMMs are exact-tier sums where the generated
+ * loops add one product at a time, and exp is the device's: agreement is to rounding, not bits.
+ * Asynchronous; 0 / -1. */
+int eshkol_b200_feed_forward_f64_device(const double* d_x, const double* d_w1, const double* d_b1,
+                                        const double* d_w2, const double* d_b2, double* d_out,
+                                        uint64_t rows, uint64_t d_model, uint64_t d_ff,
+                                        const EshkolB200GemmOpts* opts);
 
 /* conv2d backward on device tensors (NCHW, no padding, strides sH / sW), the two kernels of
  * lib/backend/gpu/gpu_cuda_kernels.cu:413-486 as GEMMs in the tier opts selects:

@@ -355,3 +355,40 @@ def test_conv2d_backward_both_gradients(gpu_lib, cfg):
     # tight on the typical element: relative error of the whole tensors
     assert normwise(gK.cpu().numpy(), wantK.astype(np.float64)) < 1e-7
     assert normwise(gX.cpu().numpy(), wantX.astype(np.float64)) < 1e-7
+
+
+def test_feed_forward_block(gpu_lib):
+    """out = gelu(x W1 + b1) W2 + b2 with the tanh-by-exp GELU of the reference's generated loops
+    (lib/backend/tensor_transformer_codegen.cpp:2469-2664), two GEMMs with fused epilogues."""
+    import torch
+    rows, d_model, d_ff = 70, 96, 200
+    x = inputs.normal(501, (rows, d_model))
+    W1 = inputs.uniform(502, (d_model, d_ff)) * 0.2
+    b1 = inputs.uniform(503, (d_ff,))
+    W2 = inputs.uniform(504, (d_ff, d_model)) * 0.2
+    b2 = inputs.uniform(505, (d_model,))
+    dev = [torch.from_numpy(np.ascontiguousarray(t)).cuda() for t in (x, W1, b1, W2, b2)]
+    out = torch.full((rows, d_model), float("nan"), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    opts = api.make_opts(eb.TIER_OZAKI2, 16)
+    rc = gpu_lib.eshkol_b200_feed_forward_f64_device(*(t.data_ptr() for t in dev), out.data_ptr(), rows, d_model,
+                                                     d_ff, ctypes.byref(opts))
+    assert rc == 0 and api.sync_status() == 0
+    ld = np.longdouble
+    pre = (x.astype(ld) @ W1.astype(ld) + b1.astype(ld)).astype(np.float64)
+    u = 0.7978845608028654 * (pre + 0.044715 * (pre * (pre * pre)))
+    e = np.exp(2.0 * u)
+    hidden = 0.5 * (pre * (1.0 + (e - 1.0) / (e + 1.0)))
+    want = (hidden.astype(ld) @ W2.astype(ld) + b2.astype(ld)).astype(np.float64)
+    got = out.cpu().numpy()
+    assert normwise(got, want) < 1e-7
+    # element by element: the exact tier's 2^-25-of-magnitude error through both products
+    mag = np.abs(hidden) @ np.abs(W2) + np.abs(b2) + (np.abs(x) @ np.abs(W1)).max() * np.abs(W2).sum(axis=0)
+    assert np.all(np.abs(got - want) <= mag * 2.0 ** -21)
+    # the fused ReLU / GELU epilogue equals the separate elementwise pass on the same product
+    plain = gu.gemm(x, W1)
+    fused = gu.gemm(x, W1, activation=2, bias=b1, bias_mode=2)
+    t = plain + b1
+    uu = 0.7978845608028654 * (t + 0.044715 * (t * (t * t)))
+    ee = np.exp(2.0 * uu)
+    np.testing.assert_allclose(fused, 0.5 * (t * (1.0 + (ee - 1.0) / (ee + 1.0))), rtol=1e-13, atol=1e-15)
