@@ -392,3 +392,48 @@ def test_feed_forward_block(gpu_lib):
     uu = 0.7978845608028654 * (t + 0.044715 * (t * (t * t)))
     ee = np.exp(2.0 * uu)
     np.testing.assert_allclose(fused, 0.5 * (t * (1.0 + (ee - 1.0) / (ee + 1.0))), rtol=1e-13, atol=1e-15)
+
+
+def _run_reference_gpu(kernel, T, M, K, N, sa, sb, tmp_path):
+    """The reference's own CUDA backend in a process of its own (tests/ref_gpu_runner.py)."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.exists(os.path.join(root, "oracle", "_ref", "libref_gpu_cuda.so")):
+        pytest.skip("reference CUDA backend not built (oracle/Makefile target _ref/libref_gpu_cuda.so)")
+    out = str(tmp_path / f"ref_{kernel}_{T}.npy")
+    r = subprocess.run([sys.executable, os.path.join(root, "tests", "ref_gpu_runner.py"), kernel, str(T), str(M),
+                        str(K), str(N), str(sa), str(sb), out], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    return np.load(out)
+
+
+@pytest.mark.parametrize("T", [4, 6])
+def test_slice_tier_against_the_reference_cuda_backend(gpu_lib, tmp_path, T):
+    """The INT8 slice tier of the reference itself (cuda_matmul_ozaki_int8_f64,
+    lib/backend/gpu/gpu_memory_cuda.cpp:339-452, compiled from the reference's sources and run on
+    this GPU) against this library's Ozaki-I tier on the same operands: integer-exact products and
+    the same reconstruction order on both sides, so the bits agree.  1024^3 is the smallest shape
+    the reference sends to that tier (gpu_memory_cuda.cpp:463)."""
+    M = K = N = 1024
+    ref = _run_reference_gpu("ozaki-int8", T, M, K, N, 601, 602, tmp_path)
+    A = inputs.uniform(601, (M, K))
+    B = inputs.uniform(602, (K, N))
+    got = gu.gemm(A, B, tier=eb.TIER_OZAKI1, param=T)
+    assert gu.same_bits(got, ref)
+    assert gu.same_bits(ol.oz1(A, B, T), ref)  # and pins the CPU restatement
+
+
+def test_exact_tier_against_the_reference_cublas_dgemm(gpu_lib, tmp_path):
+    """cublasDgemm through the reference's backend (its default f64 path on CUDA) against the exact
+    tier: both within rounding of the true product; the exact tier's error is the smaller one on
+    most elements and never beyond its 2^-25-of-magnitude bound."""
+    M, K, N = 1024, 1024, 1024
+    ref = _run_reference_gpu("dgemm", 0, M, K, N, 603, 604, tmp_path)
+    A = inputs.uniform(603, (M, K))
+    B = inputs.uniform(604, (K, N))
+    got = gu.gemm(A, B)
+    mag = np.abs(A) @ np.abs(B)
+    assert np.all(np.abs(got - ref) <= mag * 2.0 ** -22)
+    assert normwise(got, ref) < 1e-8
