@@ -366,6 +366,39 @@ def run_b200(args):
         e2e = {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                "note": "sharded configuration is defined on device-resident operands; see the 1-GPU line for PCIe"}
 
+    # The sharded configuration on this one GPU (it fits: about 90 GB): the denominator for the
+    # parallel efficiency of the 2 / 4 / 8-GPU lines, whose workload it is.
+    one_gpu_sharded_shape = None
+    if world == 1 and os.environ.get("ESHKOL_B200_SKIP_32768", "") != "1":
+        try:
+            del A, B, C_local
+            if e2e is not None:
+                del hA, hB, hC
+            torch.cuda.empty_cache()
+            nn = 32768
+            A32 = inputs.uniform(1, (nn, nn), device=dev)
+            B32 = inputs.uniform(2, (nn, nn), device=dev)
+            C32 = torch.empty((nn, nn), dtype=torch.float64, device=dev)
+            torch.cuda.synchronize()
+            api.gemm_device(A32.data_ptr(), B32.data_ptr(), C32.data_ptr(), nn, nn, nn, opts)
+            if api.sync_status() != 0:
+                raise RuntimeError("kernel status non-zero")
+            reps = 2
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(lib_stream)
+            for _ in range(reps):
+                api.gemm_device(A32.data_ptr(), B32.data_ptr(), C32.data_ptr(), nn, nn, nn, opts)
+            f1.record(lib_stream)
+            if api.sync_status() != 0:
+                raise RuntimeError("kernel status non-zero")
+            ms32 = f0.elapsed_time(f1) / reps
+            one_gpu_sharded_shape = {"workload": "f64 GEMM 32768x32768x32768, exact tier, entries uniform[-1,1), one B200",
+                                     "value": 2.0 * nn ** 3 / (ms32 * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms32,
+                                     "steps": reps, "warmup": 1}
+            del A32, B32, C32
+        except (RuntimeError, MemoryError) as exc:  # reported, never fatal to the 8192^3 line
+            one_gpu_sharded_shape = {"unavailable": str(exc).splitlines()[0][:200]}
+
     cpu = None
     if world == 1:
         cpu, _ = cpu_reference_run(n, 1024, 3, 1, "normal")
@@ -377,6 +410,8 @@ def run_b200(args):
         "data": "synthetic", "config": dict(workload_config(world), **({"b_panels": sg.panels, "transport": sg.transport, "rows_checked_against_one_gpu": verified} if sg else {})), "clocks": clocks,
         "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu,
     }
+    if one_gpu_sharded_shape is not None:
+        line["sharded_shape_on_one_gpu"] = one_gpu_sharded_shape
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
