@@ -437,3 +437,17 @@ def test_exact_tier_against_the_reference_cublas_dgemm(gpu_lib, tmp_path):
     mag = np.abs(A) @ np.abs(B)
     assert np.all(np.abs(got - ref) <= mag * 2.0 ** -22)
     assert normwise(got, ref) < 1e-8
+
+
+@pytest.mark.parametrize("T", [4, 6])
+def test_slice_tier_against_committed_reference_rows(gpu_lib, T):
+    """The committed rows of the reference's CUDA slice tier (tests/golden/reference_cuda_1024.npz,
+    made on a B200 by tests/golden/make_golden.py): this library's tier reproduces them bit for bit,
+    whether or not the reference library is present on this machine."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_cuda_1024.npz"))
+    n, rows = int(g["n"]), g["rows"]
+    A = inputs.uniform(int(g["seed_a"]), (n, n))
+    B = inputs.uniform(int(g["seed_b"]), (n, n))
+    got = gu.gemm(A, B, tier=eb.TIER_OZAKI1, param=T)
+    assert gu.same_bits(got[rows], g[f"slice_T{T}"])

@@ -156,3 +156,37 @@ def test_reference_backward_is_two_products_of_transposes():
     # 2^-25 of the row-by-column magnitude) bounds the agreement, as for the forward product
     np.testing.assert_allclose(ol.oz2_exact(G, np.ascontiguousarray(B.T), 52), gA, rtol=1e-6, atol=5e-6)
     np.testing.assert_allclose(ol.oz2_exact(np.ascontiguousarray(A.T), G, 52), gB, rtol=1e-6, atol=5e-6)
+
+
+def _golden_reference_cuda():
+    import os
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "reference_cuda_1024.npz")
+    return np.load(path)
+
+
+def test_slice_tier_restatement_matches_the_reference_cuda_backend_bits():
+    """tests/golden/reference_cuda_1024.npz holds rows of 1024^3 products computed by the reference's
+    own CUDA backend on a B200 (tests/golden/make_golden.py).  Its INT8 slice tier is integer-exact
+    with a fixed reconstruction order, so the CPU restatement must reproduce those rows bit for bit."""
+    from eshkol_b200 import inputs
+    g = _golden_reference_cuda()
+    n, rows = int(g["n"]), g["rows"]
+    A = inputs.uniform(int(g["seed_a"]), (n, n))[rows]
+    B = inputs.uniform(int(g["seed_b"]), (n, n))
+    for T in (4, 6):
+        got = ol.oz1(A, B, T)
+        want = g[f"slice_T{T}"]
+        assert np.array_equal(got.view(np.uint64), want.view(np.uint64))
+
+
+def test_exact_tier_restatement_within_its_bound_of_the_reference_cublas_dgemm():
+    """The same file's cublasDgemm rows: the exact tier's restatement agrees with them to the exact
+    tier's own error (about 2^-25 of sum |a||b| in 0.7 % of the cells) plus DGEMM's rounding."""
+    from eshkol_b200 import inputs
+    g = _golden_reference_cuda()
+    n, rows = int(g["n"]), g["rows"]
+    A = inputs.uniform(int(g["seed_a"]), (n, n))[rows]
+    B = inputs.uniform(int(g["seed_b"]), (n, n))
+    got = ol.oz2_exact(A, B, 52)
+    mag = np.abs(A) @ np.abs(B)
+    assert np.all(np.abs(got - g["dgemm"]) <= mag * 2.0 ** -22)
