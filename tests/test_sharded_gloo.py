@@ -65,3 +65,18 @@ def test_sharded_product_equals_unsharded_bits(tmp_path, world, M, panels):
     C = np.load(out)
     full = ol.oz2_exact(inputs.full53(1, (M, K)), inputs.full53(2, (K, N)), 52)
     assert np.array_equal(C.view(np.uint64), full.view(np.uint64))
+
+
+def test_transport_argument():
+    """Off a GPU the copy-engine transport is not available: the driver keeps the collectives;
+    a name it does not know is refused."""
+    def gemm(a, b, c):
+        c.copy_(a @ b)
+
+    sg = ShardedGemm(8, 4, 6, "cpu", gemm=gemm, panels=2, transport="copy_engine")
+    assert sg.transport == "collectives"
+    A = torch.arange(32, dtype=torch.float64).reshape(8, 4)
+    B = torch.arange(24, dtype=torch.float64).reshape(4, 6)
+    assert torch.equal(sg.step(A, B), A @ B)
+    with pytest.raises(ValueError):
+        ShardedGemm(8, 4, 6, "cpu", gemm=gemm, transport="carrier-pigeon")
