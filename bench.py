@@ -196,8 +196,10 @@ def run_b200(args):
         # once the collectives are a visible share of the step (4 ranks and more)
         panels = int(os.environ.get("ESHKOL_B200_PANELS", "4"))
         transport = os.environ.get("ESHKOL_B200_TRANSPORT", "copy_engine")
+        # a first and a last panel of half the width shorten the two transfers nothing hides
+        taper = os.environ.get("ESHKOL_B200_TAPER", "1") == "1"
         sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=panels, comm_sms=comm_sms,
-                         transport=transport)
+                         transport=transport, taper=taper)
         rows = sg.rows
         A = inputs.uniform(1, (rows, n), device=dev, start=sg.row0 * n)
         B = inputs.uniform(2, (n, n), device=dev) if rank == 0 else None
@@ -275,7 +277,7 @@ def run_b200(args):
 
     # per-stage times of one more (untimed) GEMM, for the roofline of the dominant kernel
     ph = (ctypes.c_float * 8)()
-    Bdev = B if sg is None else sg.Bp[0]
+    Bdev = B if sg is None else sg.Bp[sg.panels // 2]  # a full-width panel when the edge panels are halved
     api.gemm_device(A.data_ptr(), Bdev.data_ptr(), C_local.data_ptr(), rows, n, Bdev.shape[1], opts)
     got = lib.eshkol_b200_get_phase_times(ph, 8)
     lib.eshkol_b200_set_phase_timing(0)
@@ -407,7 +409,7 @@ def run_b200(args):
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(3, args.warmup), "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f64",
-        "data": "synthetic", "config": dict(workload_config(world), **({"b_panels": sg.panels, "transport": sg.transport, "rows_checked_against_one_gpu": verified} if sg else {})), "clocks": clocks,
+        "data": "synthetic", "config": dict(workload_config(world), **({"b_panels": sg.panels, "b_panel_widths": [wd for _, wd in sg.cols], "transport": sg.transport, "rows_checked_against_one_gpu": verified} if sg else {})), "clocks": clocks,
         "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu,
     }
     if one_gpu_sharded_shape is not None:

@@ -114,7 +114,7 @@ class ShardedGemm:
 
     def __init__(self, M: int, K: int, N: int, device, *, tier: int = 0, param: int = 0, src: int = 0,
                  group=None, gemm: Optional[Callable] = None, panels: int = 1, comm_sms: int = 0,
-                 transport: str = "collectives"):
+                 transport: str = "collectives", taper: bool = False):
         self.M, self.K, self.N = M, K, N
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -129,6 +129,11 @@ class ShardedGemm:
         self.trace = None  # set to [] to collect (label, CUDA event) marks of the next step
         self.panels = panels if (panels > 0 and N % panels == 0) else 1
         self.width = N // self.panels
+        # column range of every panel: equal widths, or (taper, copy-engine transport only) a first
+        # and a last panel of half the width, because the first panel's way to the ranks and the
+        # last panel's way back are the two transfers no products hide
+        self.cols = [(p * self.width, self.width) for p in range(self.panels)]
+        self._taper_wanted = bool(taper) and self.panels >= 2 and self.width % 512 == 0
         if transport not in ("collectives", "copy_engine"):
             raise ValueError(f"unknown transport {transport!r}")
         self.transport = "collectives"
@@ -139,6 +144,12 @@ class ShardedGemm:
             import datetime
             import sys
             self.ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=180))
+            uniform = (self.panels, self.width, self.cols)
+            if self._taper_wanted:
+                h = self.width // 2
+                self.cols = [(0, h)] + [(h + i * self.width, self.width) for i in range(self.panels - 1)] + \
+                            [(N - h, h)]
+                self.panels = len(self.cols)
             try:
                 self._open_peers()
                 opened = 1
@@ -149,6 +160,8 @@ class ShardedGemm:
             dist.all_reduce(agreed, op=dist.ReduceOp.MIN, group=self.ctl)
             if int(agreed.item()) == 1:
                 self.transport = "copy_engine"
+            else:
+                self.panels, self.width, self.cols = uniform
         if self.transport != "copy_engine":
             # panel-major copy of B: panel p is the contiguous K x width block of columns p*width ...
             self.Bp = torch.empty((self.panels, K, self.width), dtype=torch.float64, device=self.device)
@@ -214,7 +227,7 @@ class ShardedGemm:
             return out.value
 
         def make_blocks():
-            self._blk_B = self._DeviceBlock(lib, (P, self.K, self.width), self.device)
+            self._blk_B = self._DeviceBlock(lib, (self.K * self.N,), self.device)
             self._blk_C = self._DeviceBlock(lib, (self.M, self.N), self.device)
             return (self._blk_B.handle(), self._blk_C.handle())
 
@@ -268,7 +281,10 @@ class ShardedGemm:
         self._ev_block = make_events(P)    # this rank's block of C, panel p, is computed
         if failure:
             raise RuntimeError(failure[0])
-        self.Bp, self.C = self._blk_B.tensor, self._blk_C.tensor
+        flat = self._blk_B.tensor
+        # panel p: the contiguous K x width block of its columns, packed one panel after the other
+        self.Bp = [flat[self.K * c0:self.K * (c0 + wd)].view(self.K, wd) for c0, wd in self.cols]
+        self.C = self._blk_C.tensor
         self._x1 = torch.cuda.Stream(self.device)
         self._x2 = torch.cuda.Stream(self.device)
         self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(min(4, max(1, W - 1)))]
@@ -285,24 +301,26 @@ class ShardedGemm:
 
     def _pull_b_slice(self, q_from: int, p: int, k0: int, kn: int, stream) -> None:
         """rows [k0, k0+kn) of panel p: rank q_from's Bp -> this rank's Bp (contiguous, one copy)"""
-        off = (p * self.K + k0) * self.width * 8
+        c0, wd = self.cols[p]
+        off = (self.K * c0 + k0 * wd) * 8
         rc = self.backend.lib.eshkol_b200_copy_async(self._addr_B[self.rank] + off, self._addr_B[q_from] + off,
-                                                     kn * self.width * 8, stream.cuda_stream)
+                                                     kn * wd * 8, stream.cuda_stream)
         if rc != 0:
             raise RuntimeError("copy_async failed")
 
     def _pull_c_block(self, q: int, p: int, stream) -> None:
         """rank q's rows of the panel-p columns of C: its C -> the same place in this rank's C"""
         q0, rows_q = self.parts[q]
-        off = (q0 * self.N + p * self.width) * 8
+        c0, wd = self.cols[p]
+        off = (q0 * self.N + c0) * 8
         rc = self.backend.lib.eshkol_b200_copy2d_async(self._addr_C[self.rank] + off, self.N * 8,
-                                                       self._addr_C[q] + off, self.N * 8, self.width * 8, rows_q,
+                                                       self._addr_C[q] + off, self.N * 8, wd * 8, rows_q,
                                                        stream.cuda_stream)
         if rc != 0:
             raise RuntimeError("copy2d_async failed")
 
     def _step_copy_engine(self, A_rows: torch.Tensor, B_src: Optional[torch.Tensor]) -> torch.Tensor:
-        P, w, R, W = self.panels, self.width, self.rank, self.world
+        P, R, W = self.panels, self.rank, self.world
         cur = torch.cuda.current_stream(self.device)
         lib = self.backend.stream
         if self._side is None:
@@ -313,7 +331,7 @@ class ShardedGemm:
             st.wait_stream(cur)
         if self.rows:
             lib.wait_stream(cur)
-            self.backend.begin(A_rows, w)
+            self.backend.begin(A_rows, max(wd for _, wd in self.cols))
             self._mark("A prepared", lib)
         # B: the source packs a panel; every rank pulls its own K-slice of it from the source
         # (phase 1, the source's egress carries the panel once), then the other slices from
@@ -324,10 +342,10 @@ class ShardedGemm:
             # packed by the copy engines (about 0.9 TB/s on an idle GPU): an elementwise kernel of
             # another stream would wait for the gaps between the products kernels
             st = x1
-            for p in range(P):
+            for p, (c0, wd) in enumerate(self.cols):
                 rc = self.backend.lib.eshkol_b200_copy2d_async(
-                    self._addr_B[R] + p * self.K * w * 8, w * 8, B_src.data_ptr() + p * w * 8, self.N * 8,
-                    w * 8, self.K, st.cuda_stream)
+                    self._addr_B[R] + self.K * c0 * 8, wd * 8, B_src.data_ptr() + c0 * 8, self.N * 8,
+                    wd * 8, self.K, st.cuda_stream)
                 if rc != 0:
                     raise RuntimeError("copy2d_async failed")
                 self._mark(f"packed {p}", st)
@@ -361,7 +379,8 @@ class ShardedGemm:
             if self.rows:
                 lib.wait_event(arrived[p])
                 self._mark(f"panel {p} products start", lib)
-                self.backend.panel(A_rows, self.Bp[p], self.C[self.row0:self.row0 + self.rows, p * w:(p + 1) * w])
+                c0, wd = self.cols[p]
+                self.backend.panel(A_rows, self.Bp[p], self.C[self.row0:self.row0 + self.rows, c0:c0 + wd])
                 self._mark(f"panel {p} products done", lib)
             self._record(self._ev_block[R][p], lib)
         dist.barrier(group=self.ctl)
