@@ -140,6 +140,7 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_set_row_bands", None, [ctypes.c_longlong])
     sig("eshkol_b200_set_phase_timing", None, [ctypes.c_int])
     sig("eshkol_b200_get_phase_times", ctypes.c_int, [ctypes.POINTER(ctypes.c_float), ctypes.c_int])
+    sig("eshkol_b200_get_phase_totals", ctypes.c_int, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_int)])
     sig("eshkol_b200_launch_count", u64, [])
     sig("eshkol_b200_workspace_bytes", u64, [])
     sig("eshkol_b200_debug_fetch", ctypes.c_int, [ctypes.c_int, ctypes.c_int, vp, u64, ctypes.POINTER(u64)])

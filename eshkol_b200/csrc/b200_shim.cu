@@ -39,7 +39,12 @@ struct State {
   // optional per-stage timing of the Ozaki-II driver (CUDA events on the stream)
   bool timing = false;
   bool pair_gemm = false;  // odd-moduli products on CTA pairs (tcgen05 cta_group::2)
-  cudaEvent_t ev[9] = {};
+  // Rings of stage events, one entry per call of the stage: B side {start, scan + scales done,
+  // split done}, A side likewise, multiplication {start, modulus 256 + ties done, odd moduli
+  // done, reconstruction done}.  n_* count the entries recorded since timing was switched on.
+  static constexpr int kEvRing = 256;
+  cudaEvent_t ev_b[kEvRing][3] = {}, ev_a[kEvRing][3] = {}, ev_m[kEvRing][4] = {};
+  unsigned long long n_evb = 0, n_eva = 0, n_evm = 0;
   cudaEvent_t ev_scratch = nullptr;
   bool ev_made = false, ev_valid = false;
   // prepared right-hand operand of the exact tier (its own allocation)
@@ -180,6 +185,7 @@ static uint8_t* tbuf_reserve(size_t bytes) {
 
 uint8_t* workspace_reserve(size_t bytes) { return ensure_workspace(bytes) == 0 ? g.ws : nullptr; }
 cudaStream_t lib_stream() { return g.stream; }
+int lib_device() { return g.ready ? g.device : -1; }
 static inline int gemm_sms() {
   int n = g.num_sms;
   if (g.sm_limit > 0 && g.sm_limit < n) n = g.sm_limit;
@@ -326,7 +332,7 @@ static int oz2_check_shape(long long M, long long K, long long N, int n_mod) {
   return 0;
 }
 
-#define B200_MARK(i) do { if (timed) B200_CHECK(cudaEventRecord(g.ev[i], st)); } while (0)
+#define B200_MARK(i) do { if (timed) B200_CHECK(cudaEventRecord(g.ev_b[g.n_evb % State::kEvRing][i], st)); } while (0)
 
 // Right-hand operand of the exact tier, prepared once and kept: nu_j, 2^+-nu_j and
 // the residue planes of B.  Rows of A can then be multiplied block by block (the
@@ -384,6 +390,7 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
   if (trans) B200_CHECK(launch_split_a(dB, P.sb, pb, P.consts, st));
   else B200_CHECK(launch_split_b(dB, P.sb, N, pb, P.consts, st));
   B200_MARK(2);
+  if (timed) ++g.n_evb;
   g.launches += 3;
   if (make_plane_map(&P.mB0, P.b0, q.K0, N, 1, static_cast<long long>(N) * q.K0, bn)) return -1;
   if (make_plane_map(&P.mB1, P.bodd, q.Kp, N, n_odd, P.bodd_stride, bn)) return -1;
@@ -468,7 +475,10 @@ static int oz2_prepare_a(const double* dA, long long M, long long K, long long n
   if (ensure_workspace(oz2_a_layout(q).total) != 0) return -1;
   const bool timed = g.timing && g.ev_made;
   g.bands_timed = 0;
-  return oz2_prepare_a_at(g.prepA, g.ws, q, dA, g.stream, timed ? &g.ev[3] : nullptr, trans);
+  const int rc = oz2_prepare_a_at(g.prepA, g.ws, q, dA, g.stream,
+                                  timed ? g.ev_a[g.n_eva % State::kEvRing] : nullptr, trans);
+  if (timed && rc == 0) ++g.n_eva;
+  return rc;
 }
 
 // Streams of one multiplication.  Serial: all three are the library stream.  In the band
@@ -586,14 +596,17 @@ static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, d
   return 0;
 }
 
-// Serial multiplication on the library stream.  Stage events: [6] behind the modulus-256
-// product and its tie resolution, [7] behind the odd products, [8] behind the reconstruction;
-// the lane marks that have no serial meaning land on a scratch event.
+// Serial multiplication on the library stream.  Stage events of this call's ring entry: [0] at
+// its start, [1] behind the modulus-256 product and its tie resolution, [2] behind the odd
+// products, [3] behind the reconstruction; the lane marks that have no serial meaning land on
+// a scratch event.
 static int oz2_multiply(double* dC, const EshkolB200GemmOpts& o) {
   const bool timed = g.timing && g.ev_made;
-  cudaEvent_t tev[7] = {g.ev_scratch, g.ev[6], g.ev[7], g.ev_scratch, g.ev[6], g.ev_scratch, g.ev[8]};
+  cudaEvent_t* e = g.ev_m[g.n_evm % State::kEvRing];
+  cudaEvent_t tev[7] = {e[0], e[1], e[2], g.ev_scratch, e[1], g.ev_scratch, e[3]};
   MulLanes ln{g.stream, g.stream, nullptr, nullptr, timed ? tev : nullptr};
   const int rc = oz2_multiply_at(g.prepA, g.ws, g.ws_bytes, dC, o, ln);
+  if (timed && rc == 0) ++g.n_evm;
   g.ev_valid = timed && rc == 0;
   return rc;
 }
@@ -980,6 +993,9 @@ int eshkol_b200_init(int device) {
   }
   B200_CHECK(split_set_attributes());
   B200_CHECK(tiers_set_attributes());
+  // the allocation-free entry point's scratch array: its module is loaded and its address
+  // resolved here, so that entry point itself never causes a load or an allocation
+  if (static_scratch_setup(device) != 0) return -1;
   g.ready = true;
   return 0;
 }
@@ -993,7 +1009,11 @@ void eshkol_b200_shutdown(void) {
   if (g.tbuf) cudaFree(g.tbuf);
   if (g.d_status) cudaFree(g.d_status);
   if (g.ev_made) {
-    for (int i = 0; i < 9; ++i) cudaEventDestroy(g.ev[i]);
+    for (int r = 0; r < State::kEvRing; ++r) {
+      for (cudaEvent_t e : g.ev_b[r]) cudaEventDestroy(e);
+      for (cudaEvent_t e : g.ev_a[r]) cudaEventDestroy(e);
+      for (cudaEvent_t e : g.ev_m[r]) cudaEventDestroy(e);
+    }
     cudaEventDestroy(g.ev_scratch);
   }
   if (g.ev_band_made) for (cudaEvent_t e : g.ev_band) cudaEventDestroy(e);
@@ -1400,8 +1420,11 @@ void eshkol_b200_set_row_bands(long long rows) {
 void eshkol_b200_set_phase_timing(int on) {
   if (!g.ready) return;
   if (on && !g.ev_made) {
-    for (int i = 0; i < 9; ++i)
-      if (cudaEventCreate(&g.ev[i]) != cudaSuccess) { cudaGetLastError(); return; }
+    for (int r = 0; r < State::kEvRing; ++r) {
+      for (cudaEvent_t& e : g.ev_b[r]) if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return; }
+      for (cudaEvent_t& e : g.ev_a[r]) if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return; }
+      for (cudaEvent_t& e : g.ev_m[r]) if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return; }
+    }
     if (cudaEventCreate(&g.ev_scratch) != cudaSuccess) { cudaGetLastError(); return; }
     g.ev_made = true;
   }
@@ -1412,17 +1435,36 @@ void eshkol_b200_set_phase_timing(int on) {
   }
   g.timing = on != 0;
   g.ev_valid = false;
+  g.n_evb = g.n_eva = g.n_evm = 0;
+}
+
+// stage durations of ring entry `idx` of each group
+static int phase_entry(unsigned long long ib, unsigned long long ia, unsigned long long im, float* ms,
+                       bool with_a_and_m) {
+  const cudaEvent_t* b = g.ev_b[ib % State::kEvRing];
+  if (cudaEventElapsedTime(&ms[0], b[0], b[1]) != cudaSuccess || cudaEventElapsedTime(&ms[1], b[1], b[2]) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  if (!with_a_and_m) return 0;
+  const cudaEvent_t* a = g.ev_a[ia % State::kEvRing];
+  const cudaEvent_t* m = g.ev_m[im % State::kEvRing];
+  if (cudaEventElapsedTime(&ms[2], a[0], a[1]) != cudaSuccess || cudaEventElapsedTime(&ms[3], a[1], a[2]) != cudaSuccess ||
+      cudaEventElapsedTime(&ms[4], m[0], m[1]) != cudaSuccess || cudaEventElapsedTime(&ms[5], m[1], m[2]) != cudaSuccess ||
+      cudaEventElapsedTime(&ms[6], m[2], m[3]) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return 0;
 }
 
 int eshkol_b200_get_phase_times(float* ms, int capacity) {
-  if (!g.ready || !ms || capacity < 7 || !g.ev_valid) return -1;
+  if (!g.ready || !ms || capacity < 7 || !g.ev_valid || g.n_evb == 0) return -1;
   if (cudaStreamSynchronize(g.stream) != cudaSuccess) { cudaGetLastError(); return -1; }
-  // events 0-2 bracket the B side (scan + scales, split), events 3-8 the A side
-  static const int from[7] = {0, 1, 3, 4, 5, 6, 7};
-  const int serial = g.bands_timed > 0 ? 2 : 7;
-  for (int i = 0; i < serial; ++i)
-    if (cudaEventElapsedTime(&ms[i], g.ev[from[i]], g.ev[from[i] + 1]) != cudaSuccess) { cudaGetLastError(); return -1; }
-  if (g.bands_timed > 0) {
+  const bool banded = g.bands_timed > 0;
+  if (!banded && (g.n_eva == 0 || g.n_evm == 0)) return -1;
+  if (phase_entry(g.n_evb - 1, g.n_eva - 1, g.n_evm - 1, ms, !banded) != 0) return -1;
+  if (banded) {
     // band pipeline: each stage is the sum over the bands of its own kernels' time on its own
     // stream; the stages overlap, so they add up to more than the product took
     for (int i = 2; i < 7; ++i) ms[i] = 0.f;
@@ -1440,6 +1482,36 @@ int eshkol_b200_get_phase_times(float* ms, int capacity) {
   }
   if (capacity >= 8) ms[7] = 0.f;
   return 7;
+}
+
+int eshkol_b200_get_phase_totals(float ms[7], int counts[3]) {
+  if (!g.ready || !ms || !counts || !g.ev_made) return -1;
+  if (cudaStreamSynchronize(g.stream) != cudaSuccess) { cudaGetLastError(); return -1; }
+  for (int i = 0; i < 7; ++i) ms[i] = 0.f;
+  const unsigned long long R = State::kEvRing;
+  const unsigned long long nb = g.n_evb < R ? g.n_evb : R, na = g.n_eva < R ? g.n_eva : R,
+                           nm = g.n_evm < R ? g.n_evm : R;
+  float t = 0.f;
+#define B200_ADD(slot, e0, e1)                                                          \
+  do {                                                                                  \
+    if (cudaEventElapsedTime(&t, e0, e1) != cudaSuccess) { cudaGetLastError(); return -1; } \
+    ms[slot] += t;                                                                      \
+  } while (0)
+  for (unsigned long long i = g.n_evb - nb; i < g.n_evb; ++i) {
+    const cudaEvent_t* b = g.ev_b[i % R];
+    B200_ADD(0, b[0], b[1]); B200_ADD(1, b[1], b[2]);
+  }
+  for (unsigned long long i = g.n_eva - na; i < g.n_eva; ++i) {
+    const cudaEvent_t* a = g.ev_a[i % R];
+    B200_ADD(2, a[0], a[1]); B200_ADD(3, a[1], a[2]);
+  }
+  for (unsigned long long i = g.n_evm - nm; i < g.n_evm; ++i) {
+    const cudaEvent_t* m = g.ev_m[i % R];
+    B200_ADD(4, m[0], m[1]); B200_ADD(5, m[1], m[2]); B200_ADD(6, m[2], m[3]);
+  }
+#undef B200_ADD
+  counts[0] = static_cast<int>(nb); counts[1] = static_cast<int>(na); counts[2] = static_cast<int>(nm);
+  return 0;
 }
 
 uint64_t eshkol_b200_launch_count(void) { return g.launches; }

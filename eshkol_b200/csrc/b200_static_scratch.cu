@@ -27,10 +27,13 @@
 // stream; two calls made to overlap on the GPU by other means would race on the
 // array and must not be issued.
 //
-// Set-up: the first call on a device asks the runtime for the array's device
-// address (the array's name is only a host-side handle; it is not an address a
-// kernel can use).  That first call should be made before any stream capture
-// begins.
+// Set-up: eshkol_b200_init asks the runtime for the array's device address on the
+// device it selects (the array's name is only a host-side handle; it is not an
+// address a kernel can use) and fails if that does not work.  The CUDA runtime
+// loads this module, and with it the 24 MiB, at that moment -- so a host whose
+// arena takes all remaining device memory must call eshkol_b200_init first, and
+// the GEMM entry point itself never triggers a module load or an allocation.
+// eshkol_b200_init should be called before any stream capture begins.
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
@@ -51,24 +54,11 @@ namespace {
 constexpr int kMaxDevices = 64;
 unsigned char* s_scratch_ptr[kMaxDevices] = {};
 
-// Device address of the scratch array on the current device, resolved once per device.
+// Device address of the scratch array on the library's device (resolved by
+// static_scratch_setup at init), or null.
 unsigned char* scratch_base() {
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
-    cudaGetLastError();
-    return nullptr;
-  }
-  if (!s_scratch_ptr[dev]) {
-    unsigned char* p = nullptr;
-    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch);
-    if (e != cudaSuccess || !p) {
-      fprintf(stderr, "[eshkol-b200] cudaGetSymbolAddress(static scratch) failed: %s\n",
-              cudaGetErrorString(e));
-      cudaGetLastError();
-      return nullptr;
-    }
-    s_scratch_ptr[dev] = p;
-  }
+  const int dev = lib_device();
+  if (dev < 0 || dev >= kMaxDevices) return nullptr;
   return s_scratch_ptr[dev];
 }
 
@@ -160,6 +150,23 @@ Layout scratch_need(long long M, long long K, long long N) {
   } while (0)
 
 }  // namespace
+
+// Called by eshkol_b200_init with `device` current: resolves the array's address on that
+// device once.  This is the only place the symbol is looked up.
+int static_scratch_setup(int device) {
+  if (device < 0 || device >= kMaxDevices) return -1;
+  if (s_scratch_ptr[device]) return 0;
+  unsigned char* p = nullptr;
+  const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_scratch);
+  if (e != cudaSuccess || !p) {
+    fprintf(stderr, "[eshkol-b200] cudaGetSymbolAddress(static scratch) failed: %s\n", cudaGetErrorString(e));
+    cudaGetLastError();
+    return -1;
+  }
+  s_scratch_ptr[device] = p;
+  return 0;
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -187,7 +194,10 @@ extern "C" int eshkol_b200_gemm_f64_static_scratch(const double* dA, const doubl
     return -1;
   }
   unsigned char* ws = scratch_base();
-  if (!ws) return -1;
+  if (!ws) {
+    fprintf(stderr, "[eshkol-b200] static-scratch gemm: the scratch array was not resolved at init\n");
+    return -1;
+  }
 
   double* amax = reinterpret_cast<double*>(ws + L.o_amax);
   double* bmax = reinterpret_cast<double*>(ws + L.o_bmax);

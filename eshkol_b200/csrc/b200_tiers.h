@@ -14,6 +14,7 @@ namespace b200 {
 uint8_t* workspace_reserve(size_t bytes);  // grow-only scratch, nullptr on failure
 uint8_t* aux_reserve(size_t bytes);        // second grow-only block (outlives a nested GEMM)
 cudaStream_t lib_stream();
+int lib_device();  // the device eshkol_b200_init selected, -1 before init
 int lib_num_sms();
 int* lib_status_word();
 void count_launches(int n);
@@ -41,6 +42,8 @@ int f16_gemm(const double* dA, const double* dB, double* dC, long long batch, lo
              long long N);
 int f32_gemm(const float* dA, const float* dB, float* dC, long long M, long long K, long long N);
 cudaError_t tiers_set_attributes();
+// b200_static_scratch.cu: resolve the fixed scratch array's address on `device` (current)
+int static_scratch_setup(int device);
 // dst[cols x rows] = transpose of src[rows x cols] (row-major f64)
 cudaError_t launch_transpose(const double* src, long long rows, long long cols, double* dst, cudaStream_t st);
 cudaError_t launch_elementwise(const double* a, const double* b, double* out, long long n, int op,

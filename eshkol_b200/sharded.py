@@ -17,6 +17,39 @@ import torch
 import torch.distributed as dist
 
 
+def panel_columns(N: int, panels: int, taper) -> list[tuple[int, int]]:
+    """(first column, width) of every column panel of B.
+
+    taper False / None: `panels` equal panels.  "half": a first and a last panel of half the
+    width.  "geometric": widths w/8, w/4, w/2 at either end (w = N / panels) and the rest in
+    panels - 2 (at least one) equal middle panels -- the first panel's way to the ranks and the
+    last panel's way back are the two transfers no products hide, and a panel only has to arrive
+    before the products of the one before it end, which a doubling of the width still allows
+    (moving a column costs about a third of multiplying by it).  Widths stay multiples of 256
+    (the products kernel's tile); a shape that does not allow that gets equal panels."""
+    if panels <= 0 or N % panels != 0:
+        panels = 1
+    w = N // panels
+    equal = [(p * w, w) for p in range(panels)]
+    if taper in (True, "half") and panels >= 2 and w % 512 == 0:
+        h = w // 2
+        return [(0, h)] + [(h + i * w, w) for i in range(panels - 1)] + [(N - h, h)]
+    if taper == "geometric" and panels >= 2 and w % 2048 == 0:
+        ramp = [w // 8, w // 4, w // 2]
+        mid_total = N - 2 * sum(ramp)
+        n_mid = max(1, panels - 2)
+        mid = (mid_total // n_mid) // 256 * 256
+        if mid <= 0:
+            return equal
+        widths = ramp + [mid] * (n_mid - 1) + [mid_total - mid * (n_mid - 1)] + ramp[::-1]
+        out, c0 = [], 0
+        for wd in widths:
+            out.append((c0, wd))
+            c0 += wd
+        return out
+    return equal
+
+
 def row_partition(M: int, world: int) -> list[tuple[int, int]]:
     """(first row, row count) per rank: contiguous blocks, sizes differing by at most one."""
     base, extra = divmod(M, world)
@@ -42,6 +75,15 @@ class _DeviceBackend:
         self.lib = api.load_library()
         self.tier, self.param = tier, param
         self.prepared = tier == 0 and param in (0, 16)
+        # the stream handle is null until the library is initialised, and a null handle would
+        # wrap the legacy default stream: every ordering below would then order the wrong stream
+        index = torch.device(device).index
+        if index is None:
+            index = torch.cuda.current_device()
+        if self.lib.eshkol_b200_init(index) != 0:
+            raise RuntimeError("eshkol_b200_init failed: no usable sm_100 device")
+        if not api.stream_handle():
+            raise RuntimeError("the library reports no stream after eshkol_b200_init")
         self.stream = torch.cuda.ExternalStream(api.stream_handle(), device=device)
         if comm_sms > 0:
             # the persistent products kernels leave these SMs to the collectives' kernels
@@ -114,7 +156,7 @@ class ShardedGemm:
 
     def __init__(self, M: int, K: int, N: int, device, *, tier: int = 0, param: int = 0, src: int = 0,
                  group=None, gemm: Optional[Callable] = None, panels: int = 1, comm_sms: int = 0,
-                 transport: str = "collectives", taper: bool = False):
+                 transport: str = "collectives", taper=False):
         self.M, self.K, self.N = M, K, N
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -129,11 +171,10 @@ class ShardedGemm:
         self.trace = None  # set to [] to collect (label, CUDA event) marks of the next step
         self.panels = panels if (panels > 0 and N % panels == 0) else 1
         self.width = N // self.panels
-        # column range of every panel: equal widths, or (taper, copy-engine transport only) a first
-        # and a last panel of half the width, because the first panel's way to the ranks and the
-        # last panel's way back are the two transfers no products hide
+        # column range of every panel: equal widths, or (copy-engine transport only) narrower
+        # panels at either end (panel_columns)
         self.cols = [(p * self.width, self.width) for p in range(self.panels)]
-        self._taper_wanted = bool(taper) and self.panels >= 2 and self.width % 512 == 0
+        self._taper_wanted = taper if self.panels >= 2 else False
         if transport not in ("collectives", "copy_engine"):
             raise ValueError(f"unknown transport {transport!r}")
         self.transport = "collectives"
@@ -146,9 +187,7 @@ class ShardedGemm:
             self.ctl = dist.new_group(backend="gloo", timeout=datetime.timedelta(seconds=180))
             uniform = (self.panels, self.width, self.cols)
             if self._taper_wanted:
-                h = self.width // 2
-                self.cols = [(0, h)] + [(h + i * self.width, self.width) for i in range(self.panels - 1)] + \
-                            [(N - h, h)]
+                self.cols = panel_columns(N, self.panels, self._taper_wanted)
                 self.panels = len(self.cols)
             try:
                 self._open_peers()
@@ -161,6 +200,10 @@ class ShardedGemm:
             if int(agreed.item()) == 1:
                 self.transport = "copy_engine"
             else:
+                # falling back together: give back whatever was opened or made on the way
+                self._closed = False
+                self.close()
+                self._closed = False
                 self.panels, self.width, self.cols = uniform
         if self.transport != "copy_engine":
             # panel-major copy of B: panel p is the contiguous K x width block of columns p*width ...
@@ -186,6 +229,12 @@ class ShardedGemm:
             self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f8", "data": (self.ptr, False),
                                              "version": 2, "strides": None}
             self.tensor = torch.as_tensor(self, device=device)
+
+        def free(self) -> None:
+            if self.ptr:
+                self.tensor = None
+                self.lib.eshkol_b200_mem_free(0, self.ptr)
+                self.ptr = 0
 
         def handle(self) -> bytes:
             buf = ctypes.create_string_buffer(64)
@@ -290,6 +339,41 @@ class ShardedGemm:
         self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(min(4, max(1, W - 1)))]
         self._k_parts = row_partition(self.K, W)
         torch.cuda.synchronize(self.device)
+
+    def close(self) -> None:
+        """Give back what the constructor took: imported peer memory is closed, the hand-off
+        events destroyed and the two library blocks freed, after every rank has finished with
+        them.  The object must not be used afterwards.  Every rank has to call it."""
+        if getattr(self, "_closed", False):
+            return
+        self._closed = True
+        if self.backend.on_device:
+            torch.cuda.synchronize(self.device)
+        ctl = getattr(self, "ctl", None)
+        if ctl is not None:
+            dist.barrier(group=ctl)  # no peer still reads this rank's blocks
+        lib = getattr(self.backend, "lib", None)
+        if lib is not None:
+            for table in (getattr(self, "_addr_B", None), getattr(self, "_addr_C", None)):
+                for q, addr in enumerate(table or []):
+                    if addr and q != self.rank:
+                        lib.eshkol_b200_ipc_close_mem(addr)
+            for table in (getattr(self, "_ev_packed", None), getattr(self, "_ev_slice", None),
+                          getattr(self, "_ev_block", None)):
+                for evs in table or []:
+                    for ev in evs or []:
+                        if ev:
+                            lib.eshkol_b200_event_destroy(ev)
+            if ctl is not None:
+                dist.barrier(group=ctl)  # every import is closed before its owner frees the memory
+            self.Bp = self.C = None
+            for name in ("_blk_B", "_blk_C"):
+                blk = getattr(self, name, None)
+                if blk is not None:
+                    blk.free()
+                    setattr(self, name, None)
+        self._addr_B = self._addr_C = self._ev_packed = self._ev_slice = self._ev_block = None
+        self.Bp = self.C = self.Cp = None
 
     def _record(self, ev: int, stream) -> None:
         if self.backend.lib.eshkol_b200_event_record(ev, stream.cuda_stream) != 0:

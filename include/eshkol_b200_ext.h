@@ -178,9 +178,11 @@ int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, 
  * exceeds the array (roughly 16*(M+N)*K + 17*M*N bytes after padding; 512x512x512
  * and 256x2048x256 fit) are refused with a message and -1.  Calls share the array:
  * they are ordered on the library stream and must not be made to overlap on the GPU.
- * The first call on a device resolves the array's address and should come before
- * any stream capture.  Asynchronous.  This entry point has no counterpart in the
- * reference. */
+ * eshkol_b200_init resolves the array's address on its device (that is when the CUDA
+ * runtime loads the array's module and takes the 24 MiB), so a host that hands the
+ * rest of device memory to its own arena must call eshkol_b200_init before it does,
+ * and before any stream capture.  Asynchronous.  This entry point has no counterpart
+ * in the reference. */
 int eshkol_b200_gemm_f64_static_scratch(const double* dA, const double* dB, double* dC,
                                         uint64_t M, uint64_t K, uint64_t N);
 
@@ -283,6 +285,12 @@ void eshkol_b200_set_row_bands(long long rows);
  * or -1 when nothing was timed. */
 void eshkol_b200_set_phase_timing(int on);
 int eshkol_b200_get_phase_times(float* ms, int capacity);
+/* The same seven stages summed over every stage call made since timing was switched on
+ * (at most the last 256 calls of each group are kept): counts[0] = right-hand operands
+ * prepared, counts[1] = left-hand operands prepared, counts[2] = multiplications.  The
+ * multi-GPU driver prepares A once and B once per column panel, so the three counts differ
+ * there.  Waits for the stream.  Returns 0, or -1 when timing was never switched on. */
+int eshkol_b200_get_phase_totals(float ms[7], int counts[3]);
 
 /* Number of kernels this library has launched since init (monotonic). */
 uint64_t eshkol_b200_launch_count(void);

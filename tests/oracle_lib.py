@@ -133,6 +133,27 @@ def ref_lib(name: str):
     return ctypes.CDLL(path)
 
 
+def set_threads(n: int) -> int:
+    """Thread count of the oracle's OpenMP loops (libgomp reads OMP_NUM_THREADS only when it is
+    loaded, and launchers such as torch.distributed.run export OMP_NUM_THREADS=1).  Returns the
+    count in force."""
+    L = lib()
+    if n > 0:
+        L.omp_set_num_threads(int(n))
+    return int(L.omp_get_max_threads())
+
+
+def ref_blas_threads(n: int = 0) -> int:
+    """Set (n > 0) and read back the thread count of the OpenBLAS the reference's cblas path is
+    linked against; 0 when that library is not built."""
+    L = ref_lib("libref_matmul_blas.so")
+    if L is None:
+        return 0
+    if n > 0:
+        L.openblas_set_num_threads(int(n))
+    return int(L.openblas_get_num_threads())
+
+
 def ref_matmul(A, B, blas: bool = False):
     L = ref_lib("libref_matmul_blas.so" if blas else "libref_matmul_simd.so")
     if L is None:

@@ -301,6 +301,68 @@ def test_row_band_pipeline_stage_times(gpu_lib):
     assert gu.same_bits(got, again)
 
 
+def _device_gemm(dA, dB):
+    import torch
+    M, K = dA.shape
+    N = dB.shape[1]
+    dC = torch.full((M, N), float("nan"), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    api.gemm_device(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), M, K, N, api.make_opts(eb.TIER_OZAKI2, 16))
+    assert api.sync_status() == 0
+    return dC
+
+
+def test_c3_8192_cubed_normal_64_rows_and_64_columns(gpu_lib):
+    """The benchmarked single-GPU configuration itself: 8192^3, standard-normal operands, exact
+    tier.  64 random full rows and 64 random full columns of the result, bit for bit against the
+    oracle (rows and columns of the exact tier are independent given E = 52).  The operands are
+    generated on the device and the oracle gets the very same bits copied back."""
+    import torch
+    n = 8192
+    ol.set_threads(len(__import__("os").sched_getaffinity(0)))
+    dA = inputs.normal(1, (n, n), device="cuda")
+    dB = inputs.normal(2, (n, n), device="cuda")
+    dC = _device_gemm(dA, dB)
+    g = torch.Generator().manual_seed(83)
+    rows = torch.randperm(n, generator=g)[:64].sort().values.cuda()
+    cols = torch.randperm(n, generator=g)[:64].sort().values.cuda()
+    B_host = dB.cpu().numpy()
+    want = ol.oz2_exact(dA[rows].cpu().numpy(), B_host, 52)
+    assert gu.same_bits(dC[rows].cpu().numpy(), want)
+    want = ol.oz2_exact(dA.cpu().numpy(), np.ascontiguousarray(B_host[:, cols.cpu().numpy()]), 52)
+    assert gu.same_bits(dC[:, cols].contiguous().cpu().numpy(), want)
+
+
+def test_sharded_configuration_depth_64_rows(gpu_lib):
+    """K = 32768, the depth of the multi-GPU configuration (33 extraction chunks): 64 rows of A
+    taken from all over the 32768-row operand of that configuration against 2048 columns, bit for
+    bit against the oracle."""
+    K = 32768
+    ol.set_threads(len(__import__("os").sched_getaffinity(0)))
+    picks = [int(x) for x in np.random.default_rng(7).choice(32768, size=64, replace=False)]
+    A = np.concatenate([inputs.uniform(1, (1, K), start=r * K) for r in sorted(picks)])
+    B = inputs.uniform(2, (K, 2048))
+    assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, 52))
+
+
+@pytest.mark.parametrize("tier,param", [(eb.TIER_OZAKI2, 16), (eb.TIER_OZAKI1, 5)])
+def test_sharded_driver_on_one_device(gpu_lib, tier, param):
+    """The row-sharded driver with one rank on the device: several column panels through the
+    prepared-operand entry points (exact tier) or whole products per panel (slice tier), every
+    hand-off ordered by stream events on the library's own stream.  Same bits as one product."""
+    import torch
+    from eshkol_b200.sharded import ShardedGemm
+    M, K, N = 384, 1500, 1024
+    A = torch.from_numpy(inputs.full53(91, (M, K))).cuda()
+    B = torch.from_numpy(inputs.full53(92, (K, N))).cuda()
+    sg = ShardedGemm(M, K, N, torch.device("cuda", torch.cuda.current_device()), tier=tier, param=param, panels=4)
+    for _ in range(2):
+        C = sg.step(A, B).clone()
+    want = gu.gemm(A.cpu().numpy(), B.cpu().numpy(), tier=tier, param=param)
+    assert gu.same_bits(C.cpu().numpy(), want)
+    sg.close()
+
+
 def test_sharded_configuration_depth_sampled_rows(gpu_lib):
     """K = 32768 (33 extraction chunks), the depth of the multi-GPU configuration: a few rows
     of A against 2048 columns of B, bit for bit against the oracle."""

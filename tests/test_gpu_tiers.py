@@ -357,6 +357,50 @@ def test_conv2d_backward_both_gradients(gpu_lib, cfg):
     assert normwise(gX.cpu().numpy(), wantX.astype(np.float64)) < 1e-7
 
 
+@pytest.mark.parametrize("cfg", [(2, 3, 9, 10, 4, 3, 3, 1, 1), (3, 5, 12, 11, 6, 3, 2, 2, 1), (4, 8, 20, 20, 16, 3, 3, 1, 1)])
+def test_conv2d_backward_against_the_reference_cuda_kernels(gpu_lib, tmp_path, cfg):
+    """Both gradients against the reference's own conv2d_backward_input / _kernel kernels
+    (lib/backend/gpu/gpu_cuda_kernels.cu:413-486), compiled from the reference's sources and run on
+    this GPU in a process of its own.  The reference adds one product at a time in f64; the GEMMs
+    here are exact-tier sums, so the two agree to the reference's own rounding: n terms of half an
+    ulp of the running magnitude, plus the exact tier's 2^-25-of-magnitude bound."""
+    import os
+    import subprocess
+    import sys
+    import torch
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.exists(os.path.join(root, "oracle", "_ref", "libref_gpu_cuda.so")):
+        pytest.skip("reference CUDA backend not built (oracle/Makefile target _ref/libref_gpu_cuda.so)")
+    batch, C_in, H, W, C_out, kH, kW, sH, sW = cfg
+    out = str(tmp_path / "ref_conv_backward.npz")
+    r = subprocess.run([sys.executable, os.path.join(root, "tests", "ref_gpu_runner.py"), "conv-backward",
+                        *map(str, cfg), out], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    ref = np.load(out)
+    oH, oW = (H - kH) // sH + 1, (W - kW) // sW + 1
+    X = inputs.uniform(401, (batch, C_in, H, W))
+    Wt = inputs.uniform(402, (C_out, C_in, kH, kW))
+    G = inputs.normal(403, (batch, C_out, oH, oW))
+    dX, dW, dG = (torch.from_numpy(t).cuda() for t in (X, Wt, G))
+    gX = torch.full_like(dX, float("nan"))
+    gK = torch.full_like(dW, float("nan"))
+    torch.cuda.synchronize()
+    opts = api.make_opts(eb.TIER_OZAKI2, 16)
+    dims = (H, W, kH, kW, oH, oW, sH, sW, C_in, C_out, batch)
+    assert gpu_lib.eshkol_b200_conv2d_backward_kernel_f64_device(dG.data_ptr(), dX.data_ptr(), gK.data_ptr(),
+                                                                *dims, ctypes.byref(opts)) == 0
+    assert gpu_lib.eshkol_b200_conv2d_backward_input_f64_device(dG.data_ptr(), dW.data_ptr(), gX.data_ptr(),
+                                                               *dims, ctypes.byref(opts)) == 0
+    assert api.sync_status() == 0
+    nK, nX = batch * oH * oW, C_out * kH * kW
+    magK = float(np.abs(G).sum()) * float(np.abs(X).max())
+    magX = float(np.abs(G).max()) * float(np.abs(Wt).sum())
+    assert np.all(np.abs(gK.cpu().numpy() - ref["grad_kernel"]) <= magK * (2.0 ** -22 + nK * 2.0 ** -53))
+    assert np.all(np.abs(gX.cpu().numpy() - ref["grad_input"]) <= magX * (2.0 ** -22 + nX * 2.0 ** -53))
+    assert normwise(gK.cpu().numpy(), ref["grad_kernel"]) < 1e-7
+    assert normwise(gX.cpu().numpy(), ref["grad_input"]) < 1e-7
+
+
 def test_feed_forward_block(gpu_lib):
     """out = gelu(x W1 + b1) W2 + b2 with the tanh-by-exp GELU of the reference's generated loops
     (lib/backend/tensor_transformer_codegen.cpp:2469-2664), two GEMMs with fused epilogues."""

@@ -40,6 +40,26 @@ def test_static_scratch_gemm_matches_the_allocating_entry_point_twice(gpu_lib):
         assert gu.same_bits(got, want)  # tolerance of the exact-tier tests: none
 
 
+def test_static_scratch_gemm_takes_no_device_memory(gpu_lib):
+    """What the entry point is for: between the moment the caller's buffers exist and the
+    moment the result is there, neither the driver's free-memory figure nor the library's own
+    workspace may move -- the scratch array was taken when eshkol_b200_init loaded it."""
+    import torch
+    A = torch.from_numpy(inputs.uniform(31, (256, 900))).cuda()
+    B = torch.from_numpy(inputs.uniform(32, (900, 256))).cuda()
+    C = torch.empty((256, 256), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    ws0 = api.load_library().eshkol_b200_workspace_bytes()
+    for _ in range(2):
+        assert gpu_lib.eshkol_b200_gemm_f64_static_scratch(A.data_ptr(), B.data_ptr(), C.data_ptr(), 256, 900, 256) == 0
+        assert api.sync_status() == 0
+        free1, _ = torch.cuda.mem_get_info()
+        assert free1 == free0
+        assert api.load_library().eshkol_b200_workspace_bytes() == ws0
+    assert gu.same_bits(C.cpu().numpy(), gu.gemm(A.cpu().numpy(), B.cpu().numpy()))
+
+
 def test_static_scratch_gemm_refuses_what_the_array_cannot_hold(gpu_lib):
     import torch
     n = 2048  # needs far more than the 24 MiB array
