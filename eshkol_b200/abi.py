@@ -32,6 +32,18 @@ class EshkolGPUBuffer(ctypes.Structure):
     ]
 
 
+class EshkolTensor(ctypes.Structure):
+    """eshkol_tensor_t (lib/core/arena_memory.h:768-780): 40 bytes, elements are doubles stored
+    as int64 bit patterns."""
+    _fields_ = [
+        ("dimensions", ctypes.POINTER(ctypes.c_uint64)),
+        ("num_dimensions", ctypes.c_uint64),
+        ("elements", ctypes.POINTER(ctypes.c_int64)),
+        ("total_elements", ctypes.c_uint64),
+        ("dtype", ctypes.c_uint64),
+    ]
+
+
 class GemmOpts(ctypes.Structure):
     _fields_ = [
         ("tier", ctypes.c_int32),
@@ -143,6 +155,20 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_get_phase_totals", ctypes.c_int, [ctypes.POINTER(ctypes.c_float), ctypes.POINTER(ctypes.c_int)])
     sig("eshkol_b200_launch_count", u64, [])
     sig("eshkol_b200_workspace_bytes", u64, [])
+    sig("eshkol_b200_matmul_f64_host_resident", ctypes.c_int, [vp, vp, vp, u64, u64, u64, vp, ctypes.c_int, vp, ctypes.c_int,
+                                                                vp, ctypes.POINTER(u64)])
+    sig("eshkol_b200_prepared_b_token", u64, [])
+    sig("eshkol_b200_transfer_bytes", None, [ctypes.POINTER(u64), ctypes.POINTER(u64)])
+    sig("eshkol_b200_last_gemm_ms", ctypes.c_double, [])
+    sig("eshkol_gpu_set_residency", None, [ctypes.c_int, ctypes.c_size_t])
+    sig("eshkol_gpu_invalidate", None, [vp, ctypes.c_size_t])
+    sig("eshkol_gpu_residency_clear", None, [])
+    sig("eshkol_rt_conv2d", vp, [vp, vp, vp, i64, i64])
+    sig("eshkol_b200_set_tensor_allocator", None, [vp])
+    sig("eshkol_b200_debug_gemm_model", None, [ctypes.c_int, ctypes.POINTER(ctypes.c_double), ctypes.POINTER(ctypes.c_double)])
+    sig("eshkol_b200_debug_gemm_calibrate", None, [ctypes.c_int, ctypes.c_double, ctypes.c_double])
+    sig("eshkol_b200_debug_set_wait_limit_ns", None, [ctypes.c_ulonglong])
+    sig("eshkol_b200_debug_withhold_arrival", None, [ctypes.c_int])
     sig("eshkol_b200_debug_fetch", ctypes.c_int, [ctypes.c_int, ctypes.c_int, vp, u64, ctypes.POINTER(u64)])
     sig("eshkol_b200_debug_choose_tier", None, [u64, u64, u64, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)])
     _lib = lib

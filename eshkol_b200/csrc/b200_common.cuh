@@ -7,8 +7,9 @@
 
 namespace b200 {
 
-// Every wait in the kernels gives up after this much wall time, records a code in
-// the kernel's status word and lets the CTA run its normal teardown (TMEM freed).
+// Every wait in the kernels gives up after this much wall time (a launch parameter; this is
+// its default), records a code in the kernel's status word and lets the CTA run its normal
+// teardown (TMEM freed).
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;
 
 enum KernelStatus : int {
@@ -76,7 +77,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait.  Returns false when the limit passed or another role of this CTA
 // already gave up (abort_flag set); the caller then leaves its loop.
 template <bool kBackoff>
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          unsigned long long limit_ns) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   uint32_t spins = 0;
@@ -84,7 +86,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     if (kBackoff) __nanosleep(32);
     if ((++spins & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) return false;
+      if (globaltimer_ns() - t0 > limit_ns) return false;
     }
   }
   return true;

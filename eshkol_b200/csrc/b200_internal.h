@@ -52,6 +52,10 @@ struct GemmParams {
   uint32_t* tie_bits;
   // kEpiF16: the output is the caller's matrix, not a padded plane: rows / columns that exist
   int out_rows, out_cols;
+  // set by the launchers: how long a bounded wait may last, and (tests only) whether the
+  // producer withholds its first arrival so that the waits of this launch run out
+  unsigned long long wait_ns;
+  int withhold;
 };
 
 // Launchers (b200_modgemm.cu).  bn is 128 or 256.
@@ -89,9 +93,25 @@ inline GemmParams make_gemm_params() {
   p.n_chunks = 0;
   p.tie_bits = nullptr;
   p.out_rows = p.out_cols = 0;
+  p.wait_ns = 2000000000ull;
+  p.withhold = 0;
   return p;
 }
 cudaError_t launch_modgemm_simt(int epi, const SimtPlanes& pl, const GemmParams& prm,
                                 cudaStream_t stream);
+
+// Test hooks kept by the shim: the wait limit the launchers hand to the kernels, and a
+// one-shot request to withhold a producer arrival (cleared by the call that reads it).
+unsigned long long lib_wait_limit_ns();
+int lib_take_withhold();
+
+// Host <-> device copies on stream st (b200_staging.cu).  Pinned or registered host memory:
+// one cudaMemcpyAsync.  Pageable host memory: chunks through rings of pinned slots, the host
+// side of each chunk copied by a small thread pool; a download's last hop into the caller's
+// memory happens lazily, at the latest in staged_finish.
+cudaError_t staged_upload(void* dst_dev, const void* src_host, size_t bytes, cudaStream_t st);
+cudaError_t staged_download(void* dst_host, const void* src_dev, size_t bytes, cudaStream_t st);
+cudaError_t staged_finish(cudaStream_t st);
+void staged_shutdown();
 
 }  // namespace b200

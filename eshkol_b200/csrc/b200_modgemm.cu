@@ -122,7 +122,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int w = blockIdx.x;
       for (uint32_t item = 0; ok; ++item) {
         const uint32_t slot = item & 1u, sphase = (item >> 1) & 1u;
-        if (!mbar_wait<false>(&sched_empty[slot], sphase ^ 1u, &abort_flag)) {
+        if (!mbar_wait<false>(&sched_empty[slot], sphase ^ 1u, &abort_flag, prm.wait_ns)) {
           atomicCAS(prm.status, kStatusOk, kStatusProducerTimeout);
           abort_flag = 1;
           break;
@@ -136,11 +136,16 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int seg = 0; seg < nseg && ok; ++seg) {
           const int ap = job->a_plane[seg], bp = job->b_plane[seg];
           for (int kb = 0; kb < prm.kb_per_seg; ++kb) {
-            if (!mbar_wait<false>(&empty_bar[stage], phase ^ 1u, &abort_flag)) {
+            if (!mbar_wait<false>(&empty_bar[stage], phase ^ 1u, &abort_flag, prm.wait_ns)) {
               atomicCAS(prm.status, kStatusOk, kStatusProducerTimeout);
               abort_flag = 1;
               ok = false;
               break;
+            }
+            if (prm.withhold && item == 0 && seg == 0 && kb == 0) {
+              // tests: this stage is never filled, so the MMA lane's wait for it runs out
+              if (++stage == kStages) { stage = 0; phase ^= 1u; }
+              continue;
             }
             mbar_arrive_expect_tx(&full_bar[stage], kABytes + kBBytes);
             tma_load_3d(tiles + stage * kABytes, &tmA, &full_bar[stage], kb * kBK, it.tm * kBM, ap);
@@ -157,7 +162,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // leaving early: let every copy this thread started land before the CTA exits
         int none = 0;
         for (int s = 0; s < kStages; ++s)
-          if (issued & (1u << s)) mbar_wait<true>(&full_bar[s], (last_parity >> s) & 1u, &none);
+          if (issued & (1u << s)) mbar_wait<true>(&full_bar[s], (last_parity >> s) & 1u, &none, prm.wait_ns);
       }
     }
   } else if (warp == 1) {
@@ -169,7 +174,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       bool ok = true;
       for (uint32_t item = 0; ok; ++item) {
         const uint32_t slot = item & 1u, sphase = (item >> 1) & 1u;
-        if (!mbar_wait<false>(&sched_full[slot], sphase, &abort_flag)) {
+        if (!mbar_wait<false>(&sched_full[slot], sphase, &abort_flag, prm.wait_ns)) {
           atomicCAS(prm.status, kStatusOk, kStatusMmaTimeout);
           abort_flag = 1;
           break;
@@ -182,7 +187,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         for (int kb0 = 0; kb0 < kb_total && ok; kb0 += prm.kb_per_unit) {
           const int kb1 = min(kb0 + prm.kb_per_unit, kb_total);
           const uint32_t buf = unit & 1u, aphase = (unit >> 1) & 1u;
-          if (!mbar_wait<false>(&acc_empty[buf], aphase ^ 1u, &abort_flag)) {
+          if (!mbar_wait<false>(&acc_empty[buf], aphase ^ 1u, &abort_flag, prm.wait_ns)) {
             atomicCAS(prm.status, kStatusOk, kStatusMmaTimeout);
             abort_flag = 1;
             ok = false;
@@ -191,7 +196,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + buf * BN;
           for (int kb = kb0; kb < kb1; ++kb) {
-            if (!mbar_wait<false>(&full_bar[stage], phase, &abort_flag)) {
+            if (!mbar_wait<false>(&full_bar[stage], phase, &abort_flag, prm.wait_ns)) {
               atomicCAS(prm.status, kStatusOk, kStatusMmaTimeout);
               abort_flag = 1;
               ok = false;
@@ -224,7 +229,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     bool ok = true;
     for (uint32_t item = 0; ok; ++item) {
       const uint32_t slot = item & 1u, sphase = (item >> 1) & 1u;
-      if (!mbar_wait<true>(&sched_full[slot], sphase, &abort_flag)) {
+      if (!mbar_wait<true>(&sched_full[slot], sphase, &abort_flag, prm.wait_ns)) {
         atomicCAS(prm.status, kStatusOk, kStatusEpilogueTimeout);
         abort_flag = 1;
         break;
@@ -255,7 +260,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         int chunk = 0;
         for (int kb0 = 0; kb0 < kb_total && ok; kb0 += prm.kb_per_unit, ++chunk) {
           const uint32_t buf = unit & 1u, aphase = (unit >> 1) & 1u;
-          if (!mbar_wait<true>(&acc_full[buf], aphase, &abort_flag)) {
+          if (!mbar_wait<true>(&acc_full[buf], aphase, &abort_flag, prm.wait_ns)) {
             atomicCAS(prm.status, kStatusOk, kStatusEpilogueTimeout);
             abort_flag = 1;
             ok = false;
@@ -274,7 +279,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const uint32_t pr = __byte_perm(v[2 * p2], v[2 * p2 + 1], 0x5410);  // low halves
               const uint32_t t = pr & 0x00ff00ffu;
               const uint32_t gt = (t + 0x007f007fu) & 0x01000100u;   // 256 where t > 128
-              wsum[c2 * 16 + p2] += t + gt;                          // lanes stay below 2^16
+              wsum[c2 * 16 + p2] += t + gt;                          // lanes stay below 2^16 (masked below)
               const uint32_t x = t ^ 0x00800080u;                    // zero lane <=> t == 128
               const uint32_t z = (x - 0x00010001u) & ~x & 0x80008000u;
               tie |= __funnelshift_r(z, z, (15 - p2) & 31);
@@ -289,6 +294,12 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_before();
           mbar_arrive(&acc_empty[buf]);
           ++unit;
+          if ((chunk & 63) == 63) {
+            // only the sums modulo 512 are wanted: fold before a 16-bit lane can carry into its
+            // neighbour (64 chunks add at most 64 * 511 to a lane below 512)
+#pragma unroll
+            for (int i = 0; i < BN / 4; ++i) wsum[i] &= 0x01ff01ffu;
+          }
         }
         if (ok) {
           // sum of the chunk residues modulo 512, ties counted as +128; the reconstruction
@@ -301,8 +312,16 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                            wsum[i + 3] & 0x01ff01ffu);
         }
       } else {
+       // One accumulator hand-off per tile, except for a residue product deeper than the int32
+       // accumulator is exact for: it is handed over every kb_per_unit k-blocks (the reference
+       // extracts every 1008 elements and sums the residues, metal_softfloat.h:4054-4067; for an
+       // odd modulus only the class of the sum matters, so any interval will do) and each later
+       // part is reduced together with the residue already stored.
+       const int kb_total_i = job->n_seg * prm.kb_per_seg;
+       for (int kb0 = 0; kb0 < kb_total_i && ok; kb0 += prm.kb_per_unit) {
+        const bool later_part = (EPI == kEpiModI8) && kb0 > 0;
         const uint32_t buf = unit & 1u, aphase = (unit >> 1) & 1u;
-        if (!mbar_wait<true>(&acc_full[buf], aphase, &abort_flag)) {
+        if (!mbar_wait<true>(&acc_full[buf], aphase, &abort_flag, prm.wait_ns)) {
           atomicCAS(prm.status, kStatusOk, kStatusEpilogueTimeout);
           abort_flag = 1;
           ok = false;
@@ -346,6 +365,17 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             }
           } else if (EPI == kEpiModI8) {
             uint32_t o[8];
+            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out_plane) + elem0 + cc * 32);
+            if (later_part) {
+              // add the residue of the parts before (|r| <= 127, the sum stays inside int32)
+              const uint4 p0 = dst[0], p1 = dst[1];
+              const uint32_t prev[8] = {p0.x, p0.y, p0.z, p0.w, p1.x, p1.y, p1.z, p1.w};
+#pragma unroll
+              for (int g = 0; g < 8; ++g)
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                  v[g * 4 + b] += static_cast<uint32_t>(static_cast<int>(static_cast<int8_t>((prev[g] >> (8 * b)) & 0xffu)));
+            }
 #pragma unroll
             for (int g = 0; g < 8; ++g) {
               uint32_t word = 0;
@@ -361,7 +391,6 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               }
               o[g] = word;
             }
-            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<int8_t*>(out_plane) + elem0 + cc * 32);
             dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
             dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
           } else {
@@ -374,6 +403,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         tc_fence_before();
         mbar_arrive(&acc_empty[buf]);
         ++unit;
+       }
       }
     }
   }
@@ -398,7 +428,10 @@ cudaError_t launch_one(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   if (grid <= 0) return cudaSuccess;
   const cudaError_t e = cudaMemsetAsync(prm.work_counter, 0, sizeof(int), stream);
   if (e != cudaSuccess) return e;
-  modgemm_kernel<BN, EPI><<<grid, EpiShape<EPI>::kThreads, smem_bytes<BN>(), stream>>>(tmA, tmB, prm, total_work);
+  GemmParams p = prm;
+  p.wait_ns = lib_wait_limit_ns();
+  p.withhold = lib_take_withhold();
+  modgemm_kernel<BN, EPI><<<grid, EpiShape<EPI>::kThreads, smem_bytes<BN>(), stream>>>(tmA, tmB, p, total_work);
   return cudaGetLastError();
 }
 
@@ -436,7 +469,7 @@ __global__ void modgemm_simt_kernel(int epi, SimtPlanes pl, GemmParams prm, int 
     reinterpret_cast<int16_t*>(out_plane)[o] = static_cast<int16_t>(static_cast<uint32_t>(w) & 511u);
     return;
   }
-  int acc = 0;
+  long long acc = 0;  // a residue product may be deeper than int32 holds
   for (int s = 0; s < job->n_seg; ++s) {
     const int8_t* a = pl.a_base + static_cast<long long>(job->a_plane[s]) * pl.a_plane_stride +
                       static_cast<long long>(i) * pl.lda;
@@ -445,10 +478,10 @@ __global__ void modgemm_simt_kernel(int epi, SimtPlanes pl, GemmParams prm, int 
     for (int k = 0; k < K_per_seg; ++k) acc += static_cast<int>(a[k]) * static_cast<int>(b[k]);
   }
   if (epi == kEpiRawI32) {
-    reinterpret_cast<int32_t*>(out_plane)[o] = acc;
+    reinterpret_cast<int32_t*>(out_plane)[o] = static_cast<int32_t>(acc);
   } else {
     const int p = static_cast<int>(job->modulus);
-    int r = acc % p;
+    int r = static_cast<int>(acc % p);
     if (r < 0) r += p;
     if (r > (p >> 1)) r -= p;
     reinterpret_cast<int8_t*>(out_plane)[o] = static_cast<int8_t>(r);

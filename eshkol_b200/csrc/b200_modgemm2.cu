@@ -158,6 +158,7 @@ modgemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       tma_prefetch_desc(&tmB);
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t issued = 0, last_parity = 0;
       bool ok = true;
       for (int w = pair; w < total_work && ok; w += npairs) {
         const PairWork it = decode_pair(w, tiles_m2, prm);
@@ -166,7 +167,7 @@ modgemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         for (int seg = 0; seg < nseg && ok; ++seg) {
           const int ap = job->a_plane[seg], bp = job->b_plane[seg];
           for (int kb = 0; kb < prm.kb_per_seg; ++kb) {
-            if (!mbar_wait<false>(&empty_bar[stage], phase ^ 1u, &abort_flag)) {
+            if (!mbar_wait<false>(&empty_bar[stage], phase ^ 1u, &abort_flag, prm.wait_ns)) {
               atomicCAS(prm.status, kStatusOk, kStatusProducerTimeout);
               abort_flag = 1;
               ok = false;
@@ -178,9 +179,20 @@ modgemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                              it.tm * 256 + static_cast<int>(rank) * kBM, ap);
             tma_load_3d_pair(tiles + kStages2 * kABytes2 + stage * kBBytes2, &tmB, leader_full, kb * kBK,
                              it.tn * kBN2 + static_cast<int>(rank) * (kBN2 / 2), bp);
+            issued |= 1u << stage;
+            last_parity = (last_parity & ~(1u << stage)) | (phase << stage);
             if (++stage == kStages2) { stage = 0; phase ^= 1u; }
           }
         }
+      }
+      if ((!ok || abort_flag) && rank == 0) {
+        // leaving early: both CTAs' copies of a stage complete on the leader's barrier, so the
+        // leader waits (bounded) for every stage it armed; the peer cannot leave before the
+        // leader does (the cluster barrier at the end of the kernel), and its own copies, which
+        // take microseconds, have long landed by then
+        int none = 0;
+        for (int s = 0; s < kStages2; ++s)
+          if (issued & (1u << s)) mbar_wait<true>(&full_bar[s], (last_parity >> s) & 1u, &none, prm.wait_ns);
       }
     }
   } else if (warp == 1) {
@@ -194,7 +206,7 @@ modgemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const PairWork it = decode_pair(w, tiles_m2, prm);
         const int kb_total = prm.jobs[it.job].n_seg * prm.kb_per_seg;
         const uint32_t buf = unit & 1u, aphase = (unit >> 1) & 1u;
-        if (!mbar_wait<false>(&acc_empty[buf], aphase ^ 1u, &abort_flag)) {
+        if (!mbar_wait<false>(&acc_empty[buf], aphase ^ 1u, &abort_flag, prm.wait_ns)) {
           atomicCAS(prm.status, kStatusOk, kStatusMmaTimeout);
           abort_flag = 1;
           break;
@@ -202,7 +214,7 @@ modgemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * kBN2;
         for (int kb = 0; kb < kb_total; ++kb) {
-          if (!mbar_wait<false>(&full_bar[stage], phase, &abort_flag)) {
+          if (!mbar_wait<false>(&full_bar[stage], phase, &abort_flag, prm.wait_ns)) {
             atomicCAS(prm.status, kStatusOk, kStatusMmaTimeout);
             abort_flag = 1;
             ok = false;
@@ -234,7 +246,7 @@ modgemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       uint8_t* out_plane = prm.out + static_cast<long long>(job->out_plane) * prm.out_plane_stride;
       const long long elem0 = row * prm.ldo + static_cast<long long>(it.tn) * kBN2;
       const uint32_t buf = unit & 1u, aphase = (unit >> 1) & 1u;
-      if (!mbar_wait<true>(&acc_full[buf], aphase, &abort_flag)) {
+      if (!mbar_wait<true>(&acc_full[buf], aphase, &abort_flag, prm.wait_ns)) {
         atomicCAS(prm.status, kStatusOk, kStatusEpilogueTimeout);
         abort_flag = 1;
         break;
@@ -299,7 +311,10 @@ cudaError_t launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const Ge
   int grid = (num_sms / 2) * 2;
   if (2 * total_work < grid) grid = 2 * total_work;
   if (grid <= 0) return cudaSuccess;
-  modgemm2_kernel<EPI><<<grid, kThreads2, kSmem2, stream>>>(tmA, tmB, prm, tiles_m2, total_work);
+  GemmParams p = prm;
+  p.wait_ns = lib_wait_limit_ns();
+  p.withhold = 0;
+  modgemm2_kernel<EPI><<<grid, kThreads2, kSmem2, stream>>>(tmA, tmB, p, tiles_m2, total_work);
   return cudaGetLastError();
 }
 

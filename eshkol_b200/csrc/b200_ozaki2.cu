@@ -59,20 +59,52 @@ __global__ void __launch_bounds__(256) scan_rows_kernel(const double* __restrict
   if (lane == 0) amax[row] = mx;
 }
 
+// ------------------------------------------------- the operand as an im2col view
+// Where column n of the view starts in the tensor: image base, top-left input coordinate.
+struct ViewColumn {
+  long long base;
+  int ih0, iw0;
+};
+__device__ __forceinline__ ViewColumn view_column(const Im2colView& v, long long n) {
+  const long long ow = n % v.oW, t = n / v.oW;
+  const long long oh = t % v.oH, b = t / v.oH;
+  ViewColumn c;
+  c.base = b * v.in_c * v.H * v.W;
+  c.ih0 = static_cast<int>(oh * v.stride - v.pad);
+  c.iw0 = static_cast<int>(ow * v.stride - v.pad);
+  return c;
+}
+__device__ __forceinline__ double view_load(const Im2colView& v, const ViewColumn& c, long long kk) {
+  const int kw = static_cast<int>(kk % v.kW);
+  const long long t = kk / v.kW;
+  const int kh = static_cast<int>(t % v.kH);
+  const long long ic = t / v.kH;
+  const int ih = c.ih0 + kh, iw = c.iw0 + kw;
+  if (ih < 0 || ih >= v.H || iw < 0 || iw >= v.W) return 0.0;
+  return __ldg(v.in + c.base + (ic * v.H + ih) * v.W + iw);
+}
+
 // ---------------------------------------------------------------- column scan
 // Block = 64 columns x 4 row phases over a slab of rows; partial maxima merge
 // through atomicMax on the bit pattern (order-preserving for non-negative doubles).
 constexpr int kColSlab = 256;
+template <bool kView>
 __global__ void __launch_bounds__(256) scan_cols_kernel(const double* __restrict__ B, long long K,
                                                         long long N,
-                                                        unsigned long long* __restrict__ bmax_bits) {
+                                                        unsigned long long* __restrict__ bmax_bits,
+                                                        const Im2colView view) {
   __shared__ double red[4][64];
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
   const long long j = static_cast<long long>(blockIdx.x) * 64 + tx;
   const long long k0 = static_cast<long long>(blockIdx.y) * kColSlab;
   const long long k1 = (k0 + kColSlab < K) ? k0 + kColSlab : K;
   double mx = 0.0;
-  if (j < N) {
+  if (kView) {
+    if (j < N) {
+      const ViewColumn vc = view_column(view, j);
+      for (long long k = k0 + ty; k < k1; k += 4) mx = dmax_ref(mx, fabs(view_load(view, vc, k)));
+    }
+  } else if (j < N) {
     long long k = k0 + ty;
     for (; k + 12 < k1; k += 16) {
       const double v0 = __ldg(B + k * N + j), v1 = __ldg(B + (k + 4) * N + j),
@@ -233,10 +265,12 @@ __global__ void __launch_bounds__(256) split_a_kernel(const double* __restrict__
 // (row pitch 33 words: conflict-free both ways), then written out as 16-byte
 // vectors along k.
 constexpr int kSplitBJ = 32, kSplitBK = 128, kSplitBPitch = 33;
+template <bool kView>
 __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__ B,
                                                       const double* __restrict__ scale,
                                                       long long N, const SplitGeom g,
-                                                      const __grid_constant__ Oz2DeviceConsts c) {
+                                                      const __grid_constant__ Oz2DeviceConsts c,
+                                                      const __grid_constant__ Im2colView view) {
   extern __shared__ uint32_t sm[];  // [n_odd + 2][32][33]: bytes mod 256, flag nibbles, odd moduli
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const long long j = static_cast<long long>(blockIdx.x) * kSplitBJ + tx;
@@ -246,12 +280,23 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
   // all 16 loads of this thread are issued before any arithmetic: two resident blocks
   // per SM then keep 64 KB of reads in flight, enough to cover HBM latency
   double bv[4][4];
+  if (kView) {
+    const ViewColumn vc = view_column(view, (j < N) ? j : 0);
 #pragma unroll
-  for (int t = 0; t < 4; ++t) {
-    const long long k = kbase + (ty + 8 * t) * 4;
+    for (int t = 0; t < 4; ++t) {
+      const long long k = kbase + (ty + 8 * t) * 4;
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
-      bv[t][e] = (j < N && k + e < g.K) ? __ldg(B + (k + e) * N + j) : 0.0;
+      for (int e = 0; e < 4; ++e)
+        bv[t][e] = (j < N && k + e < g.K) ? view_load(view, vc, k + e) : 0.0;
+    }
+  } else {
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+      const long long k = kbase + (ty + 8 * t) * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        bv[t][e] = (j < N && k + e < g.K) ? __ldg(B + (k + e) * N + j) : 0.0;
+    }
   }
 #pragma unroll
   for (int t = 0; t < 4; ++t) {
@@ -418,13 +463,14 @@ cudaError_t launch_scan_rows(const double* A, long long M, long long K, double* 
 }
 
 cudaError_t launch_scan_cols(const double* B, long long K, long long N,
-                             unsigned long long* bmax_bits, cudaStream_t st) {
+                             unsigned long long* bmax_bits, cudaStream_t st, const Im2colView* view) {
   if (N <= 0 || K <= 0) return cudaSuccess;
   cudaError_t e = cudaMemsetAsync(bmax_bits, 0, static_cast<size_t>(N) * 8, st);
   if (e != cudaSuccess) return e;
   const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((K + kColSlab - 1) / kColSlab));
   if (grid.y > 65535u) return cudaErrorInvalidValue;
-  scan_cols_kernel<<<grid, 256, 0, st>>>(B, K, N, bmax_bits);
+  if (view) scan_cols_kernel<true><<<grid, 256, 0, st>>>(nullptr, K, N, bmax_bits, *view);
+  else scan_cols_kernel<false><<<grid, 256, 0, st>>>(B, K, N, bmax_bits, Im2colView{});
   return cudaGetLastError();
 }
 
@@ -438,6 +484,14 @@ cudaError_t launch_scales(const double* vmax, long long n, int E, int* shift, do
 
 // the padding inside the modulus-256 plane and the unused flag units must read as zero
 static cudaError_t clear_plane0(const SplitPlanes& p, cudaStream_t st) {
+  const size_t fbytes = static_cast<size_t>(p.rows) * p.n_chunks * kChunkUnits * sizeof(uint16_t);
+  const uint8_t* b0 = reinterpret_cast<const uint8_t*>(p.plane0);
+  const uint8_t* f1 = reinterpret_cast<const uint8_t*>(p.flag_hi);
+  const uint8_t* f2 = reinterpret_cast<const uint8_t*>(p.flag_odd);
+  // the drivers carve the three pieces one behind the other: one fill then covers them all
+  if (b0 < f1 && f1 < f2 && static_cast<size_t>(f1 - b0) < static_cast<size_t>(p.rows) * p.K0 + 1024 &&
+      static_cast<size_t>(f2 - f1) < fbytes + 1024)
+    return cudaMemsetAsync(p.plane0, 0, static_cast<size_t>(f2 - b0) + fbytes, st);
   cudaError_t e = cudaMemsetAsync(p.plane0, 0, static_cast<size_t>(p.rows) * p.K0, st);
   if (e != cudaSuccess) return e;
   const size_t fb = static_cast<size_t>(p.rows) * p.n_chunks * kChunkUnits * sizeof(uint16_t);
@@ -470,18 +524,22 @@ size_t split_b_smem_bytes(int n_odd) {
 }
 
 cudaError_t split_set_attributes() {
-  return cudaFuncSetAttribute(split_b_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(split_b_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(split_b_smem_bytes(15)));
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(split_b_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(split_b_smem_bytes(15)));
 }
 
 cudaError_t launch_split_b(const double* B, const double* scale, long long N, const SplitPlanes& p,
-                           const Oz2DeviceConsts& c, cudaStream_t st) {
+                           const Oz2DeviceConsts& c, cudaStream_t st, const Im2colView* view) {
   cudaError_t e = clear_plane0(p, st);
   if (e != cudaSuccess) return e;
   const dim3 grid(static_cast<unsigned>((N + kSplitBJ - 1) / kSplitBJ),
                   static_cast<unsigned>(p.Kp / kSplitBK));
   if (grid.y > 65535u) return cudaErrorInvalidValue;
-  split_b_kernel<<<grid, 256, split_b_smem_bytes(p.n_odd), st>>>(B, scale, N, make_geom(p), c);
+  if (view) split_b_kernel<true><<<grid, 256, split_b_smem_bytes(p.n_odd), st>>>(nullptr, scale, N, make_geom(p), c, *view);
+  else split_b_kernel<false><<<grid, 256, split_b_smem_bytes(p.n_odd), st>>>(B, scale, N, make_geom(p), c, Im2colView{});
   return cudaGetLastError();
 }
 

@@ -44,15 +44,28 @@ struct CrtArgs {
   long long pixels_per_image; // > 0: scatter columns to [image][row][pixel] (conv2d NCHW)
 };
 
+// A right-hand operand that is never materialised: the im2col view of an NCHW tensor.
+// Element (kk, n), kk = (ic*kH + kh)*kW + kw, n = (b*oH + oh)*oW + ow, is
+// in[b][ic][oh*stride + kh - pad][ow*stride + kw - pad], or 0 outside the image (the loop
+// bounds of eshkol_conv2d_kernel, lib/backend/tensor_conv_kernel.h:66-105).  The column scan
+// and the split read the tensor through this map, so HBM sees the tensor once per kernel tap
+// that L2 does not serve instead of a kH*kW times larger f64 matrix written and read back.
+struct Im2colView {
+  const double* in;
+  long long batch, in_c, H, W, kH, kW, stride, pad, oH, oW;
+};
+
 cudaError_t launch_scan_rows(const double* A, long long M, long long K, double* amax, cudaStream_t st);
+// view != nullptr: B is ignored and the K x N operand is the im2col view
 cudaError_t launch_scan_cols(const double* B, long long K, long long N,
-                             unsigned long long* bmax_bits, cudaStream_t st);
+                             unsigned long long* bmax_bits, cudaStream_t st,
+                             const Im2colView* view = nullptr);
 cudaError_t launch_scales(const double* vmax, long long n, int E, int* shift, double* scale,
                           double* inv_scale, cudaStream_t st);
 cudaError_t launch_split_a(const double* A, const double* scale, const SplitPlanes& p,
                            const Oz2DeviceConsts& c, cudaStream_t st);
 cudaError_t launch_split_b(const double* B, const double* scale, long long N, const SplitPlanes& p,
-                           const Oz2DeviceConsts& c, cudaStream_t st);
+                           const Oz2DeviceConsts& c, cudaStream_t st, const Im2colView* view = nullptr);
 cudaError_t split_set_attributes();
 cudaError_t launch_crt(const CrtArgs& a, const Oz2DeviceConsts& c, cudaStream_t st);
 

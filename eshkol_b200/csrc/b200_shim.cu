@@ -2,6 +2,7 @@
 // TMA tensor maps, and the drivers that chain scan -> split -> tensor-core
 // products -> reconstruction for each precision tier.
 #include "../../include/eshkol_b200_ext.h"
+#include "../../include/eshkol_b200_testing.h"
 
 #include <cuda.h>
 #include <cudaTypedefs.h>
@@ -31,6 +32,10 @@ struct State {
   size_t ws_bytes = 0;
   int* d_status = nullptr;
   unsigned long long launches = 0;
+  unsigned long long h2d_bytes = 0, d2h_bytes = 0;  // host <-> device bytes this library has moved
+  cudaEvent_t ev_g0 = nullptr, ev_g1 = nullptr;     // around the last eshkol_b200_gemm_f64_device
+  bool ev_g_valid = false;
+  unsigned long long prep_token = 0;                // bumped whenever a right-hand operand is prepared
   uint8_t* aux = nullptr;  // second scratch block (conv2d im2col operand)
   size_t aux_bytes = 0;
   uint8_t* tbuf = nullptr;  // third scratch block: operands transposed for the tiers that need it
@@ -186,6 +191,10 @@ static uint8_t* tbuf_reserve(size_t bytes) {
 uint8_t* workspace_reserve(size_t bytes) { return ensure_workspace(bytes) == 0 ? g.ws : nullptr; }
 cudaStream_t lib_stream() { return g.stream; }
 int lib_device() { return g.ready ? g.device : -1; }
+static unsigned long long g_dbg_wait_ns = 0;
+static int g_dbg_withhold = 0;
+unsigned long long lib_wait_limit_ns() { return g_dbg_wait_ns ? g_dbg_wait_ns : 2000000000ull; }
+int lib_take_withhold() { const int w = g_dbg_withhold; g_dbg_withhold = 0; return w; }
 static inline int gemm_sms() {
   int n = g.num_sms;
   if (g.sm_limit > 0 && g.sm_limit < n) n = g.sm_limit;
@@ -318,14 +327,23 @@ static Oz2Geom oz2_geometry(long long M, long long K, long long N, int bn) {
   return q;
 }
 
+// k-blocks of 128 an odd-modulus accumulator takes before it is handed to the epilogue:
+// 1023 * 128 * 128^2 < 2^31
+constexpr int kOddUnitKb = 1023;
+// deepest product for which the exponent E is 52 whatever the data (gpu_memory.mm:2510-2512 with
+// log2 P = 125.37 and both fractional parts below 1): beyond it E needs the maxima of both
+// operands, and operands can no longer be prepared one without the other
+constexpr long long kMaxPreparedK = 262144;
+
 static int oz2_check_shape(long long M, long long K, long long N, int n_mod) {
   if (n_mod < 2 || n_mod > 16) {
     fprintf(stderr, "[eshkol-b200] Ozaki-II: moduli count %d outside [2,16]\n", n_mod);
     return -1;
   }
-  // int32 accumulation of K products of magnitude <= 127^2 is exact below this bound
-  if (K > 131071) {
-    fprintf(stderr, "[eshkol-b200] Ozaki-II: K=%lld exceeds the int32-exact bound 131071\n", K);
+  // int32 accumulation of products of magnitude <= 128^2 is exact for 131071 of them; deeper
+  // products hand the accumulator over every kOddUnitKb k-blocks and sum the residues
+  if (K > (1LL << 24)) {
+    fprintf(stderr, "[eshkol-b200] Ozaki-II: K=%lld is beyond what this library accepts (2^24)\n", K);
     return -1;
   }
   if (M > 0x7fffff00LL || N > 0x7fffff00LL) return -1;
@@ -339,8 +357,13 @@ static int oz2_check_shape(long long M, long long K, long long N, int n_mod) {
 // host pipeline, the row-sharded multi-GPU driver) without touching B again.  Only
 // with all 16 moduli, where the exponent E is 52 whatever the data; with fewer moduli
 // E depends on the maxima of both operands and the one-shot path below is used.
-static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, bool trans = false) {
+static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, bool trans = false,
+                         const Im2colView* view = nullptr) {
   if (oz2_check_shape(1, K, N, 16)) return -1;
+  if (K > kMaxPreparedK) {
+    fprintf(stderr, "[eshkol-b200] an operand can be prepared on its own only for K <= %lld\n", kMaxPreparedK);
+    return -1;
+  }
   const Oz2Geom q = oz2_geometry(1, K, N, bn);
   const int n_odd = 15;
   Carver cv;
@@ -383,12 +406,12 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
   // trans: B is stored N x K (each column of the operand is a contiguous row), which is the
   // layout the row scan and the non-transposing split of a left-hand operand read
   if (trans) B200_CHECK(launch_scan_rows(dB, N, K, P.bmax, st));
-  else B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(P.bmax), st));
+  else B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(P.bmax), st, view));
   B200_CHECK(launch_scales(P.bmax, N, 52, P.nu, P.sb, P.sbi, st));
   B200_MARK(1);
   SplitPlanes pb{N, K, q.Kp, q.K0, q.n_chunks, n_odd, P.b0, P.b_hi, P.b_odd, P.bodd, P.bodd_stride};
   if (trans) B200_CHECK(launch_split_a(dB, P.sb, pb, P.consts, st));
-  else B200_CHECK(launch_split_b(dB, P.sb, N, pb, P.consts, st));
+  else B200_CHECK(launch_split_b(dB, P.sb, N, pb, P.consts, st, view));
   B200_MARK(2);
   if (timed) ++g.n_evb;
   g.launches += 3;
@@ -396,6 +419,7 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
   if (make_plane_map(&P.mB1, P.bodd, q.Kp, N, n_odd, P.bodd_stride, bn)) return -1;
   if (make_plane_map(&P.mB1_half, P.bodd, q.Kp, N, n_odd, P.bodd_stride, kBM)) return -1;
   P.valid = true;
+  ++g.prep_token;
   return 0;
 }
 
@@ -540,7 +564,7 @@ static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, d
   GemmParams p1 = p0;
   p1.n_jobs = n_odd;
   p1.kb_per_seg = static_cast<int>(A.Kp / kBK);
-  p1.kb_per_unit = 1 << 28;
+  p1.kb_per_unit = kOddUnitKb;
   p1.jobs = A.jobs + 1;
   p1.out = reinterpret_cast<uint8_t*>(wodd);
   p1.out_plane_stride = static_cast<long long>(w_stride);
@@ -564,7 +588,7 @@ static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, d
     B200_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(P.N), sp));
     if (tev) B200_CHECK(cudaEventRecord(tev[4], sp));
     if (tev) B200_CHECK(cudaEventRecord(tev[1], st));
-    if (g.pair_gemm && P.bn == 256) {
+    if (g.pair_gemm && P.bn == 256 && p1.kb_per_seg <= kOddUnitKb) {
       B200_CHECK(launch_modgemm_pair(kEpiModI8, A.mA1, P.mB1_half, p1, static_cast<int>(A.Mp / (2 * kBM)),
                                      gemm_sms(), st));
     } else {
@@ -801,7 +825,7 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   GemmParams p1 = p0;
   p1.n_jobs = n_odd;
   p1.kb_per_seg = static_cast<int>(q.Kp / kBK);
-  p1.kb_per_unit = 1 << 28;
+  p1.kb_per_unit = kOddUnitKb;
   p1.jobs = d_jobs + 1;
   p1.out = reinterpret_cast<uint8_t*>(wodd);
   p1.out_plane_stride = static_cast<long long>(w_stride);
@@ -847,11 +871,28 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
 
 static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long M, long long K,
                        long long N, int n_mod, const EshkolB200GemmOpts& o) {
-  if (n_mod != 16) return ozaki2_gemm_general(dA, dB, dC, M, K, N, n_mod, o);
+  if (n_mod != 16 || K > kMaxPreparedK) {
+    if (o.trans_a || o.trans_b) {
+      fprintf(stderr, "[eshkol-b200] transposed operands beyond K = %lld are not served\n", kMaxPreparedK);
+      return -1;
+    }
+    return ozaki2_gemm_general(dA, dB, dC, M, K, N, n_mod, o);
+  }
   if (oz2_check_shape(M, K, N, 16)) return -1;
   if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256, o.trans_b != 0)) return -1;
   const int rc = oz2_gemm_rows(dA, dC, M, o, true);
   g.prep.valid = false;  // dB belongs to the caller and may change before the next call
+  return rc;
+}
+
+// Exact tier with the right-hand operand given as an im2col view of an NCHW tensor (conv2d):
+// the view is scanned and split directly, no K x N matrix of doubles exists.
+int ozaki2_exact_gemm_im2col(const double* dA, const Im2colView& view, double* dC, long long M, long long K,
+                             long long N, const EshkolB200GemmOpts& o) {
+  if (oz2_check_shape(M, K, N, 16)) return -1;
+  if (oz2_prepare_b(nullptr, K, N, (o.gemm_tile_n == 128) ? 128 : 256, false, &view)) return -1;
+  const int rc = oz2_gemm_rows(dA, dC, M, o, true);
+  g.prep.valid = false;
   return rc;
 }
 
@@ -860,8 +901,20 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
 // C travels back.  Three streams (upload, compute = the library stream, download) and
 // double-buffered device blocks.  Pinned host memory overlaps fully; pageable memory
 // is staged by the runtime and still produces the same bits.
+// rs (optional): full-size device copies of the three matrices that the caller keeps across
+// calls.  a_state 0: hA is uploaded into rs->dA block by block; 1: rs->dA already holds A.
+// b_state 0: hB is uploaded into rs->dB and prepared; 1: rs->dB already holds B, which is
+// prepared from there; 2: the library's prepared right-hand operand is this B (the caller
+// compared the token), nothing is uploaded or split.  rs->dC receives the whole result, which
+// is also downloaded.  The prepared operand stays valid afterwards.
+struct ResidentSet {
+  double* dA; int a_state;
+  double* dB; int b_state;
+  double* dC;
+};
+
 static int oz2_matmul_host(const double* hA, const double* hB, double* hC, long long M, long long K,
-                           long long N, const EshkolB200GemmOpts& o) {
+                           long long N, const EshkolB200GemmOpts& o, const ResidentSet* rs = nullptr) {
   if (oz2_check_shape(M, K, N, 16)) return -1;
   long long bm = 1024;
   if (M <= 2048) bm = M;  // too small to be worth splitting
@@ -883,15 +936,21 @@ static int oz2_matmul_host(const double* hA, const double* hB, double* hC, long 
   }
   const size_t bytesB = static_cast<size_t>(K) * N * 8;
   const size_t bytesA = static_cast<size_t>(bm) * K * 8, bytesC = static_cast<size_t>(bm) * N * 8;
-  const size_t need = ((bytesB + 1023) & ~size_t(1023)) + 2 * ((bytesA + 1023) & ~size_t(1023)) +
-                      2 * ((bytesC + 1023) & ~size_t(1023));
-  uint8_t* base = aux_reserve(need);
-  if (!base) return -1;
-  double* dB = reinterpret_cast<double*>(base);
-  size_t off = (bytesB + 1023) & ~size_t(1023);
-  double* dA[2]; double* dC[2];
-  for (int i = 0; i < 2; ++i) { dA[i] = reinterpret_cast<double*>(base + off); off += (bytesA + 1023) & ~size_t(1023); }
-  for (int i = 0; i < 2; ++i) { dC[i] = reinterpret_cast<double*>(base + off); off += (bytesC + 1023) & ~size_t(1023); }
+  double* dB = nullptr;
+  double* dA[2] = {nullptr, nullptr};
+  double* dC[2] = {nullptr, nullptr};
+  if (rs) {
+    dB = rs->dB;
+  } else {
+    const size_t need = ((bytesB + 1023) & ~size_t(1023)) + 2 * ((bytesA + 1023) & ~size_t(1023)) +
+                        2 * ((bytesC + 1023) & ~size_t(1023));
+    uint8_t* base = aux_reserve(need);
+    if (!base) return -1;
+    dB = reinterpret_cast<double*>(base);
+    size_t off = (bytesB + 1023) & ~size_t(1023);
+    for (int i = 0; i < 2; ++i) { dA[i] = reinterpret_cast<double*>(base + off); off += (bytesA + 1023) & ~size_t(1023); }
+    for (int i = 0; i < 2; ++i) { dC[i] = reinterpret_cast<double*>(base + off); off += (bytesC + 1023) & ~size_t(1023); }
+  }
   if (!g.pipe_made) {
     B200_CHECK(cudaStreamCreateWithFlags(&g.s_in, cudaStreamNonBlocking));
     B200_CHECK(cudaStreamCreateWithFlags(&g.s_out, cudaStreamNonBlocking));
@@ -905,32 +964,52 @@ static int oz2_matmul_host(const double* hA, const double* hB, double* hC, long 
     g.pipe_made = true;
   }
   cudaStream_t st = g.stream;
-  // earlier work on the compute stream may still read the scratch block
+  const int b_state = rs ? rs->b_state : 0;
+  const bool a_resident = rs && rs->a_state == 1;
+  // earlier work on the compute stream may still read the buffers written below
   B200_CHECK(cudaEventRecord(g.e_b_ready, st));
   B200_CHECK(cudaStreamWaitEvent(g.s_in, g.e_b_ready, 0));
-  B200_CHECK(cudaMemcpyAsync(dB, hB, bytesB, cudaMemcpyHostToDevice, g.s_in));
-  B200_CHECK(cudaEventRecord(g.e_b_ready, g.s_in));
-  // first block of A rides behind B on the upload stream
-  B200_CHECK(cudaStreamWaitEvent(st, g.e_b_ready, 0));
-  if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256)) return -1;
+  B200_CHECK(cudaStreamWaitEvent(g.s_out, g.e_b_ready, 0));
+  if (b_state == 0) {
+    B200_CHECK(staged_upload(dB, hB, bytesB, g.s_in));
+    g.h2d_bytes += bytesB;
+    B200_CHECK(cudaEventRecord(g.e_b_ready, g.s_in));
+    // the first block of A rides behind B on the upload stream
+    B200_CHECK(cudaStreamWaitEvent(st, g.e_b_ready, 0));
+  }
+  if (b_state == 2) {
+    if (!g.prep.valid || g.prep.K != K || g.prep.N != N) {
+      fprintf(stderr, "[eshkol-b200] the prepared right-hand operand is not the one the caller expects\n");
+      return -1;
+    }
+  } else if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256)) {
+    return -1;
+  }
   int rc = 0;
   for (int i = 0; i < nblk && rc == 0; ++i) {
     const int s = i & 1;
     const long long r0 = blk_r0[i], rows = blk_rows[i];
-    if (i >= 2) B200_CHECK(cudaStreamWaitEvent(g.s_in, g.e_a_free[s], 0));
-    B200_CHECK(cudaMemcpyAsync(dA[s], hA + r0 * K, static_cast<size_t>(rows) * K * 8, cudaMemcpyHostToDevice, g.s_in));
-    B200_CHECK(cudaEventRecord(g.e_a_ready[s], g.s_in));
-    B200_CHECK(cudaStreamWaitEvent(st, g.e_a_ready[s], 0));
-    if (i >= 2) B200_CHECK(cudaStreamWaitEvent(st, g.e_c_free[s], 0));
-    rc = oz2_gemm_rows(dA[s], dC[s], rows, o, false);
+    double* a_blk = rs ? rs->dA + r0 * K : dA[s];
+    double* c_blk = rs ? rs->dC + r0 * N : dC[s];
+    if (!a_resident) {
+      if (i >= 2 && !rs) B200_CHECK(cudaStreamWaitEvent(g.s_in, g.e_a_free[s], 0));
+      B200_CHECK(staged_upload(a_blk, hA + r0 * K, static_cast<size_t>(rows) * K * 8, g.s_in));
+      g.h2d_bytes += static_cast<size_t>(rows) * K * 8;
+      B200_CHECK(cudaEventRecord(g.e_a_ready[s], g.s_in));
+      B200_CHECK(cudaStreamWaitEvent(st, g.e_a_ready[s], 0));
+    }
+    if (i >= 2 && !rs) B200_CHECK(cudaStreamWaitEvent(st, g.e_c_free[s], 0));
+    rc = oz2_gemm_rows(a_blk, c_blk, rows, o, false);
     if (rc) break;
     B200_CHECK(cudaEventRecord(g.e_a_free[s], st));
     B200_CHECK(cudaEventRecord(g.e_c_ready[s], st));
     B200_CHECK(cudaStreamWaitEvent(g.s_out, g.e_c_ready[s], 0));
-    B200_CHECK(cudaMemcpyAsync(hC + r0 * N, dC[s], static_cast<size_t>(rows) * N * 8, cudaMemcpyDeviceToHost, g.s_out));
+    B200_CHECK(staged_download(hC + r0 * N, c_blk, static_cast<size_t>(rows) * N * 8, g.s_out));
+    g.d2h_bytes += static_cast<size_t>(rows) * N * 8;
     B200_CHECK(cudaEventRecord(g.e_c_free[s], g.s_out));
   }
-  g.prep.valid = false;
+  if (!rs) g.prep.valid = false;  // the staging copy of B is overwritten by the next call
+  B200_CHECK(staged_finish(g.s_out));
   B200_CHECK(cudaStreamSynchronize(g.s_out));
   B200_CHECK(cudaStreamSynchronize(g.s_in));
   return rc;
@@ -965,6 +1044,8 @@ int eshkol_b200_init(int device) {
     const bool raise = !(pe && !strcmp(pe, "default"));
     B200_CHECK(cudaStreamCreateWithPriority(&g.stream, cudaStreamNonBlocking, raise ? greatest : least));
   }
+  B200_CHECK(cudaEventCreate(&g.ev_g0));
+  B200_CHECK(cudaEventCreate(&g.ev_g1));
   // [0] kernel status word, [1] work counter of the persistent products kernel
   B200_CHECK(cudaMalloc(&g.d_status, 2 * sizeof(int)));
   B200_CHECK(cudaMemset(g.d_status, 0, 2 * sizeof(int)));
@@ -1004,10 +1085,13 @@ void eshkol_b200_shutdown(void) {
   std::lock_guard<std::mutex> lock(g_mu);
   if (!g.ready) return;
   cudaStreamSynchronize(g.stream);
+  staged_shutdown();
   if (g.ws) cudaFree(g.ws);
   if (g.aux) cudaFree(g.aux);
   if (g.tbuf) cudaFree(g.tbuf);
   if (g.d_status) cudaFree(g.d_status);
+  if (g.ev_g0) cudaEventDestroy(g.ev_g0);
+  if (g.ev_g1) cudaEventDestroy(g.ev_g1);
   if (g.ev_made) {
     for (int r = 0; r < State::kEvRing; ++r) {
       for (cudaEvent_t e : g.ev_b[r]) cudaEventDestroy(e);
@@ -1053,7 +1137,8 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC, 
   if (opts) o = *opts;
   const long long m = static_cast<long long>(M), k = static_cast<long long>(K), n = static_cast<long long>(N);
   if ((o.trans_a || o.trans_b) &&
-      !(o.tier == ESHKOL_B200_TIER_OZAKI2 && (o.param == 0 || o.param == 16) && !o.use_simt_products)) {
+      !(o.tier == ESHKOL_B200_TIER_OZAKI2 && (o.param == 0 || o.param == 16) && !o.use_simt_products &&
+        k <= kMaxPreparedK)) {
     // only the 16-moduli exact tier reads transposed storage directly
     const size_t ba = o.trans_a ? ((static_cast<size_t>(m) * k * 8 + 1023) & ~size_t(1023)) : 0;
     const size_t bb = o.trans_b ? static_cast<size_t>(k) * n * 8 : 0;
@@ -1070,19 +1155,41 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC, 
     g.launches += (o.trans_a ? 1 : 0) + (o.trans_b ? 1 : 0);
     o.trans_a = o.trans_b = 0;
   }
+  g.ev_g_valid = false;
+  if (g.ev_g0) B200_CHECK(cudaEventRecord(g.ev_g0, g.stream));
+  int rc;
   switch (o.tier) {
     case ESHKOL_B200_TIER_OZAKI2:
-      return ozaki2_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 16, o);
+      rc = ozaki2_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 16, o);
+      break;
     case ESHKOL_B200_TIER_OZAKI1:
-      return ozaki1_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 6, o);
+      rc = ozaki1_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 6, o);
+      break;
     case ESHKOL_B200_TIER_OZAKI2_FAST:
-      return ozaki2_fast_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 11, o);
+      rc = ozaki2_fast_gemm(dA, dB, dC, m, k, n, o.param ? o.param : 11, o);
+      break;
     case ESHKOL_B200_TIER_DGEMM:
-      return native_dgemm(dA, dB, dC, m, k, n, o);
+      rc = native_dgemm(dA, dB, dC, m, k, n, o);
+      break;
     default:
       fprintf(stderr, "[eshkol-b200] unknown tier %d\n", o.tier);
       return -1;
   }
+  if (rc == 0 && g.ev_g1) {
+    B200_CHECK(cudaEventRecord(g.ev_g1, g.stream));
+    g.ev_g_valid = true;
+  }
+  return rc;
+}
+
+double eshkol_b200_last_gemm_ms(void) {
+  if (!g.ready || !g.ev_g_valid) return -1.0;
+  float ms = 0.f;
+  if (cudaEventSynchronize(g.ev_g1) != cudaSuccess || cudaEventElapsedTime(&ms, g.ev_g0, g.ev_g1) != cudaSuccess) {
+    cudaGetLastError();
+    return -1.0;
+  }
+  return static_cast<double>(ms);
 }
 
 int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, uint64_t M,
@@ -1095,7 +1202,7 @@ int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, 
   EshkolB200GemmOpts o;
   memset(&o, 0, sizeof(o));
   if (opts) o = *opts;
-  if (o.tier != ESHKOL_B200_TIER_OZAKI2 || (o.param != 0 && o.param != 16)) return -2;
+  if (o.tier != ESHKOL_B200_TIER_OZAKI2 || (o.param != 0 && o.param != 16) || K > static_cast<uint64_t>(kMaxPreparedK)) return -2;
   return oz2_matmul_host(hA, hB, hC, static_cast<long long>(M), static_cast<long long>(K),
                          static_cast<long long>(N), o);
 }
@@ -1272,14 +1379,41 @@ void eshkol_b200_mem_free(int kind, void* ptr) {
 
 int eshkol_b200_copy_h2d(void* device_dst, const void* host_src, size_t bytes) {
   if (!g.ready) return -1;
-  B200_CHECK(cudaMemcpyAsync(device_dst, host_src, bytes, cudaMemcpyHostToDevice, g.stream));
+  B200_CHECK(staged_upload(device_dst, host_src, bytes, g.stream));
+  g.h2d_bytes += bytes;
   return 0;
 }
 
 int eshkol_b200_copy_d2h(void* host_dst, const void* device_src, size_t bytes) {
   if (!g.ready) return -1;
-  B200_CHECK(cudaMemcpyAsync(host_dst, device_src, bytes, cudaMemcpyDeviceToHost, g.stream));
+  B200_CHECK(staged_download(host_dst, device_src, bytes, g.stream));
+  g.d2h_bytes += bytes;
   return 0;
+}
+
+void eshkol_b200_transfer_bytes(uint64_t* h2d, uint64_t* d2h) {
+  if (h2d) *h2d = g.h2d_bytes;
+  if (d2h) *d2h = g.d2h_bytes;
+}
+
+uint64_t eshkol_b200_prepared_b_token(void) { return (g.ready && g.prep.valid) ? g.prep_token : 0; }
+
+int eshkol_b200_matmul_f64_host_resident(const double* hA, const double* hB, double* hC, uint64_t M,
+                                         uint64_t K, uint64_t N, double* dA, int a_state, double* dB,
+                                         int b_state, double* dC, uint64_t* prepared_token) {
+  if (!g.ready) {
+    fprintf(stderr, "[eshkol-b200] matmul called before eshkol_b200_init succeeded\n");
+    return -1;
+  }
+  if (!hC || !dA || !dB || !dC || M == 0 || K == 0 || N == 0) return -1;
+  if ((a_state == 0 && !hA) || (b_state == 0 && !hB) || a_state < 0 || a_state > 1 || b_state < 0 || b_state > 2) return -1;
+  EshkolB200GemmOpts o;
+  memset(&o, 0, sizeof(o));
+  ResidentSet rs{dA, a_state, dB, b_state, dC};
+  const int rc = oz2_matmul_host(hA, hB, hC, static_cast<long long>(M), static_cast<long long>(K),
+                                 static_cast<long long>(N), o, &rs);
+  if (prepared_token) *prepared_token = (rc == 0 && g.prep.valid) ? g.prep_token : 0;
+  return rc;
 }
 
 int eshkol_b200_elementwise_f64_device(const double* a, const double* b, double* out,
@@ -1292,6 +1426,10 @@ int eshkol_b200_elementwise_f64_device(const double* a, const double* b, double*
 
 int eshkol_b200_sync_status(void) {
   if (!g.ready) return -1;
+  if (staged_finish(g.stream) != cudaSuccess) {
+    fprintf(stderr, "[eshkol-b200] a staged download failed: %s\n", cudaGetErrorString(cudaGetLastError()));
+    return -1;
+  }
   int h = 0;
   if (cudaMemcpyAsync(&h, g.d_status, sizeof(int), cudaMemcpyDeviceToHost, g.stream) != cudaSuccess ||
       cudaStreamSynchronize(g.stream) != cudaSuccess) {
@@ -1513,6 +1651,9 @@ int eshkol_b200_get_phase_totals(float ms[7], int counts[3]) {
   counts[0] = static_cast<int>(nb); counts[1] = static_cast<int>(na); counts[2] = static_cast<int>(nm);
   return 0;
 }
+
+void eshkol_b200_debug_set_wait_limit_ns(unsigned long long ns) { g_dbg_wait_ns = ns; }
+void eshkol_b200_debug_withhold_arrival(int on) { g_dbg_withhold = on ? 1 : 0; }
 
 uint64_t eshkol_b200_launch_count(void) { return g.launches; }
 uint64_t eshkol_b200_workspace_bytes(void) { return g.ws_bytes + g.aux_bytes + g.bside_bytes; }

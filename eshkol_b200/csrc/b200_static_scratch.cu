@@ -254,7 +254,7 @@ extern "C" int eshkol_b200_gemm_f64_static_scratch(const double* dA, const doubl
   GemmParams p1 = p0;
   p1.n_jobs = 15;
   p1.kb_per_seg = static_cast<int>(L.Kp / kBK);
-  p1.kb_per_unit = 1 << 28;
+  p1.kb_per_unit = 1023;  // deeper products hand the accumulator over in parts (none fits the array anyway)
   p1.jobs = jobs + 1;
   p1.out = reinterpret_cast<uint8_t*>(wodd);
   p1.out_plane_stride = static_cast<long long>(L.w_stride);

@@ -11,8 +11,9 @@
 //    integers instead of double-float and the exact tier's moduli (int32 accumulation
 //    lifts the cap the f32 GEMM imposed on them).
 //  * native f64 GEMM on CUDA cores: the stand-in for the reference's cublasDgemm call.
-//  * conv2d: explicit im2col of the input, then the chosen GEMM tier with the NCHW
-//    scatter and optional bias / ReLU fused into its last pass.
+//  * conv2d: in the exact tier the right-hand operand is the im2col index map over the NCHW
+//    tensor, read in place by the column scan and the split; the other tiers materialise the
+//    im2col matrix first.  NCHW scatter and optional bias / ReLU are fused into the last pass.
 #include <math.h>
 #include <stdio.h>
 #include <string.h>
@@ -589,7 +590,7 @@ int f32_gemm(const float* dA, const float* dB, float* dC, long long M, long long
   TIER_CHECK(cudaGetLastError());
   EshkolB200GemmOpts o;
   memset(&o, 0, sizeof(o));
-  o.tier = (K <= 131071) ? ESHKOL_B200_TIER_OZAKI2 : ESHKOL_B200_TIER_DGEMM;
+  o.tier = ESHKOL_B200_TIER_OZAKI2;
   if (eshkol_b200_gemm_f64_device(wA, wB, wC, M, K, N, &o) != 0) return -1;
   narrow_f32_kernel<<<static_cast<unsigned>((M * N + 255) / 256), 256, 0, st>>>(wC, M * N, dC);
   TIER_CHECK(cudaGetLastError());
@@ -642,11 +643,6 @@ cudaError_t tiers_set_attributes() {
   return cudaFuncSetAttribute(oz1_split_b_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               9 * kTJ * kTPitch * 4);
 }
-
-// scan helpers live in b200_ozaki2.cu
-cudaError_t launch_scan_rows(const double* A, long long M, long long K, double* amax, cudaStream_t st);
-cudaError_t launch_scan_cols(const double* B, long long K, long long N,
-                             unsigned long long* bmax_bits, cudaStream_t st);
 
 int ozaki1_gemm(const double* dA, const double* dB, double* dC, long long M, long long K,
                 long long N, int T, const EshkolB200GemmOpts& o) {
@@ -889,6 +885,15 @@ int conv2d_lowered(const double* d_in, long long batch, long long in_c, long lon
   if (spanH < 0 || spanW < 0) return 0;  // empty output, as the reference returns
   const long long oH = spanH / stride + 1, oW = spanW / stride + 1;
   const long long Kc = in_c * kH * kW, ncol = batch * oH * oW;
+  if (o_in.tier == ESHKOL_B200_TIER_OZAKI2 && (o_in.param == 0 || o_in.param == 16) && !o_in.use_simt_products &&
+      H < 0x7fffffffLL && W < 0x7fffffffLL) {
+    // exact tier: the scan and the split read the NCHW tensor through the im2col index map
+    const Im2colView view{d_in, batch, in_c, H, W, kH, kW, stride, pad, oH, oW};
+    EshkolB200GemmOpts o = o_in;
+    o.pixels_per_image = oH * oW;
+    o.trans_a = o.trans_b = 0;
+    return ozaki2_exact_gemm_im2col(d_ker, view, d_out, out_c, Kc, ncol, o);
+  }
   if (Kc > 65535) return -1;
   double* col = reinterpret_cast<double*>(aux_reserve(static_cast<size_t>(Kc) * ncol * 8));
   if (!col) return -1;

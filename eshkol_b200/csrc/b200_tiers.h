@@ -21,6 +21,8 @@ void count_launches(int n);
 int make_plane_map(CUtensorMap* map, const void* base, long long inner_bytes, long long rows,
                    long long planes, long long plane_stride, int box_rows);
 void oz2_host_consts(int n_mod, Oz2DeviceConsts* c, double* log2P);
+int ozaki2_exact_gemm_im2col(const double* dA, const Im2colView& view, double* dC, long long M, long long K,
+                             long long N, const EshkolB200GemmOpts& o);
 
 // b200_tiers.cu
 int ozaki1_gemm(const double* dA, const double* dB, double* dC, long long M, long long K,

@@ -23,6 +23,7 @@
  */
 #include "../../include/eshkol_gpu_memory_b200.h"
 #include "../../include/eshkol_b200_ext.h"
+#include "../../include/eshkol_b200_testing.h"
 
 #include <math.h>
 #include <pthread.h>
@@ -74,9 +75,14 @@ int eshkol_gpu_init(void) {
   return g_backend != ESHKOL_GPU_NONE;
 }
 
+void eshkol_gpu_residency_clear(void);
+
 void eshkol_gpu_shutdown(void) {
   pthread_mutex_lock(&g_init_mutex);
-  if (g_backend == ESHKOL_GPU_CUDA) eshkol_b200_shutdown();
+  if (g_backend == ESHKOL_GPU_CUDA) {
+    eshkol_gpu_residency_clear();
+    eshkol_b200_shutdown();
+  }
   g_backend = ESHKOL_GPU_NONE;
   __atomic_store_n(&g_initialized, 0, __ATOMIC_RELEASE);
   pthread_mutex_unlock(&g_init_mutex);
@@ -232,6 +238,57 @@ static int env_int_clamped(const char* name, int lo, int hi, int dflt, int clamp
   return used;
 }
 
+/* Self-calibrated time model per kernel, t_ns = overhead_ns + work / peak_gflops with
+ * work = 2*M*K*N (gpu_memory_cuda.cpp:499-522).  Index 0 is the full-precision kernel -- the
+ * reference's cublasDgemm, here the Ozaki-II exact tier -- and 1..8 are the slice tiers.  The
+ * seeds are this library's own rates on a B200 at 8192^3 under sustained load (f64-equivalent
+ * GFLOP/s) and the fixed cost of its launches on a small shape; peak_gflops then follows the
+ * best rate each kernel has actually shown (cuda_gemm_calibrate, :515-522). */
+typedef struct { double overhead_ns, peak_gflops; } GemmModel;
+static GemmModel g_gemm_model[9] = {
+    /* exact  */ {90000.0, 123000.0},
+    /* T = 1  */ {60000.0, 510000.0},
+    /* T = 2  */ {60000.0, 328000.0},
+    /* T = 3  */ {65000.0, 224000.0},
+    /* T = 4  */ {65000.0, 156000.0},
+    /* T = 5  */ {70000.0, 114000.0},
+    /* T = 6  */ {70000.0, 86600.0},
+    /* T = 7  */ {75000.0, 66400.0},
+    /* T = 8  */ {80000.0, 52000.0}};
+/* Ozaki must be predicted this much faster before the full-precision kernel is left
+ * (gpu_memory_cuda.cpp:549-552) */
+static const double OZAKI_SAFETY = 1.15;
+
+static double gemm_predict_ns(int idx, double work) {
+  return g_gemm_model[idx].overhead_ns + work / g_gemm_model[idx].peak_gflops;
+}
+
+static void gemm_calibrate(int idx, double work, double measured_ns) {
+  if (idx < 0 || idx > 8) return;
+  const double compute_ns = measured_ns - g_gemm_model[idx].overhead_ns;
+  if (compute_ns <= 0.0) return; /* overhead-dominated: no throughput signal */
+  const double achieved = work / compute_ns;
+  if (achieved > g_gemm_model[idx].peak_gflops) g_gemm_model[idx].peak_gflops = achieved;
+}
+
+/* the crude size guard of the slice tiers (gpu_memory_cuda.cpp:462-464) */
+static int ozaki_worthwhile(uint64_t M, uint64_t K, uint64_t N) { return M >= 1024 && N >= 1024 && K >= 1024; }
+
+/* cuda_select_f64 (gpu_memory_cuda.cpp:560-575): the smallest T whose guaranteed error meets
+ * the budget, taken only if the model predicts it clearly faster than the full-precision kernel */
+static int select_slice_tier(uint64_t M, uint64_t K, uint64_t N, double budget, double* speedup) {
+  const double work = 2.0 * (double)M * (double)K * (double)N;
+  *speedup = 1.0;
+  if (K > 133000 || !ozaki_worthwhile(M, K, N)) return 0;
+  int Treq = 0;
+  for (int T = 1; T <= 7; ++T)
+    if (OZAKI_TOL[T] <= budget) { Treq = T; break; }
+  if (!Treq) return 0;
+  const double t_full = gemm_predict_ns(0, work), t_oz = gemm_predict_ns(Treq, work);
+  if (t_oz * OZAKI_SAFETY < t_full) { *speedup = t_full / t_oz; return Treq; }
+  return 0;
+}
+
 static TierChoice choose_tier(uint64_t M, uint64_t K, uint64_t N) {
   TierChoice c = {ESHKOL_B200_TIER_OZAKI2, 16, "default: Ozaki-II exact"};
   const char* k;
@@ -245,22 +302,22 @@ static TierChoice choose_tier(uint64_t M, uint64_t K, uint64_t N) {
   /* CUDA backend's explicit switch: fixed T when every dimension is >= 1024 */
   if ((k = getenv("ESHKOL_CUDA_F64_KERNEL")) != NULL && !strcmp(k, "ozaki-int8")) {
     const int T = env_int_clamped("ESHKOL_OZAKI_CUDA_T", 1, 8, 6, 0);
-    if (M >= 1024 && K >= 1024 && N >= 1024) {
+    if (ozaki_worthwhile(M, K, N)) {
       c.tier = ESHKOL_B200_TIER_OZAKI1; c.param = T; c.why = "ESHKOL_CUDA_F64_KERNEL override";
       return c;
     }
   }
-  /* CUDA backend's accuracy budget: smallest T whose guaranteed error meets it */
+  /* CUDA backend's accuracy budget: the cheapest kernel that meets it.  "exact" / "full" and any
+   * budget no slice tier guarantees stay on the full-precision kernel, which here is the
+   * Ozaki-II exact tier */
   if ((k = getenv("ESHKOL_MATMUL_ACCURACY")) != NULL && *k) {
-    double budget;
+    double budget, speedup;
     if (!strcmp(k, "fast")) budget = 1e-2;
     else if (!strcmp(k, "exact") || !strcmp(k, "full")) budget = 1e-15;
     else { budget = atof(k); if (!(budget > 0.0)) budget = 1e-15; }
-    if (K <= 133000) {
-      for (int T = 1; T <= 7; ++T)
-        if (OZAKI_TOL[T] <= budget) { c.tier = ESHKOL_B200_TIER_OZAKI1; c.param = T; c.why = "accuracy-budget selector"; return c; }
-    }
-    c.why = "accuracy budget tighter than any slice tier: Ozaki-II exact";
+    const int T = select_slice_tier(M, K, N, budget, &speedup);
+    if (T) { c.tier = ESHKOL_B200_TIER_OZAKI1; c.param = T; c.why = "accuracy-budget selector"; return c; }
+    c.why = "budget met cheapest by the full-precision kernel: Ozaki-II exact";
     return c;
   }
   /* Metal backend's switches */
@@ -277,11 +334,28 @@ static TierChoice choose_tier(uint64_t M, uint64_t K, uint64_t N) {
   return c;
 }
 
+/* model slot of a choice: 0 the full-precision kernel, T for a slice tier, -1 for the others */
+static int model_index(const TierChoice* c) {
+  if (c->tier == ESHKOL_B200_TIER_OZAKI2 && c->param == 16) return 0;
+  if (c->tier == ESHKOL_B200_TIER_OZAKI1 && c->param >= 1 && c->param <= 8) return c->param;
+  return -1;
+}
+
 /* tests: the tier the environment selects for a shape, without touching a GPU */
 void eshkol_b200_debug_choose_tier(uint64_t M, uint64_t K, uint64_t N, int* tier, int* param) {
   const TierChoice c = choose_tier(M, K, N);
   if (tier) *tier = c.tier;
   if (param) *param = c.param;
+}
+
+/* tests: read one slot of the time model, or feed it one measurement */
+void eshkol_b200_debug_gemm_model(int idx, double* overhead_ns, double* peak_gflops) {
+  if (idx < 0 || idx > 8) return;
+  if (overhead_ns) *overhead_ns = g_gemm_model[idx].overhead_ns;
+  if (peak_gflops) *peak_gflops = g_gemm_model[idx].peak_gflops;
+}
+void eshkol_b200_debug_gemm_calibrate(int idx, double work, double measured_ns) {
+  gemm_calibrate(idx, work, measured_ns);
 }
 
 int eshkol_gpu_matmul_f64(EshkolGPUBuffer* A, EshkolGPUBuffer* B, EshkolGPUBuffer* C,
@@ -292,9 +366,15 @@ int eshkol_gpu_matmul_f64(EshkolGPUBuffer* A, EshkolGPUBuffer* B, EshkolGPUBuffe
     return -1;
   }
   if (!A->device_ptr || !B->device_ptr || !C->device_ptr) return -1;
+  if (M == 0 || K == 0 || N == 0 || A->size_bytes / 8 / K < M || B->size_bytes / 8 / N < K ||
+      C->size_bytes / 8 / N < M) {
+    fprintf(stderr, "[GPU] eshkol_gpu_matmul_f64: a buffer is smaller than its %llux%llux%llu operand\n",
+            (unsigned long long)M, (unsigned long long)K, (unsigned long long)N);
+    return -1;
+  }
   TierChoice c = choose_tier(M, K, N);
-  if (c.tier != ESHKOL_B200_TIER_DGEMM && K > 131071) {
-    c.tier = ESHKOL_B200_TIER_DGEMM; c.param = 0; c.why = "K beyond the int32-exact bound";
+  if (c.tier != ESHKOL_B200_TIER_DGEMM && !(c.tier == ESHKOL_B200_TIER_OZAKI2 && c.param == 16) && K > 131071) {
+    c.tier = ESHKOL_B200_TIER_OZAKI2; c.param = 16; c.why = "K beyond the reduced tiers' int32-exact bound: Ozaki-II exact";
   }
   GPU_LOG("matmul %llux%llu @ %llux%llu -> tier %d param %d (%s)", (unsigned long long)M,
           (unsigned long long)K, (unsigned long long)K, (unsigned long long)N, c.tier, c.param, c.why);
@@ -307,7 +387,12 @@ int eshkol_gpu_matmul_f64(EshkolGPUBuffer* A, EshkolGPUBuffer* B, EshkolGPUBuffe
     return -1;
   if (C->flags & FLAG_WRAPPED) C->flags |= FLAG_DIRTY;
   /* every operator returns only after the device finished (gpu_memory_cuda.cpp:611, 642) */
-  return eshkol_b200_sync_status() == 0 ? 0 : -1;
+  if (eshkol_b200_sync_status() != 0) return -1;
+  /* every real GEMM calibrates the model of the kernel that ran (:611-614), here from the
+   * device time between two events on the library stream */
+  const double ms = eshkol_b200_last_gemm_ms();
+  if (ms > 0.0) gemm_calibrate(model_index(&c), 2.0 * (double)M * (double)K * (double)N, ms * 1e6);
+  return 0;
 }
 
 int eshkol_gpu_matmul_f32(EshkolGPUBuffer* A, EshkolGPUBuffer* B, EshkolGPUBuffer* C,
@@ -355,6 +440,10 @@ int eshkol_gpu_elementwise_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPU
                                uint64_t n, EshkolElementwiseOp op) {
   if (!a || !out || n == 0) return -1;
   if (g_backend != ESHKOL_GPU_CUDA || !a->device_ptr || !out->device_ptr) return -1;
+  if (a->size_bytes / 8 < n || out->size_bytes / 8 < n || (b && b->device_ptr && b->size_bytes / 8 < n)) {
+    fprintf(stderr, "[GPU] eshkol_gpu_elementwise_f64: a buffer holds fewer than %llu doubles\n", (unsigned long long)n);
+    return -1;
+  }
   const double* bp = (b && b->device_ptr) ? (const double*)b->device_ptr : NULL;
   if (eshkol_b200_elementwise_f64_device((const double*)a->device_ptr, bp, (double*)out->device_ptr,
                                          n, (int)op))
@@ -386,7 +475,9 @@ int eshkol_gpu_normalize_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t
 /* tier of one GEMM of a conv2d gradient: what the forward product of that shape would get */
 static void conv_grad_opts(uint64_t M, uint64_t K, uint64_t N, EshkolB200GemmOpts* o) {
   TierChoice c = choose_tier(M, K, N);
-  if (c.tier != ESHKOL_B200_TIER_DGEMM && K > 131071) { c.tier = ESHKOL_B200_TIER_DGEMM; c.param = 0; }
+  if (c.tier != ESHKOL_B200_TIER_DGEMM && !(c.tier == ESHKOL_B200_TIER_OZAKI2 && c.param == 16) && K > 131071) {
+    c.tier = ESHKOL_B200_TIER_OZAKI2; c.param = 16;
+  }
   memset(o, 0, sizeof(*o));
   o->tier = c.tier; o->param = c.param;
 }
@@ -398,6 +489,12 @@ int eshkol_gpu_conv2d_backward_input_f64(EshkolGPUBuffer* grad_out, EshkolGPUBuf
   /* gpu_memory.h:404; kernel lib/backend/gpu/gpu_cuda_kernels.cu:413-449 */
   if (!grad_out || !kernel_weights || !grad_input || g_backend != ESHKOL_GPU_CUDA) return -1;
   if (!grad_out->device_ptr || !kernel_weights->device_ptr || !grad_input->device_ptr) return -1;
+  if (grad_out->size_bytes / 8 < batch_size * channels_out * out_h * out_w ||
+      kernel_weights->size_bytes / 8 < channels_out * channels_in * k_h * k_w ||
+      grad_input->size_bytes / 8 < batch_size * channels_in * in_h * in_w) {
+    fprintf(stderr, "[GPU] eshkol_gpu_conv2d_backward_input_f64: a buffer is smaller than its tensor\n");
+    return -1;
+  }
   EshkolB200GemmOpts o;
   conv_grad_opts(channels_in * k_h * k_w, channels_out, batch_size * out_h * out_w, &o);
   if (eshkol_b200_conv2d_backward_input_f64_device((const double*)grad_out->device_ptr,
@@ -414,6 +511,12 @@ int eshkol_gpu_conv2d_backward_kernel_f64(EshkolGPUBuffer* grad_out, EshkolGPUBu
   /* gpu_memory.h:415; kernel lib/backend/gpu/gpu_cuda_kernels.cu:451-486 */
   if (!grad_out || !saved_input || !grad_kernel || g_backend != ESHKOL_GPU_CUDA) return -1;
   if (!grad_out->device_ptr || !saved_input->device_ptr || !grad_kernel->device_ptr) return -1;
+  if (grad_out->size_bytes / 8 < batch_size * channels_out * out_h * out_w ||
+      saved_input->size_bytes / 8 < batch_size * channels_in * in_h * in_w ||
+      grad_kernel->size_bytes / 8 < channels_out * channels_in * k_h * k_w) {
+    fprintf(stderr, "[GPU] eshkol_gpu_conv2d_backward_kernel_f64: a buffer is smaller than its tensor\n");
+    return -1;
+  }
   EshkolB200GemmOpts o;
   conv_grad_opts(channels_out, batch_size * out_h * out_w, channels_in * k_h * k_w, &o);
   if (eshkol_b200_conv2d_backward_kernel_f64_device((const double*)grad_out->device_ptr,
@@ -432,6 +535,170 @@ int eshkol_gpu_batchnorm_backward_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, Es
 int eshkol_gpu_layernorm_backward_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
     EshkolGPUBuffer* d, EshkolGPUBuffer* e, EshkolGPUBuffer* f, uint64_t n0, uint64_t n1) {
   (void)a; (void)b; (void)c; (void)d; (void)e; (void)f; (void)n0; (void)n1; return -1;
+}
+
+/* ------------------------------------------------- residency of operands ---- */
+typedef struct {
+  const char* host;      /* NULL: free slot */
+  size_t bytes;
+  void* dev;
+  uint64_t finger;       /* sampled contents of the host range when the copy was made */
+  uint64_t last_use;
+  uint64_t prep_token;   /* token of the prepared right-hand operand made from this copy, or 0 */
+  int pinned;            /* in use by the call in progress: not evictable */
+} ResEntry;
+enum { RES_SLOTS = 64 };
+static ResEntry g_res[RES_SLOTS];
+static size_t g_res_bytes = 0, g_res_limit = 0;
+static uint64_t g_res_clock = 0;
+static int g_res_on = -1; /* -1: read the environment on first use */
+
+static int res_enabled(void) {
+  if (g_res_on < 0) {
+    const char* e = getenv("ESHKOL_B200_RESIDENCY");
+    g_res_on = (e && e[0] == '1') ? 1 : 0;
+    const char* m = getenv("ESHKOL_B200_RESIDENCY_MB");
+    const long mb = m ? atol(m) : 0;
+    g_res_limit = (size_t)(mb > 0 ? mb : 65536) << 20;
+  }
+  return g_res_on;
+}
+
+/* 256 evenly spaced 8-byte words of the range and its length, FNV-1a */
+static uint64_t res_fingerprint(const void* p, size_t bytes) {
+  const uint64_t* w = (const uint64_t*)p;
+  const size_t n = bytes / 8;
+  uint64_t h = 1469598103934665603ull ^ (uint64_t)bytes;
+  const size_t samples = n < 256 ? n : 256;
+  for (size_t i = 0; i < samples; ++i) {
+    uint64_t v;
+    memcpy(&v, w + (samples > 1 ? i * (n - 1) / (samples - 1) : 0), 8);
+    h = (h ^ v) * 1099511628211ull;
+  }
+  return h;
+}
+
+static void res_drop(ResEntry* e) {
+  if (!e->host) return;
+  if (e->dev) eshkol_b200_mem_free(0, e->dev);
+  g_res_bytes -= e->bytes;
+  memset(e, 0, sizeof(*e));
+}
+
+static void res_drop_overlapping(const void* host, size_t bytes, const ResEntry* keep) {
+  const char* lo = (const char*)host;
+  const char* hi = lo + (bytes ? bytes : 1);
+  for (int i = 0; i < RES_SLOTS; ++i) {
+    ResEntry* e = &g_res[i];
+    if (e->host && e != keep && e->host < hi && lo < e->host + e->bytes) res_drop(e);
+  }
+}
+
+/* the cached copy of exactly this range, if its sampled contents are still what was uploaded */
+static ResEntry* res_find(const void* host, size_t bytes) {
+  for (int i = 0; i < RES_SLOTS; ++i) {
+    ResEntry* e = &g_res[i];
+    if (e->host == (const char*)host && e->bytes == bytes) {
+      if (e->finger != res_fingerprint(host, bytes)) {
+        GPU_LOG("residency: host range %p changed since it was uploaded; dropping the device copy", host);
+        res_drop(e);
+        return NULL;
+      }
+      e->last_use = ++g_res_clock;
+      return e;
+    }
+  }
+  return NULL;
+}
+
+/* a new entry with a device buffer of `bytes`; evicts least recently used copies to stay under
+ * the limit; NULL when there is no room (every candidate pinned, or the allocation fails) */
+static ResEntry* res_insert(const void* host, size_t bytes) {
+  res_drop_overlapping(host, bytes, NULL);
+  for (;;) {
+    ResEntry* slot = NULL;
+    ResEntry* lru = NULL;
+    for (int i = 0; i < RES_SLOTS; ++i) {
+      ResEntry* e = &g_res[i];
+      if (!e->host) { if (!slot) slot = e; continue; }
+      if (!e->pinned && (!lru || e->last_use < lru->last_use)) lru = e;
+    }
+    if (slot && g_res_bytes + bytes <= g_res_limit) {
+      void* d = NULL;
+      if (eshkol_b200_mem_alloc(0, bytes, &d) == 0) {
+        slot->host = (const char*)host; slot->bytes = bytes; slot->dev = d;
+        slot->finger = 0; slot->prep_token = 0; slot->pinned = 1;
+        slot->last_use = ++g_res_clock;
+        g_res_bytes += bytes;
+        return slot;
+      }
+    }
+    if (!lru) return NULL;
+    res_drop(lru);
+  }
+}
+
+void eshkol_gpu_set_residency(int on, size_t limit_mb) {
+  (void)res_enabled();
+  g_res_on = on ? 1 : 0;
+  if (limit_mb) g_res_limit = limit_mb << 20;
+  if (!on) eshkol_gpu_residency_clear();
+}
+
+void eshkol_gpu_invalidate(const void* host_ptr, size_t bytes) {
+  if (host_ptr) res_drop_overlapping(host_ptr, bytes, NULL);
+}
+
+void eshkol_gpu_residency_clear(void) {
+  for (int i = 0; i < RES_SLOTS; ++i) res_drop(&g_res[i]);
+}
+
+/* exact-tier product with cached device copies; 0 done, -1 failed, -2 not served this way */
+static int matmul_resident(const double* A, const double* B, double* C, uint64_t M, uint64_t K, uint64_t N) {
+  const size_t ab = (size_t)(M * K) * 8, bb = (size_t)(K * N) * 8, cb = (size_t)(M * N) * 8;
+  const char *a0 = (const char*)A, *b0 = (const char*)B, *c0 = (const char*)C;
+  /* a result that overlaps an operand is not a case the reference's callers produce */
+  if ((c0 < a0 + ab && a0 < c0 + cb) || (c0 < b0 + bb && b0 < c0 + cb)) return -2;
+  for (int i = 0; i < RES_SLOTS; ++i) g_res[i].pinned = 0;
+  ResEntry* ea = res_find(A, ab);
+  int a_state = ea ? 1 : 0;
+  if (ea) ea->pinned = 1; else ea = res_insert(A, ab);
+  if (!ea) return -2;
+  ResEntry* eb = ((const void*)A == (const void*)B && ab == bb) ? ea : res_find(B, bb);
+  int b_state = 0;
+  if (eb == ea) b_state = a_state;  /* A * A: one copy serves both; uploaded (if at all) as the right-hand operand */
+  else if (eb) b_state = 1;
+  if (eb) eb->pinned = 1; else eb = res_insert(B, bb);
+  if (!eb) { if (!a_state) res_drop(ea); return -2; }
+  if (eb == ea && !a_state) a_state = 1;  /* the upload of B fills the shared copy before any block of A is read */
+  if (b_state == 1 && eb->prep_token && eb->prep_token == eshkol_b200_prepared_b_token()) b_state = 2;
+  ResEntry* ec = res_insert(C, cb);
+  if (!ec) {
+    if (!ea->finger) res_drop(ea);
+    if (eb != ea && !eb->finger) res_drop(eb);
+    return -2;
+  }
+  uint64_t token = 0;
+  GPU_LOG("matmul %llux%llu @ %llux%llu -> Ozaki-II exact, resident operands (A %s, B %s)", (unsigned long long)M,
+          (unsigned long long)K, (unsigned long long)K, (unsigned long long)N, a_state ? "on device" : "uploaded",
+          b_state == 2 ? "prepared" : (b_state == 1 ? "on device" : "uploaded"));
+  int rc = eshkol_b200_matmul_f64_host_resident(A, B, C, M, K, N, (double*)ea->dev, a_state, (double*)eb->dev,
+                                                b_state, (double*)ec->dev, &token);
+  if (rc == 0 && eshkol_b200_sync_status() != 0) rc = -1;
+  if (rc != 0) {
+    res_drop(ec);
+    if (!ea->finger) res_drop(ea);
+    if (eb != ea && !eb->finger) res_drop(eb);
+    return -1;
+  }
+  if (!ea->finger) ea->finger = res_fingerprint(A, ab);
+  if (!eb->finger) eb->finger = res_fingerprint(B, bb);
+  ec->finger = res_fingerprint(C, cb);
+  /* only one right-hand operand is prepared at a time */
+  for (int i = 0; i < RES_SLOTS; ++i) g_res[i].prep_token = 0;
+  eb->prep_token = token;
+  for (int i = 0; i < RES_SLOTS; ++i) g_res[i].pinned = 0;
+  return 0;
 }
 
 /* ------------------------------------------------------------ dispatchers ---- */
@@ -486,13 +753,19 @@ void eshkol_matmul_dispatch(const double* A, const double* B, double* C, uint64_
     /* exact tier: upload, products and download pipelined over row blocks of A */
     const TierChoice c = choose_tier(M, K, N);
     int rc = -2;
-    if (c.tier == ESHKOL_B200_TIER_OZAKI2 && c.param == 16 && K <= 131071) {
+    if (c.tier == ESHKOL_B200_TIER_OZAKI2 && c.param == 16 && K <= 262144) {
       EshkolB200GemmOpts o;
       memset(&o, 0, sizeof(o));
       o.tier = c.tier; o.param = c.param;
-      GPU_LOG("matmul %llux%llu @ %llux%llu -> Ozaki-II exact, host pipeline (%s)", (unsigned long long)M,
-              (unsigned long long)K, (unsigned long long)K, (unsigned long long)N, c.why);
-      rc = eshkol_b200_matmul_f64_host(A, B, C, M, K, N, &o);
+      if (res_enabled()) {
+        rc = matmul_resident(A, B, C, M, K, N);
+        if (rc == 0) return;
+      }
+      if (rc == -2) {
+        GPU_LOG("matmul %llux%llu @ %llux%llu -> Ozaki-II exact, host pipeline (%s)", (unsigned long long)M,
+                (unsigned long long)K, (unsigned long long)K, (unsigned long long)N, c.why);
+        rc = eshkol_b200_matmul_f64_host(A, B, C, M, K, N, &o);
+      }
       if (rc == 0 && eshkol_b200_sync_status() != 0) rc = -1;
       if (rc == 0) return;
     }

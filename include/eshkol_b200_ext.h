@@ -77,6 +77,12 @@ int eshkol_b200_gemm_f64_device(const double* dA, const double* dB, double* dC,
                                 uint64_t M, uint64_t K, uint64_t N,
                                 const EshkolB200GemmOpts* opts);
 
+/* Device time in milliseconds of the last eshkol_b200_gemm_f64_device call (two events on the
+ * library stream around everything it enqueued); waits for that call.  -1 when there is none.
+ * The C host layer feeds it to the time model of its accuracy-budget selector, as the reference
+ * feeds its wall-clock time (lib/backend/gpu/gpu_memory_cuda.cpp:605-614). */
+double eshkol_b200_last_gemm_ms(void);
+
 /* feed-forward block on device tensors, the arithmetic of the loops the reference generates inline
  * for (feed-forward x W1 b1 W2 b2) (lib/backend/tensor_transformer_codegen.cpp:2557-2664):
  *   out[rows x d_model] = gelu(x[rows x d_model] * W1[d_model x d_ff] + b1) * W2[d_ff x d_model] + b2
@@ -164,9 +170,30 @@ int eshkol_b200_multiply_prepared_f64_device(double* dC, const EshkolB200GemmOpt
  * their rows of C downloaded on three streams so PCIe and the tensor cores overlap.
  * Returns when C is complete in host memory: 0, -1 on failure, -2 when opts ask for a
  * tier this path does not serve (the caller then uses the buffer API).  Pinned host
- * memory overlaps fully; pageable memory gives the same bits with less overlap. */
+ * memory is read and written by DMA directly; pageable memory (what an arena hands out)
+ * moves in chunks through pinned staging slots filled by a few copy threads
+ * (ESHKOL_B200_COPY_THREADS, default 8) -- same bits, about half the rate. */
 int eshkol_b200_matmul_f64_host(const double* hA, const double* hB, double* hC, uint64_t M,
                                 uint64_t K, uint64_t N, const EshkolB200GemmOpts* opts);
+
+/* The host pipeline with device copies the CALLER keeps between calls (the mechanism under the
+ * residency cache of eshkol_matmul_dispatch; the reference wraps and unwraps host memory on
+ * every call, lib/backend/gpu/gpu_memory_cuda.cpp:1136-1145).  dA, dB, dC are device buffers of
+ * M*K, K*N and M*N doubles.  a_state 0: hA is uploaded into dA block by block, overlapped with
+ * the products; 1: dA already holds A (hA is not read).  b_state 0: hB is uploaded into dB and
+ * prepared; 1: dB already holds B and is prepared from there; 2: the library's prepared
+ * right-hand operand is still this B -- the caller checks that eshkol_b200_prepared_b_token()
+ * equals the token this function wrote when it prepared that B -- and nothing is uploaded or
+ * split.  C is written to dC and downloaded to hC.  Returns when hC is complete; 0 / -1.
+ * *prepared_token receives the token of the operand now prepared (0 if none). */
+int eshkol_b200_matmul_f64_host_resident(const double* hA, const double* hB, double* hC, uint64_t M,
+                                         uint64_t K, uint64_t N, double* dA, int a_state, double* dB,
+                                         int b_state, double* dC, uint64_t* prepared_token);
+/* Token of the currently prepared right-hand operand: changes whenever one is prepared, 0 when
+ * none is valid (any one-shot GEMM invalidates it). */
+uint64_t eshkol_b200_prepared_b_token(void);
+/* Bytes this library has copied host -> device and device -> host since init. */
+void eshkol_b200_transfer_bytes(uint64_t* h2d, uint64_t* d2h);
 
 /* The same exact-tier product (16 moduli, identical bits) for callers that must not
  * allocate: a host whose own arena already owns all device memory, so that
@@ -297,22 +324,6 @@ uint64_t eshkol_b200_launch_count(void);
 
 /* Bytes of device scratch currently held by the library's workspace. */
 uint64_t eshkol_b200_workspace_bytes(void);
-
-/* Tests only: copy one intermediate of the LAST Ozaki-II GEMM to host memory.
- * what: 0 mu (int32[M])          1 nu (int32[N])
- *       2 A residues, modulus 256 plane   3 A residues, odd plane `index` (0-based)
- *       4 B residues, modulus 256 plane   5 B residues, odd plane `index`
- *       6 products mod 256: sum of chunk residues mod 512, ties as +128 (int16); 12 its flip bits
- *       7 product residues, odd plane `index` (int8)
- *       8 / 9 A flags (+128, odd)   10 / 11 B flags (+128, odd): uint16 units, 64 per chunk
- * info[0..5] receive rows, row pitch (elements), element size, n_chunks, last
- * segment length, bytes copied.  Synchronises the stream. */
-int eshkol_b200_debug_fetch(int what, int index, void* host_dst, uint64_t capacity_bytes,
-                            uint64_t info[6]);
-
-/* Tests only: the tier and parameter eshkol_gpu_matmul_f64 would select for this
- * shape from the current environment.  Touches no GPU. */
-void eshkol_b200_debug_choose_tier(uint64_t M, uint64_t K, uint64_t N, int* tier, int* param);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,48 @@
+/*
+ * Test hooks of libeshkol_gpu_b200.so.  Not part of the installed interface: a host
+ * runtime includes eshkol_gpu_memory_b200.h (and eshkol_b200_ext.h if it keeps tensors on
+ * the device); only the test suite includes this file.
+ */
+#ifndef ESHKOL_B200_TESTING_H
+#define ESHKOL_B200_TESTING_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Tests only: copy one intermediate of the LAST Ozaki-II GEMM to host memory.
+ * what: 0 mu (int32[M])          1 nu (int32[N])
+ *       2 A residues, modulus 256 plane   3 A residues, odd plane `index` (0-based)
+ *       4 B residues, modulus 256 plane   5 B residues, odd plane `index`
+ *       6 products mod 256: sum of chunk residues mod 512, ties as +128 (int16); 12 its flip bits
+ *       7 product residues, odd plane `index` (int8)
+ *       8 / 9 A flags (+128, odd)   10 / 11 B flags (+128, odd): uint16 units, 64 per chunk
+ * info[0..5] receive rows, row pitch (elements), element size, n_chunks, last
+ * segment length, bytes copied.  Synchronises the stream. */
+int eshkol_b200_debug_fetch(int what, int index, void* host_dst, uint64_t capacity_bytes,
+                            uint64_t info[6]);
+
+/* Tests only: the tier and parameter eshkol_gpu_matmul_f64 would select for this
+ * shape from the current environment.  Touches no GPU. */
+void eshkol_b200_debug_choose_tier(uint64_t M, uint64_t K, uint64_t N, int* tier, int* param);
+
+/* Tests only: one slot of the selector's time model (0 = the full-precision kernel, 1..8 = the
+ * slice tiers), and one measurement fed to it as a finished GEMM would feed it. */
+void eshkol_b200_debug_gemm_model(int idx, double* overhead_ns, double* peak_gflops);
+void eshkol_b200_debug_gemm_calibrate(int idx, double work_flop, double measured_ns);
+
+/* Tests only: the wait limit of every bounded wait inside the kernels, in nanoseconds
+ * (0 restores the default of two seconds), and a switch that makes the next products launch
+ * withhold one producer arrival so that its waits run out.  The kernel then returns by itself
+ * with a status code, which eshkol_b200_sync_status reports once and clears. */
+void eshkol_b200_debug_set_wait_limit_ns(unsigned long long ns);
+void eshkol_b200_debug_withhold_arrival(int on);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ESHKOL_B200_TESTING_H */

@@ -81,7 +81,7 @@ void eshkol_gpu_wait(EshkolGPUBuffer* buffer);                    /* gpu_memory.
 
 /* ---- matrix products ---- */
 /* C = A*B, row-major f64; the tier is chosen from the environment exactly as the
- * reference's backends read it (see INTEGRATION.md).  gpu_memory.h:242 */
+ * reference's backends read it.  gpu_memory.h:242 */
 int eshkol_gpu_matmul_f64(EshkolGPUBuffer* A, EshkolGPUBuffer* B, EshkolGPUBuffer* C,
                           uint64_t M, uint64_t K, uint64_t N);
 /* f32 buffers.  gpu_memory.h:250 */
@@ -179,6 +179,28 @@ int eshkol_gpu_conv2d_f64(const double* in, int64_t batch, int64_t in_c, int64_t
  * element threshold of eshkol_gpu_should_use it returns -1 without touching the GPU. */
 int eshkol_gpu_matmul_backward_f64(const double* grad_out, const double* A, const double* B,
                                    double* grad_A, double* grad_B, uint64_t M, uint64_t K, uint64_t N);
+
+/* ---- residency of operands across eshkol_matmul_dispatch calls (no counterpart in the
+ * reference, whose dispatcher wraps and unwraps host memory on every call,
+ * lib/backend/gpu/gpu_memory_cuda.cpp:1136-1145) ----
+ * Off unless ESHKOL_B200_RESIDENCY=1 or eshkol_gpu_set_residency(1, ...).  When on, the exact-tier
+ * dispatcher keeps a device copy of every operand and result, keyed on (host pointer, bytes);
+ * a later call that passes the same host range finds the copy and skips the upload, and a
+ * right-hand operand that is still the library's prepared one also skips its split.  The
+ * result of one call is found as an operand of the next, so a chain such as
+ * (matmul (matmul A B) A) (tests/gpu/matmul_correctness_test.esk:54) uploads each distinct
+ * operand once.  Results are still written to host memory on every call.
+ * The host must call eshkol_gpu_invalidate after writing to a range it has passed before
+ * (tensor-set!, an arena reset that reuses the address): the library cannot see host writes.
+ * As a guard against a forgotten call, 256 values of the range, evenly spaced, are compared
+ * with the ones seen at upload; a mismatch drops the copy.  Copies are evicted least recently
+ * used first once they exceed limit_mb (ESHKOL_B200_RESIDENCY_MB, default 65536). */
+void eshkol_gpu_set_residency(int on, size_t limit_mb);
+/* Forget the device copy of any cached range that overlaps [host_ptr, host_ptr + bytes);
+ * bytes = 0 means every range that contains host_ptr. */
+void eshkol_gpu_invalidate(const void* host_ptr, size_t bytes);
+/* Forget every cached range and free the device copies. */
+void eshkol_gpu_residency_clear(void);
 
 #ifdef __cplusplus
 }

@@ -62,15 +62,31 @@ def rel_err(got: float, ref: float) -> float:
     return abs(got - ref) / denom
 
 
-# tests/ml/conv_correctness_test.esk:38-106: (input shape, input, kernel shape, kernel, stride, pad, out shape, out)
+# tests/ml/conv_correctness_test.esk:38-106: (input shape, input, kernel shape, kernel, stride, pad, out shape, out);
+# all seven cases, the second one in the 2-D single-plane form (:46-52)
 CONV_CASES = [
     ((1, 1, 3, 3), [1.0] * 9, (1, 1, 2, 2), [1.0] * 4, 1, 0, (1, 1, 2, 2), [4.0] * 4),
+    ((3, 3), [1.0] * 9, (2, 2), [1.0] * 4, 1, 0, (2, 2), [4.0] * 4),
     ((1, 1, 3, 3), [1, 2, 3, 4, 5, 6, 7, 8, 9], (1, 1, 2, 2), [1, 0, 0, 1], 1, 0, (1, 1, 2, 2), [6, 8, 12, 14]),
     ((1, 2, 2, 2), [1, 2, 3, 4, 5, 6, 7, 8], (1, 2, 2, 2), [1.0] * 8, 1, 0, (1, 1, 1, 1), [36.0]),
     ((1, 1, 2, 2), [1, 2, 3, 4], (2, 1, 2, 2), [1, 1, 1, 1, 1, 0, 0, 0], 1, 0, (1, 2, 1, 1), [10.0, 1.0]),
     ((1, 1, 4, 4), list(range(1, 17)), (1, 1, 2, 2), [1.0] * 4, 2, 0, (1, 1, 2, 2), [14, 22, 46, 54]),
     ((1, 1, 3, 3), [1.0] * 9, (1, 1, 3, 3), [1.0] * 9, 1, 1, (1, 1, 3, 3), [4, 6, 4, 6, 9, 6, 4, 6, 4]),
 ]
+
+
+def conv_promote(ishape, kshape):
+    """NCHW shapes the runtime entry point gives the kernel (lib/backend/tensor_conv_kernel.cpp:58-79):
+    a kernel of rank >= 4 is [out_c, in_c, kH, kW] and every leading input dimension is a batch
+    index; a kernel of lower rank is a single plane, every leading input dimension a plane."""
+    ishape, kshape = tuple(ishape), tuple(kshape)
+    H, W = ishape[-2:]
+    kH, kW = kshape[-2:]
+    if len(kshape) >= 4:
+        batch = int(np.prod(ishape[:-3], dtype=np.int64)) if len(ishape) > 3 else 1
+        return (batch, kshape[1], H, W), (kshape[0], kshape[1], kH, kW)
+    batch = int(np.prod(ishape[:-2], dtype=np.int64)) if len(ishape) > 2 else 1
+    return (batch, 1, H, W), (1, 1, kH, kW)
 
 
 def conv2d_numpy(inp, ker, stride=1, pad=0):

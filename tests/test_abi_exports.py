@@ -99,6 +99,69 @@ def test_tier_selection_follows_the_reference_switches(monkeypatch):
     assert _choose(monkeypatch, {"ESHKOL_B200_TIER": "dgemm"}) == (eb.TIER_DGEMM, 0)
 
 
+def test_accuracy_budget_selector_consults_the_time_model(monkeypatch):
+    """cuda_select_f64 (lib/backend/gpu/gpu_memory_cuda.cpp:552-575): the smallest T that meets the
+    budget is taken only when the model predicts it 1.15 x faster than the full-precision kernel
+    (here the Ozaki-II exact tier), only for shapes whose dimensions all reach 1024
+    (cuda_ozaki_worthwhile, :462-464), and the model follows the best rate a kernel has shown."""
+    lib = eb.load_library()
+    ov, pk = ctypes.c_double(), ctypes.c_double()
+    lib.eshkol_b200_debug_gemm_model(0, ctypes.byref(ov), ctypes.byref(pk))
+    full = (ov.value, pk.value)
+    lib.eshkol_b200_debug_gemm_model(5, ctypes.byref(ov), ctypes.byref(pk))
+    t5 = (ov.value, pk.value)
+    n = 4096
+    work = 2.0 * n ** 3
+    # T = 5 is slower than the exact tier on a B200: a 1e-11 budget stays exact, a 1e-9 budget takes T = 4
+    assert (t5[0] + work / t5[1]) * 1.15 > full[0] + work / full[1]
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "1e-11"}, (n, n, n)) == (eb.TIER_OZAKI2, 16)
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "1e-9"}, (n, n, n)) == (eb.TIER_OZAKI1, 4)
+    # budgets no slice tier guarantees, and the words for them, keep the exact tier
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "1e-15"}, (n, n, n)) == (eb.TIER_OZAKI2, 16)
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "full"}, (n, n, n)) == (eb.TIER_OZAKI2, 16)
+    # a dimension below 1024: the slice tiers do not amortise their passes
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "fast"}, (512, n, n)) == (eb.TIER_OZAKI2, 16)
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "fast"}, (n, 1000, n)) == (eb.TIER_OZAKI2, 16)
+    # K beyond the int32-exact bound of a slice product
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "fast"}, (2048, 140000, 2048)) == (eb.TIER_OZAKI2, 16)
+    # calibration is a high-water mark: a slower measurement changes nothing, a faster one does
+    lib.eshkol_b200_debug_gemm_calibrate(5, work, t5[0] + work / (t5[1] * 0.5))
+    lib.eshkol_b200_debug_gemm_model(5, ctypes.byref(ov), ctypes.byref(pk))
+    assert pk.value == t5[1]
+    lib.eshkol_b200_debug_gemm_calibrate(5, work, t5[0] + work / (t5[1] * 3.0))
+    lib.eshkol_b200_debug_gemm_model(5, ctypes.byref(ov), ctypes.byref(pk))
+    assert abs(pk.value / (t5[1] * 3.0) - 1.0) < 1e-9
+    assert _choose(monkeypatch, {"ESHKOL_MATMUL_ACCURACY": "1e-11"}, (n, n, n)) == (eb.TIER_OZAKI1, 5)
+    # a measurement shorter than the fixed cost carries no rate
+    lib.eshkol_b200_debug_gemm_calibrate(6, work, 1.0)
+    lib.eshkol_b200_debug_gemm_model(6, ctypes.byref(ov), ctypes.byref(pk))
+    assert pk.value < 1e6
+
+
+def test_tensor_struct_layout_is_the_references():
+    # lib/core/arena_memory.h:768-785: five 8-byte fields, 40 bytes, dtype appended at index 4
+    from eshkol_b200.abi import EshkolTensor
+    assert ctypes.sizeof(EshkolTensor) == 40
+    off = {f[0]: getattr(EshkolTensor, f[0]).offset for f in EshkolTensor._fields_}
+    assert off == {"dimensions": 0, "num_dimensions": 8, "elements": 16, "total_elements": 24, "dtype": 32}
+
+
+def test_c_host_compiled_against_the_reference_headers_links():
+    """tests/c_harness: a C program that includes the reference's own gpu_memory.h and
+    vm_gpu_dispatch.h, built by oracle/Makefile (where the reference tree is present) and linked
+    to this library; `link` takes the address of all 31 functions and checks the 48-byte buffer."""
+    import subprocess
+    exe = os.path.join(ROOT, "oracle", "_ref", "c_harness")
+    if os.path.isdir("/root/reference"):
+        subprocess.run(["make", "-C", os.path.join(ROOT, "oracle"), "-s", "_ref/c_harness"], check=True,
+                       capture_output=True)
+    if not os.path.exists(exe):
+        pytest.skip("the harness is built where the reference tree is present")
+    r = subprocess.run([exe, "link"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "linked 31 functions" in r.stdout and "sizeof(EshkolGPUBuffer) = 48" in r.stdout
+
+
 def test_inputs_stream_is_drand48():
     from eshkol_b200 import inputs
     libc = ctypes.CDLL(None)

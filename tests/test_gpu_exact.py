@@ -372,21 +372,76 @@ def test_sharded_configuration_depth_sampled_rows(gpu_lib):
     assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, 52))
 
 
-def test_largest_exact_depth(gpu_lib):
-    """K = 131071 is the last depth whose int32 accumulation of 127^2-bounded products is exact
-    and the last the exact tier accepts; one more is refused."""
-    K = 131071
+@pytest.mark.parametrize("K", [131071, 131072, 140001, 262144])
+def test_exact_tier_at_and_beyond_the_int32_depth(gpu_lib, K):
+    """K = 131071 is the last depth whose int32 accumulation of 128^2-bounded products is exact.
+    The reference's modular GEMM has no depth limit (it extracts every 1008 elements,
+    lib/backend/gpu/metal_softfloat.h:3966-3969, 4054-4067); beyond that depth the odd-modulus
+    accumulators are handed over in parts of 1023 k-blocks and their residues summed.  Bit for bit
+    against the oracle up to the last depth whose exponent E is 52 whatever the data."""
     A = inputs.full53(81, (3, K))
     B = inputs.full53(82, (K, 40))
     assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, 52))
+
+
+def test_exact_tier_where_the_exponent_depends_on_the_data(gpu_lib):
+    """Beyond K = 262144 the exponent E of gpu_memory.mm:2510-2512 falls below 52 and depends on the
+    maxima of both operands: the one-shot driver scans both before it scales either."""
+    K = 300000
+    A = inputs.full53(83, (2, K))
+    B = inputs.full53(84, (K, 5))
+    E = ol.oz2_E(A, B)
+    assert E < 52
+    assert gu.same_bits(gu.gemm(A, B), ol.oz2_exact(A, B, E))
+
+
+def test_a_wait_that_runs_out_ends_the_kernel_and_leaves_the_library_usable(gpu_lib):
+    """Every wait inside the products kernel is bounded.  With the limit set to a millisecond and
+    the producer told to withhold the first stage's arrival, the kernel's waits run out: it
+    returns by itself, the status word says which role gave up, eshkol_b200_sync_status reports
+    it once, and the next product is bit-exact again.  Nothing faults and nothing hangs: the
+    waits simply end."""
+    lib = gpu_lib
+    A = inputs.uniform(85, (128, 128))
+    B = inputs.uniform(86, (128, 128))
+    want = ol.oz2_exact(A, B, 52)
+    assert gu.same_bits(gu.gemm(A, B), want)
     import torch
-    dA = torch.zeros((1, K + 1), dtype=torch.float64, device="cuda")
-    dB = torch.zeros((K + 1, 1), dtype=torch.float64, device="cuda")
-    dC = torch.zeros((1, 1), dtype=torch.float64, device="cuda")
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.zeros((128, 128), dtype=torch.float64, device="cuda")
     torch.cuda.synchronize()
-    rc = gpu_lib.eshkol_b200_gemm_f64_device(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 1, K + 1, 1,
-                                             api.make_opts(eb.TIER_OZAKI2, 16))
-    assert rc == -1
+    lib.eshkol_b200_debug_set_wait_limit_ns(1_000_000)
+    lib.eshkol_b200_debug_withhold_arrival(1)
+    try:
+        api.gemm_device(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), 128, 128, 128, api.make_opts(eb.TIER_OZAKI2, 16))
+        st = api.sync_status()
+        assert st in (1, 2, 3), st
+    finally:
+        lib.eshkol_b200_debug_set_wait_limit_ns(0)
+        lib.eshkol_b200_debug_withhold_arrival(0)
+    assert api.sync_status() == 0  # reported once, then clear
+    assert gu.same_bits(gu.gemm(A, B), want)
+
+
+def test_c_host_built_against_the_reference_headers(gpu_lib, tmp_path):
+    """tests/c_harness, compiled against the reference's own gpu_memory.h and vm_gpu_dispatch.h
+    and linked to this library: eshkol_matmul_dispatch and the VM's vm_gpu_try_matmul on operands
+    that are 8- but not 16-byte aligned (arena payloads behind their header) give the oracle's bits."""
+    import os
+    import subprocess
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = os.path.join(root, "oracle", "_ref", "c_harness")
+    if not os.path.exists(exe):
+        pytest.skip("the harness is built where the reference tree is present (oracle/Makefile)")
+    M, K, N = 300, 1100, 200
+    r = subprocess.run([exe, "run", str(M), str(K), str(N), str(tmp_path)], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout + r.stderr
+    A = inputs.uniform(1, (M, K))
+    B = inputs.uniform(2, (K, N))
+    want = ol.oz2_exact(A, B, 52)
+    for name in ("dispatch.bin", "vm.bin"):
+        got = np.fromfile(str(tmp_path / name), dtype=np.float64).reshape(M, N)
+        assert gu.same_bits(got, want), name
 
 
 @pytest.mark.parametrize("shape", [(130, 300, 70), (257, 1100, 129), (64, 64, 64)])

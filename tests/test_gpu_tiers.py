@@ -93,11 +93,12 @@ def _conv_gpu(inp, ker, stride, pad, activation=0):
 @pytest.mark.parametrize("case", range(len(fx.CONV_CASES)))
 def test_conv_known_answers(gpu_lib, case):
     ishape, ival, kshape, kval, stride, pad, oshape, oval = fx.CONV_CASES[case]
+    ishape, kshape = fx.conv_promote(ishape, kshape)  # the 2-D form reaches the kernel as NCHW with one plane
     inp = np.array(ival, dtype=np.float64).reshape(ishape)
     ker = np.array(kval, dtype=np.float64).reshape(kshape)
     got = _conv_gpu(inp, ker, stride, pad)
-    assert got.shape == tuple(oshape)
-    assert np.allclose(got, np.array(oval, dtype=np.float64).reshape(oshape), rtol=0, atol=1e-9)
+    assert got.size == int(np.prod(oshape))
+    assert np.allclose(got.reshape(oshape), np.array(oval, dtype=np.float64).reshape(oshape), rtol=0, atol=1e-9)
 
 
 @pytest.mark.parametrize("cfg", [(2, 5, 13, 11, 7, 3, 3, 1, 1), (3, 4, 9, 9, 6, 2, 3, 2, 0), (1, 3, 8, 8, 130, 3, 3, 1, 1)])
@@ -117,23 +118,80 @@ def test_conv_bits_match_oracle_on_the_lowered_operands(gpu_lib, cfg):
     assert np.median(err) < 1e-15 and np.mean(err < 1e-12) > 0.95 and err.max() < 1e-7
 
 
-def test_conv_c4_shape_sampled(gpu_lib):
-    # batch 32, 64 -> 128 channels, 56x56, 3x3, stride 1, pad 1, fused ReLU
+def test_conv_c4_whole_result_bit_exact(gpu_lib):
+    """The conv2d benchmark configuration: batch 32, 64 -> 128 channels, 56 x 56, 3 x 3, stride 1,
+    pad 1, inputs and weights normal(0, 0.1), fused ReLU.  The whole output, bit for bit, against
+    the oracle's exact-tier product of the weight matrix with the im2col operand (the library
+    itself never builds that operand: its scan and split read the NCHW tensor through the index
+    map), and against the reference's direct loop to the exact tier's own error."""
+    ol.set_threads(len(__import__("os").sched_getaffinity(0)))
     inp = inputs.normal(1, (32, 64, 56, 56), scale=0.1)
     ker = inputs.normal(2, (128, 64, 3, 3), scale=0.1)
     got = _conv_gpu(inp, ker, 1, 1, activation=1)
     assert got.shape == (32, 128, 56, 56)
-    # bits on sampled output pixels: oracle on the matching im2col columns
-    col, oH, oW = fx.im2col(inp[[0, 31]], 3, 3, 1, 1)
-    cols = np.array([0, 57, 3135, 3136 + 1000, 2 * 3136 - 1])
-    low = ol.oz2_exact(ker.reshape(128, -1), np.ascontiguousarray(col[:, cols]), 52)
-    low = np.where(low > 0.0, low, 0.0)
-    flat = got[[0, 31]].transpose(1, 0, 2, 3).reshape(128, -1)
-    assert gu.same_bits(np.ascontiguousarray(flat[:, cols]), low)
+    col, oH, oW = fx.im2col(inp, 3, 3, 1, 1)
+    low = ol.oz2_exact(ker.reshape(128, -1), col, 52)
+    low = np.where(low > 0.0, low, 0.0).reshape(128, 32, oH, oW).transpose(1, 0, 2, 3)
+    assert gu.same_bits(got, np.ascontiguousarray(low))
     ref = ol.ref_conv2d(inp[:1], ker, 1, 1)
     if ref is not None:
         err = np.abs(got[0] - np.where(ref[0] > 0.0, ref[0], 0.0))
         assert np.mean(err < 1e-12) > 0.95 and err.max() < 1e-6
+
+
+def _make_tensor(arr):
+    """eshkol_tensor_t over a numpy array (kept alive by the returned tuple)"""
+    from eshkol_b200.abi import EshkolTensor
+    arr = np.ascontiguousarray(arr, dtype=np.float64)
+    dims = (ctypes.c_uint64 * arr.ndim)(*arr.shape)
+    t = EshkolTensor()
+    t.dimensions = ctypes.cast(dims, ctypes.POINTER(ctypes.c_uint64))
+    t.num_dimensions = arr.ndim
+    t.elements = ctypes.cast(arr.ctypes.data, ctypes.POINTER(ctypes.c_int64))
+    t.total_elements = arr.size
+    t.dtype = 0
+    return t, (arr, dims)
+
+
+@pytest.mark.parametrize("case", range(len(fx.CONV_CASES)))
+def test_rt_conv2d_on_tensor_structs(gpu_lib, case):
+    """eshkol_rt_conv2d, the symbol generated code calls (lib/backend/tensor_conv_kernel.cpp:32-109):
+    heap tensors in, a fresh tensor out whose shape follows the reference's contract -- including
+    the 2-D single-plane form, which keeps its rank."""
+    from eshkol_b200.abi import EshkolTensor
+    ishape, ival, kshape, kval, stride, pad, oshape, oval = fx.CONV_CASES[case]
+    made = []
+
+    @ctypes.CFUNCTYPE(ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_uint64)
+    def allocate(arena, nd, total):
+        t = EshkolTensor()
+        dims = (ctypes.c_uint64 * max(1, nd))()
+        elems = (ctypes.c_int64 * max(1, total))()
+        t.dimensions = ctypes.cast(dims, ctypes.POINTER(ctypes.c_uint64))
+        t.elements = ctypes.cast(elems, ctypes.POINTER(ctypes.c_int64))
+        t.num_dimensions, t.total_elements, t.dtype = nd, total, 0
+        made.append((t, dims, elems))
+        return ctypes.addressof(t)
+
+    gpu_lib.eshkol_b200_set_tensor_allocator(ctypes.cast(allocate, ctypes.c_void_p))
+    try:
+        ti, keep_i = _make_tensor(np.array(ival, dtype=np.float64).reshape(ishape))
+        tk, keep_k = _make_tensor(np.array(kval, dtype=np.float64).reshape(kshape))
+        arena = ctypes.c_int(0)
+        out = gpu_lib.eshkol_rt_conv2d(ctypes.addressof(arena), ctypes.addressof(ti), ctypes.addressof(tk), stride, pad)
+        assert out, "eshkol_rt_conv2d returned NULL"
+        t = EshkolTensor.from_address(out)
+        assert tuple(t.dimensions[i] for i in range(t.num_dimensions)) == tuple(oshape)
+        got = np.ctypeslib.as_array(ctypes.cast(t.elements, ctypes.POINTER(ctypes.c_double)), shape=(t.total_elements,))
+        assert np.allclose(got, np.array(oval, dtype=np.float64), rtol=0, atol=1e-9)
+        # shape errors give NULL, as in the reference: mismatched channels, kernel larger than the input
+        bad, keep_b = _make_tensor(np.zeros((1, 3, 5, 5)))
+        k2, keep_k2 = _make_tensor(np.zeros((2, 2, 3, 3)))
+        assert not gpu_lib.eshkol_rt_conv2d(ctypes.addressof(arena), ctypes.addressof(bad), ctypes.addressof(k2), 1, 0)
+        big, keep_big = _make_tensor(np.zeros((1, 1, 9, 9)))
+        assert not gpu_lib.eshkol_rt_conv2d(ctypes.addressof(arena), ctypes.addressof(ti), ctypes.addressof(big), 1, 0)
+    finally:
+        gpu_lib.eshkol_b200_set_tensor_allocator(None)
 
 
 def test_dispatch_on_host_pointers(gpu_lib):
@@ -184,14 +242,120 @@ def test_buffer_api_round_trip_like_the_vm(gpu_lib):
     gpu_lib.eshkol_gpu_free(ctypes.byref(x))
 
 
-def test_k_beyond_int32_bound_is_refused_loudly(gpu_lib):
+def test_residency_chain_uploads_each_operand_once(gpu_lib):
+    """(matmul (matmul A B) A), the chain of tests/gpu/matmul_correctness_test.esk:54, through
+    eshkol_matmul_dispatch with residency on: A and B cross the link once each, the first result
+    is found on the device as the left operand of the second product, a repeated product with
+    the same right-hand operand neither uploads nor splits it again, and every result carries the
+    bits of the plain path.  After eshkol_gpu_invalidate a changed operand is uploaded again."""
+    lib = gpu_lib
+    n = 1024
+    A = inputs.uniform(71, (n, n))
+    B = inputs.uniform(72, (n, n))
+    C1 = np.full((n, n), np.nan)
+    C2 = np.full((n, n), np.nan)
+    want1 = ol.oz2_exact(A, B, 52)
+    want2 = ol.oz2_exact(want1, A, 52)
+    h2d, d2h = ctypes.c_uint64(), ctypes.c_uint64()
+
+    def moved():
+        lib.eshkol_b200_transfer_bytes(ctypes.byref(h2d), ctypes.byref(d2h))
+        return h2d.value, d2h.value
+
+    old = lib.eshkol_gpu_get_threshold()
+    lib.eshkol_gpu_set_threshold(1)
+    lib.eshkol_gpu_set_residency(1, 4096)
+    try:
+        up0, down0 = moved()
+        lib.eshkol_matmul_dispatch(A.ctypes.data, B.ctypes.data, C1.ctypes.data, n, n, n, 0)
+        up1, down1 = moved()
+        assert up1 - up0 == A.nbytes + B.nbytes and down1 - down0 == C1.nbytes
+        assert gu.same_bits(C1, want1)
+        lib.eshkol_matmul_dispatch(C1.ctypes.data, A.ctypes.data, C2.ctypes.data, n, n, n, 0)
+        up2, down2 = moved()
+        assert up2 == up1, "the second product of the chain uploaded something"
+        assert down2 - down1 == C2.nbytes
+        assert gu.same_bits(C2, want2)
+        # the same right-hand operand again: still prepared, so no upload and no new preparation
+        tok = lib.eshkol_b200_prepared_b_token()
+        assert tok != 0
+        A2 = inputs.uniform(73, (n, n))
+        C3 = np.full((n, n), np.nan)
+        lib.eshkol_matmul_dispatch(A2.ctypes.data, A.ctypes.data, C3.ctypes.data, n, n, n, 0)
+        up3, _ = moved()
+        assert up3 - up2 == A2.nbytes
+        assert lib.eshkol_b200_prepared_b_token() == tok
+        assert gu.same_bits(C3, ol.oz2_exact(A2, A, 52))
+        # the host changes B and says so
+        B[17, 33] = 0.123
+        lib.eshkol_gpu_invalidate(B.ctypes.data, 0)
+        lib.eshkol_matmul_dispatch(A.ctypes.data, B.ctypes.data, C1.ctypes.data, n, n, n, 0)
+        up4, _ = moved()
+        assert up4 - up3 == B.nbytes
+        assert gu.same_bits(C1, ol.oz2_exact(A, B, 52))
+        # ... and a change it forgot to report is caught when it touches a sampled value
+        A[0, 0] = 0.5
+        lib.eshkol_matmul_dispatch(A.ctypes.data, B.ctypes.data, C1.ctypes.data, n, n, n, 0)
+        assert gu.same_bits(C1, ol.oz2_exact(A, B, 52))
+    finally:
+        lib.eshkol_gpu_set_residency(0, 0)
+        lib.eshkol_gpu_set_threshold(old)
+
+
+def test_dispatch_on_pageable_and_pinned_host_memory_agree(gpu_lib):
+    """Arena memory is pageable: the dispatcher moves it through pinned staging slots filled by a
+    few copy threads.  Same bits as from pinned memory, for a shape of several row blocks and
+    with sizes that are not multiples of the staging chunk."""
     import torch
-    a = torch.zeros((1, 131072), dtype=torch.float64, device="cuda")
-    b = torch.zeros((131072, 1), dtype=torch.float64, device="cuda")
+    lib = gpu_lib
+    M, K, N = 3000, 1100, 1300
+    A = inputs.uniform(75, (M, K))
+    B = inputs.uniform(76, (K, N))
+    C_page = np.full((M, N), np.nan)
+    pA, pB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+    pC = torch.empty((M, N), dtype=torch.float64).pin_memory()
+    old = lib.eshkol_gpu_get_threshold()
+    lib.eshkol_gpu_set_threshold(1)
+    try:
+        lib.eshkol_matmul_dispatch(A.ctypes.data, B.ctypes.data, C_page.ctypes.data, M, K, N, 0)
+        lib.eshkol_matmul_dispatch(pA.data_ptr(), pB.data_ptr(), pC.data_ptr(), M, K, N, 0)
+    finally:
+        lib.eshkol_gpu_set_threshold(old)
+    assert gu.same_bits(C_page, pC.numpy())
+    assert gu.same_bits(C_page[:64], ol.oz2_exact(A[:64], B, 52))
+
+
+def test_buffer_api_rejects_buffers_smaller_than_their_operands(gpu_lib):
+    lib = gpu_lib
+    bufs = [eb.EshkolGPUBuffer() for _ in range(3)]
+    for b, nbytes in zip(bufs, (64 * 64 * 8, 64 * 64 * 8, 64 * 32 * 8)):
+        assert lib.eshkol_gpu_alloc(nbytes, 1, ctypes.byref(b)) == 0  # ESHKOL_MEM_DEVICE
+    a, b, c = (ctypes.byref(x) for x in bufs)
+    assert lib.eshkol_gpu_matmul_f64(a, b, c, 64, 64, 64) == -1      # C holds 64 x 32
+    assert lib.eshkol_gpu_matmul_f64(a, b, c, 64, 128, 32) == -1     # A and B too small for K = 128
+    assert lib.eshkol_gpu_matmul_f64(a, b, c, 64, 64, 32) == 0
+    assert lib.eshkol_gpu_elementwise_f64(a, b, c, 64 * 64, 0) == -1  # out holds 64 x 32
+    assert lib.eshkol_gpu_elementwise_f64(a, b, c, 64 * 32, 0) == 0
+    assert lib.eshkol_gpu_conv2d_backward_input_f64(a, b, c, 64, 64, 3, 3, 62, 62, 1, 1, 4, 4, 1) == -1
+    assert lib.eshkol_gpu_conv2d_backward_kernel_f64(a, b, c, 64, 64, 3, 3, 62, 62, 1, 1, 4, 4, 1) == -1
+    for x in bufs:
+        lib.eshkol_gpu_free(ctypes.byref(x))
+
+
+def test_reduced_tiers_refuse_k_beyond_their_int32_bound(gpu_lib):
+    """One int8 product of the slice tier is exact only while K * 127^2 < 2^31
+    (lib/backend/gpu/gpu_memory_cuda.cpp:351-361): the slice and fast tiers say so and return -1;
+    the buffer API then takes the exact tier, which has no depth limit."""
+    import torch
+    K = 140000
+    a = torch.zeros((1, K), dtype=torch.float64, device="cuda")
+    b = torch.zeros((K, 1), dtype=torch.float64, device="cuda")
     c = torch.zeros((1, 1), dtype=torch.float64, device="cuda")
     torch.cuda.synchronize()
-    rc = gpu_lib.eshkol_b200_gemm_f64_device(a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, 131072, 1, None)
-    assert rc == -1
+    for tier, param in ((eb.TIER_OZAKI1, 6), (eb.TIER_OZAKI2_FAST, 11)):
+        opts = api.make_opts(tier, param)
+        assert gpu_lib.eshkol_b200_gemm_f64_device(a.data_ptr(), b.data_ptr(), c.data_ptr(), 1, K, 1, ctypes.byref(opts)) == -1
+    assert api.sync_status() == 0
 
 
 def _f16_reference(A, B):

