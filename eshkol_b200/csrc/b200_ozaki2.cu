@@ -61,50 +61,94 @@ __global__ void __launch_bounds__(256) scan_rows_kernel(const double* __restrict
 
 // ------------------------------------------------- the operand as an im2col view
 // Where column n of the view starts in the tensor: image base, top-left input coordinate.
+// All of it in 32-bit arithmetic (the launchers refuse extents beyond int).
 struct ViewColumn {
   long long base;
   int ih0, iw0;
 };
 __device__ __forceinline__ ViewColumn view_column(const Im2colView& v, long long n) {
-  const long long ow = n % v.oW, t = n / v.oW;
-  const long long oh = t % v.oH, b = t / v.oH;
+  const int oW = static_cast<int>(v.oW), oH = static_cast<int>(v.oH);
+  const int t = static_cast<int>(n / oW), ow = static_cast<int>(n - static_cast<long long>(t) * oW);
+  const int b = t / oH, oh = t - b * oH;
   ViewColumn c;
-  c.base = b * v.in_c * v.H * v.W;
-  c.ih0 = static_cast<int>(oh * v.stride - v.pad);
-  c.iw0 = static_cast<int>(ow * v.stride - v.pad);
+  c.base = static_cast<long long>(b) * v.in_c * v.H * v.W;
+  c.ih0 = oh * static_cast<int>(v.stride) - static_cast<int>(v.pad);
+  c.iw0 = ow * static_cast<int>(v.stride) - static_cast<int>(v.pad);
   return c;
 }
-__device__ __forceinline__ double view_load(const Im2colView& v, const ViewColumn& c, long long kk) {
-  const int kw = static_cast<int>(kk % v.kW);
-  const long long t = kk / v.kW;
-  const int kh = static_cast<int>(t % v.kH);
-  const long long ic = t / v.kH;
-  const int ih = c.ih0 + kh, iw = c.iw0 + kw;
-  if (ih < 0 || ih >= v.H || iw < 0 || iw >= v.W) return 0.0;
-  return __ldg(v.in + c.base + (ic * v.H + ih) * v.W + iw);
+// kernel tap of row kk: (ic, kh, kw)
+struct ViewTap {
+  int ic, kh, kw;
+};
+__device__ __forceinline__ ViewTap view_tap(const Im2colView& v, int kk) {
+  const int kW = static_cast<int>(v.kW), kH = static_cast<int>(v.kH);
+  ViewTap t;
+  const int q = kk / kW;
+  t.kw = kk - q * kW;
+  t.ic = q / kH;
+  t.kh = q - t.ic * kH;
+  return t;
+}
+__device__ __forceinline__ void view_tap_next(const Im2colView& v, ViewTap& t) {
+  if (++t.kw == static_cast<int>(v.kW)) {
+    t.kw = 0;
+    if (++t.kh == static_cast<int>(v.kH)) { t.kh = 0; ++t.ic; }
+  }
+}
+__device__ __forceinline__ double view_load(const Im2colView& v, const ViewColumn& c, const ViewTap& t) {
+  const int ih = c.ih0 + t.kh, iw = c.iw0 + t.kw;
+  const int H = static_cast<int>(v.H), W = static_cast<int>(v.W);
+  if (ih < 0 || ih >= H || iw < 0 || iw >= W) return 0.0;
+  return __ldg(v.in + c.base + (static_cast<long long>(t.ic) * H + ih) * W + iw);
+}
+
+// Column maxima of the view without walking it: first the maximum over the channels of every
+// input pixel (the tensor is read once), then for every output pixel the maximum over its
+// kH x kW window of that image.
+__global__ void __launch_bounds__(256) view_channel_max_kernel(const Im2colView v, double* __restrict__ cmax) {
+  const long long plane = v.H * v.W;
+  const long long idx = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;  // (b, ih, iw)
+  if (idx >= v.batch * plane) return;
+  const long long b = idx / plane, pix = idx - b * plane;
+  const double* p = v.in + b * v.in_c * plane + pix;
+  double mx = 0.0;
+  for (long long ic = 0; ic < v.in_c; ++ic) mx = dmax_ref(mx, fabs(__ldg(p + ic * plane)));
+  cmax[idx] = mx;
+}
+__global__ void __launch_bounds__(256) view_window_max_kernel(const Im2colView v, const double* __restrict__ cmax,
+                                                              long long N, double* __restrict__ bmax) {
+  const long long n = static_cast<long long>(blockIdx.x) * 256 + threadIdx.x;
+  if (n >= N) return;
+  const ViewColumn c = view_column(v, n);
+  const long long plane = v.H * v.W;
+  const double* img = cmax + (c.base / (v.in_c * plane)) * plane;
+  double mx = 0.0;
+  for (int kh = 0; kh < static_cast<int>(v.kH); ++kh) {
+    const int ih = c.ih0 + kh;
+    if (ih < 0 || ih >= static_cast<int>(v.H)) continue;
+    for (int kw = 0; kw < static_cast<int>(v.kW); ++kw) {
+      const int iw = c.iw0 + kw;
+      if (iw < 0 || iw >= static_cast<int>(v.W)) continue;
+      mx = dmax_ref(mx, img[static_cast<long long>(ih) * v.W + iw]);
+    }
+  }
+  bmax[n] = mx;
 }
 
 // ---------------------------------------------------------------- column scan
 // Block = 64 columns x 4 row phases over a slab of rows; partial maxima merge
 // through atomicMax on the bit pattern (order-preserving for non-negative doubles).
 constexpr int kColSlab = 256;
-template <bool kView>
 __global__ void __launch_bounds__(256) scan_cols_kernel(const double* __restrict__ B, long long K,
                                                         long long N,
-                                                        unsigned long long* __restrict__ bmax_bits,
-                                                        const Im2colView view) {
+                                                        unsigned long long* __restrict__ bmax_bits) {
   __shared__ double red[4][64];
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
   const long long j = static_cast<long long>(blockIdx.x) * 64 + tx;
   const long long k0 = static_cast<long long>(blockIdx.y) * kColSlab;
   const long long k1 = (k0 + kColSlab < K) ? k0 + kColSlab : K;
   double mx = 0.0;
-  if (kView) {
-    if (j < N) {
-      const ViewColumn vc = view_column(view, j);
-      for (long long k = k0 + ty; k < k1; k += 4) mx = dmax_ref(mx, fabs(view_load(view, vc, k)));
-    }
-  } else if (j < N) {
+  if (j < N) {
     long long k = k0 + ty;
     for (; k + 12 < k1; k += 16) {
       const double v0 = __ldg(B + k * N + j), v1 = __ldg(B + (k + 4) * N + j),
@@ -285,9 +329,12 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
       const long long k = kbase + (ty + 8 * t) * 4;
+      ViewTap tap = view_tap(view, static_cast<int>(k));
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        bv[t][e] = (j < N && k + e < g.K) ? view_load(view, vc, k + e) : 0.0;
+      for (int e = 0; e < 4; ++e) {
+        bv[t][e] = (j < N && k + e < g.K) ? view_load(view, vc, tap) : 0.0;
+        view_tap_next(view, tap);
+      }
     }
   } else {
 #pragma unroll
@@ -463,14 +510,24 @@ cudaError_t launch_scan_rows(const double* A, long long M, long long K, double* 
 }
 
 cudaError_t launch_scan_cols(const double* B, long long K, long long N,
-                             unsigned long long* bmax_bits, cudaStream_t st, const Im2colView* view) {
+                             unsigned long long* bmax_bits, cudaStream_t st) {
   if (N <= 0 || K <= 0) return cudaSuccess;
   cudaError_t e = cudaMemsetAsync(bmax_bits, 0, static_cast<size_t>(N) * 8, st);
   if (e != cudaSuccess) return e;
   const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((K + kColSlab - 1) / kColSlab));
   if (grid.y > 65535u) return cudaErrorInvalidValue;
-  if (view) scan_cols_kernel<true><<<grid, 256, 0, st>>>(nullptr, K, N, bmax_bits, *view);
-  else scan_cols_kernel<false><<<grid, 256, 0, st>>>(B, K, N, bmax_bits, Im2colView{});
+  scan_cols_kernel<<<grid, 256, 0, st>>>(B, K, N, bmax_bits);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_scan_view(const Im2colView& view, long long N, double* pixel_max, double* bmax, cudaStream_t st) {
+  const long long pixels = view.batch * view.H * view.W;
+  if (N <= 0 || pixels <= 0) return cudaSuccess;
+  if (view.H * view.W > 0x7fffffffLL || view.in_c * view.kH * view.kW > 0x7fffffffLL ||
+      N / view.oW > 0x7fffffffLL)
+    return cudaErrorInvalidValue;
+  view_channel_max_kernel<<<static_cast<unsigned>((pixels + 255) / 256), 256, 0, st>>>(view, pixel_max);
+  view_window_max_kernel<<<static_cast<unsigned>((N + 255) / 256), 256, 0, st>>>(view, pixel_max, N, bmax);
   return cudaGetLastError();
 }
 

@@ -56,10 +56,11 @@ struct Im2colView {
 };
 
 cudaError_t launch_scan_rows(const double* A, long long M, long long K, double* amax, cudaStream_t st);
-// view != nullptr: B is ignored and the K x N operand is the im2col view
 cudaError_t launch_scan_cols(const double* B, long long K, long long N,
-                             unsigned long long* bmax_bits, cudaStream_t st,
-                             const Im2colView* view = nullptr);
+                             unsigned long long* bmax_bits, cudaStream_t st);
+// column maxima of an im2col view: the maximum over the channels of every input pixel (into
+// pixel_max, batch * H * W doubles of scratch), then the window maximum per output pixel
+cudaError_t launch_scan_view(const Im2colView& view, long long N, double* pixel_max, double* bmax, cudaStream_t st);
 cudaError_t launch_scales(const double* vmax, long long n, int E, int* shift, double* scale,
                           double* inv_scale, cudaStream_t st);
 cudaError_t launch_split_a(const double* A, const double* scale, const SplitPlanes& p,

@@ -373,6 +373,7 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
   const size_t o_bhi = cv.take(flag_bytes), o_bodd_f = cv.take(flag_bytes);
   const size_t b_stride = static_cast<size_t>(N) * q.Kp;
   const size_t o_bodd = cv.take(b_stride * n_odd);
+  const size_t o_pix = cv.take(view ? static_cast<size_t>(view->batch * view->H * view->W) * 8 : 0);
   g.prep.valid = false;
   if (cv.off > g.bside_bytes) {
     B200_CHECK(cudaStreamSynchronize(g.stream));
@@ -406,7 +407,8 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
   // trans: B is stored N x K (each column of the operand is a contiguous row), which is the
   // layout the row scan and the non-transposing split of a left-hand operand read
   if (trans) B200_CHECK(launch_scan_rows(dB, N, K, P.bmax, st));
-  else B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(P.bmax), st, view));
+  else if (view) B200_CHECK(launch_scan_view(*view, N, reinterpret_cast<double*>(ws + o_pix), P.bmax, st));
+  else B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(P.bmax), st));
   B200_CHECK(launch_scales(P.bmax, N, 52, P.nu, P.sb, P.sbi, st));
   B200_MARK(1);
   SplitPlanes pb{N, K, q.Kp, q.K0, q.n_chunks, n_odd, P.b0, P.b_hi, P.b_odd, P.bodd, P.bodd_stride};

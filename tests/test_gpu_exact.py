@@ -387,7 +387,7 @@ def test_exact_tier_at_and_beyond_the_int32_depth(gpu_lib, K):
 def test_exact_tier_where_the_exponent_depends_on_the_data(gpu_lib):
     """Beyond K = 262144 the exponent E of gpu_memory.mm:2510-2512 falls below 52 and depends on the
     maxima of both operands: the one-shot driver scans both before it scales either."""
-    K = 300000
+    K = 400000
     A = inputs.full53(83, (2, K))
     B = inputs.full53(84, (K, 5))
     E = ol.oz2_E(A, B)

@@ -329,7 +329,7 @@ def test_buffer_api_rejects_buffers_smaller_than_their_operands(gpu_lib):
     lib = gpu_lib
     bufs = [eb.EshkolGPUBuffer() for _ in range(3)]
     for b, nbytes in zip(bufs, (64 * 64 * 8, 64 * 64 * 8, 64 * 32 * 8)):
-        assert lib.eshkol_gpu_alloc(nbytes, 1, ctypes.byref(b)) == 0  # ESHKOL_MEM_DEVICE
+        assert lib.eshkol_gpu_alloc(nbytes, 2, ctypes.byref(b)) == 0  # ESHKOL_MEM_DEVICE
     a, b, c = (ctypes.byref(x) for x in bufs)
     assert lib.eshkol_gpu_matmul_f64(a, b, c, 64, 64, 64) == -1      # C holds 64 x 32
     assert lib.eshkol_gpu_matmul_f64(a, b, c, 64, 128, 32) == -1     # A and B too small for K = 128
