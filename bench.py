@@ -373,10 +373,13 @@ def run_b200(args):
         # column panels of B overlap the distribution and the gather with the products
         panels = int(os.environ.get("ESHKOL_B200_PANELS", "4"))
         transport = os.environ.get("ESHKOL_B200_TRANSPORT", "copy_engine")
+        # every rank splits 1/N of each panel's columns and the residue planes are exchanged,
+        # instead of every rank splitting all of B
+        share = os.environ.get("ESHKOL_B200_SHARE_SPLIT", "1") == "1"
         # narrow first and last panels shorten the two transfers nothing hides
-        taper = os.environ.get("ESHKOL_B200_TAPER", "geometric")
+        taper = os.environ.get("ESHKOL_B200_TAPER", "gentle" if share else "geometric")
         sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=panels, comm_sms=comm_sms,
-                         transport=transport, taper=taper)
+                         transport=transport, taper=taper, share_split=share)
         rows = sg.rows
         A = inputs.uniform(1, (rows, n), device=dev, start=sg.row0 * n)
         B = inputs.uniform(2, (n, n), device=dev) if rank == 0 else None

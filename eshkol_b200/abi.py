@@ -126,6 +126,10 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_prepare_b_f64_device", ctypes.c_int, [vp, u64, u64])
     sig("eshkol_b200_gemm_prepared_f64_device", ctypes.c_int, [vp, vp, u64, optp])
     sig("eshkol_b200_prepare_a_f64_device", ctypes.c_int, [vp, u64, u64, u64])
+    sig("eshkol_b200_prepared_b_bytes", u64, [u64, u64])
+    sig("eshkol_b200_prepare_b_columns_f64_device", ctypes.c_int, [vp, u64, u64, u64, u64, u64, vp])
+    sig("eshkol_b200_prepared_b_regions", ctypes.c_int, [u64, u64, u64, u64, ctypes.POINTER(u64)])
+    sig("eshkol_b200_adopt_prepared_b", ctypes.c_int, [vp, u64, u64])
     sig("eshkol_b200_multiply_prepared_f64_device", ctypes.c_int, [vp, optp])
     sig("eshkol_b200_conv2d_f64_device", ctypes.c_int, [vp, i64, i64, i64, i64, vp, i64, i64, i64, i64, i64, vp, optp])
     sig("eshkol_b200_mem_alloc", ctypes.c_int, [ctypes.c_int, ctypes.c_size_t, ctypes.POINTER(vp)])

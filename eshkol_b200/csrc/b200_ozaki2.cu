@@ -140,7 +140,7 @@ __global__ void __launch_bounds__(256) view_window_max_kernel(const Im2colView v
 // through atomicMax on the bit pattern (order-preserving for non-negative doubles).
 constexpr int kColSlab = 256;
 __global__ void __launch_bounds__(256) scan_cols_kernel(const double* __restrict__ B, long long K,
-                                                        long long N,
+                                                        long long N, long long ld,
                                                         unsigned long long* __restrict__ bmax_bits) {
   __shared__ double red[4][64];
   const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
@@ -151,12 +151,12 @@ __global__ void __launch_bounds__(256) scan_cols_kernel(const double* __restrict
   if (j < N) {
     long long k = k0 + ty;
     for (; k + 12 < k1; k += 16) {
-      const double v0 = __ldg(B + k * N + j), v1 = __ldg(B + (k + 4) * N + j),
-                   v2 = __ldg(B + (k + 8) * N + j), v3 = __ldg(B + (k + 12) * N + j);
+      const double v0 = __ldg(B + k * ld + j), v1 = __ldg(B + (k + 4) * ld + j),
+                   v2 = __ldg(B + (k + 8) * ld + j), v3 = __ldg(B + (k + 12) * ld + j);
       mx = dmax_ref(mx, fabs(v0)); mx = dmax_ref(mx, fabs(v1));
       mx = dmax_ref(mx, fabs(v2)); mx = dmax_ref(mx, fabs(v3));
     }
-    for (; k < k1; k += 4) mx = dmax_ref(mx, fabs(__ldg(B + k * N + j)));
+    for (; k < k1; k += 4) mx = dmax_ref(mx, fabs(__ldg(B + k * ld + j)));
   }
   red[ty][tx] = mx;
   __syncthreads();
@@ -312,7 +312,7 @@ constexpr int kSplitBJ = 32, kSplitBK = 128, kSplitBPitch = 33;
 template <bool kView>
 __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__ B,
                                                       const double* __restrict__ scale,
-                                                      long long N, const SplitGeom g,
+                                                      long long N, long long ld, const SplitGeom g,
                                                       const __grid_constant__ Oz2DeviceConsts c,
                                                       const __grid_constant__ Im2colView view) {
   extern __shared__ uint32_t sm[];  // [n_odd + 2][32][33]: bytes mod 256, flag nibbles, odd moduli
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
       const long long k = kbase + (ty + 8 * t) * 4;
 #pragma unroll
       for (int e = 0; e < 4; ++e)
-        bv[t][e] = (j < N && k + e < g.K) ? __ldg(B + (k + e) * N + j) : 0.0;
+        bv[t][e] = (j < N && k + e < g.K) ? __ldg(B + (k + e) * ld + j) : 0.0;
     }
   }
 #pragma unroll
@@ -510,13 +510,14 @@ cudaError_t launch_scan_rows(const double* A, long long M, long long K, double* 
 }
 
 cudaError_t launch_scan_cols(const double* B, long long K, long long N,
-                             unsigned long long* bmax_bits, cudaStream_t st) {
+                             unsigned long long* bmax_bits, cudaStream_t st, long long ld) {
+  if (ld <= 0) ld = N;
   if (N <= 0 || K <= 0) return cudaSuccess;
   cudaError_t e = cudaMemsetAsync(bmax_bits, 0, static_cast<size_t>(N) * 8, st);
   if (e != cudaSuccess) return e;
   const dim3 grid(static_cast<unsigned>((N + 63) / 64), static_cast<unsigned>((K + kColSlab - 1) / kColSlab));
   if (grid.y > 65535u) return cudaErrorInvalidValue;
-  scan_cols_kernel<<<grid, 256, 0, st>>>(B, K, N, bmax_bits);
+  scan_cols_kernel<<<grid, 256, 0, st>>>(B, K, N, ld, bmax_bits);
   return cudaGetLastError();
 }
 
@@ -589,14 +590,15 @@ cudaError_t split_set_attributes() {
 }
 
 cudaError_t launch_split_b(const double* B, const double* scale, long long N, const SplitPlanes& p,
-                           const Oz2DeviceConsts& c, cudaStream_t st, const Im2colView* view) {
+                           const Oz2DeviceConsts& c, cudaStream_t st, const Im2colView* view, long long ld) {
+  if (ld <= 0) ld = N;
   cudaError_t e = clear_plane0(p, st);
   if (e != cudaSuccess) return e;
   const dim3 grid(static_cast<unsigned>((N + kSplitBJ - 1) / kSplitBJ),
                   static_cast<unsigned>(p.Kp / kSplitBK));
   if (grid.y > 65535u) return cudaErrorInvalidValue;
-  if (view) split_b_kernel<true><<<grid, 256, split_b_smem_bytes(p.n_odd), st>>>(nullptr, scale, N, make_geom(p), c, *view);
-  else split_b_kernel<false><<<grid, 256, split_b_smem_bytes(p.n_odd), st>>>(B, scale, N, make_geom(p), c, Im2colView{});
+  if (view) split_b_kernel<true><<<grid, 256, split_b_smem_bytes(p.n_odd), st>>>(nullptr, scale, N, ld, make_geom(p), c, *view);
+  else split_b_kernel<false><<<grid, 256, split_b_smem_bytes(p.n_odd), st>>>(B, scale, N, ld, make_geom(p), c, Im2colView{});
   return cudaGetLastError();
 }
 

@@ -56,8 +56,9 @@ struct Im2colView {
 };
 
 cudaError_t launch_scan_rows(const double* A, long long M, long long K, double* amax, cudaStream_t st);
+// ld: elements between rows of B (0 = N): B may be a block of columns of a wider matrix
 cudaError_t launch_scan_cols(const double* B, long long K, long long N,
-                             unsigned long long* bmax_bits, cudaStream_t st);
+                             unsigned long long* bmax_bits, cudaStream_t st, long long ld = 0);
 // column maxima of an im2col view: the maximum over the channels of every input pixel (into
 // pixel_max, batch * H * W doubles of scratch), then the window maximum per output pixel
 cudaError_t launch_scan_view(const Im2colView& view, long long N, double* pixel_max, double* bmax, cudaStream_t st);
@@ -66,7 +67,8 @@ cudaError_t launch_scales(const double* vmax, long long n, int E, int* shift, do
 cudaError_t launch_split_a(const double* A, const double* scale, const SplitPlanes& p,
                            const Oz2DeviceConsts& c, cudaStream_t st);
 cudaError_t launch_split_b(const double* B, const double* scale, long long N, const SplitPlanes& p,
-                           const Oz2DeviceConsts& c, cudaStream_t st, const Im2colView* view = nullptr);
+                           const Oz2DeviceConsts& c, cudaStream_t st, const Im2colView* view = nullptr,
+                           long long ld = 0);
 cudaError_t split_set_attributes();
 cudaError_t launch_crt(const CrtArgs& a, const Oz2DeviceConsts& c, cudaStream_t st);
 

@@ -357,6 +357,59 @@ static int oz2_check_shape(long long M, long long K, long long N, int n_mod) {
 // host pipeline, the row-sharded multi-GPU driver) without touching B again.  Only
 // with all 16 moduli, where the exponent E is 52 whatever the data; with fewer moduli
 // E depends on the maxima of both operands and the one-shot path below is used.
+// Where the pieces of a prepared right-hand operand sit behind a base address.
+struct BLayout {
+  size_t bmax, nu, sb, sbi, b0, bhi, boddf, bodd, pix, total;
+  size_t flag_row_bytes, b_stride;
+};
+
+static BLayout oz2_b_layout(const Oz2Geom& q, size_t view_pixels) {
+  const int n_odd = 15;
+  BLayout L;
+  Carver cv;
+  L.bmax = cv.take(q.N * 8); L.nu = cv.take(q.N * 4); L.sb = cv.take(q.N * 8); L.sbi = cv.take(q.N * 8);
+  L.b0 = cv.take(static_cast<size_t>(q.N) * q.K0);
+  L.flag_row_bytes = static_cast<size_t>(q.n_chunks) * kChunkUnits * sizeof(uint16_t);
+  L.bhi = cv.take(static_cast<size_t>(q.N) * L.flag_row_bytes);
+  L.boddf = cv.take(static_cast<size_t>(q.N) * L.flag_row_bytes);
+  L.b_stride = static_cast<size_t>(q.N) * q.Kp;
+  L.bodd = cv.take(L.b_stride * n_odd);
+  L.pix = cv.take(view_pixels * 8);
+  L.total = cv.off;
+  return L;
+}
+
+// g.prep <- the operand whose pieces lie behind ws (its planes written or about to be written)
+static void oz2_bind_b(uint8_t* ws, const Oz2Geom& q, const BLayout& L, int bn) {
+  State::Prepared& P = g.prep;
+  P.K = q.K; P.N = q.N; P.Kp = q.Kp; P.K0 = q.K0; P.n_chunks = q.n_chunks; P.last_seg = q.last_seg;
+  P.bn = bn; P.Np = q.Np; P.tiles_n = q.tiles_n;
+  P.bmax = reinterpret_cast<double*>(ws + L.bmax);
+  P.nu = reinterpret_cast<int*>(ws + L.nu);
+  P.sb = reinterpret_cast<double*>(ws + L.sb);
+  P.sbi = reinterpret_cast<double*>(ws + L.sbi);
+  P.b0 = reinterpret_cast<int8_t*>(ws + L.b0);
+  P.b_hi = reinterpret_cast<uint16_t*>(ws + L.bhi);
+  P.b_odd = reinterpret_cast<uint16_t*>(ws + L.boddf);
+  P.bodd = reinterpret_cast<int8_t*>(ws + L.bodd);
+  P.bodd_stride = static_cast<long long>(L.b_stride);
+  oz2_host_consts(16, &P.consts, nullptr);
+}
+
+static int oz2_b_maps(const Oz2Geom& q, int bn) {
+  State::Prepared& P = g.prep;
+  const int n_odd = 15;
+  if (make_plane_map(&P.mB0, P.b0, q.K0, q.N, 1, static_cast<long long>(q.N) * q.K0, bn)) return -1;
+  if (make_plane_map(&P.mB1, P.bodd, q.Kp, q.N, n_odd, P.bodd_stride, bn)) return -1;
+  if (make_plane_map(&P.mB1_half, P.bodd, q.Kp, q.N, n_odd, P.bodd_stride, kBM)) return -1;
+  return 0;
+}
+
+// Right-hand operand of the exact tier, prepared once and kept: nu_j, 2^+-nu_j and
+// the residue planes of B.  Rows of A can then be multiplied block by block (the
+// host pipeline, the row-sharded multi-GPU driver) without touching B again.  Only
+// with all 16 moduli, where the exponent E is 52 whatever the data; with fewer moduli
+// E depends on the maxima of both operands and the one-shot path below is used.
 static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, bool trans = false,
                          const Im2colView* view = nullptr) {
   if (oz2_check_shape(1, K, N, 16)) return -1;
@@ -366,40 +419,22 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
   }
   const Oz2Geom q = oz2_geometry(1, K, N, bn);
   const int n_odd = 15;
-  Carver cv;
-  const size_t o_bmax = cv.take(N * 8), o_nu = cv.take(N * 4), o_sb = cv.take(N * 8), o_sbi = cv.take(N * 8);
-  const size_t o_b0 = cv.take(static_cast<size_t>(N) * q.K0);
-  const size_t flag_bytes = static_cast<size_t>(N) * q.n_chunks * kChunkUnits * sizeof(uint16_t);
-  const size_t o_bhi = cv.take(flag_bytes), o_bodd_f = cv.take(flag_bytes);
-  const size_t b_stride = static_cast<size_t>(N) * q.Kp;
-  const size_t o_bodd = cv.take(b_stride * n_odd);
-  const size_t o_pix = cv.take(view ? static_cast<size_t>(view->batch * view->H * view->W) * 8 : 0);
+  const BLayout L = oz2_b_layout(q, view ? static_cast<size_t>(view->batch * view->H * view->W) : 0);
   g.prep.valid = false;
-  if (cv.off > g.bside_bytes) {
+  if (L.total > g.bside_bytes) {
     B200_CHECK(cudaStreamSynchronize(g.stream));
     if (g.bside) B200_CHECK(cudaFree(g.bside));
     g.bside = nullptr; g.bside_bytes = 0;
-    if (cudaMalloc(&g.bside, cv.off) != cudaSuccess) {
-      fprintf(stderr, "[eshkol-b200] allocation of %zu bytes for the prepared operand failed\n", cv.off);
+    if (cudaMalloc(&g.bside, L.total) != cudaSuccess) {
+      fprintf(stderr, "[eshkol-b200] allocation of %zu bytes for the prepared operand failed\n", L.total);
       cudaGetLastError();
       return -1;
     }
-    g.bside_bytes = cv.off;
+    g.bside_bytes = L.total;
   }
   uint8_t* ws = g.bside;
+  oz2_bind_b(ws, q, L, bn);
   State::Prepared& P = g.prep;
-  P.K = K; P.N = N; P.Kp = q.Kp; P.K0 = q.K0; P.n_chunks = q.n_chunks; P.last_seg = q.last_seg;
-  P.bn = bn; P.Np = q.Np; P.tiles_n = q.tiles_n;
-  P.bmax = reinterpret_cast<double*>(ws + o_bmax);
-  P.nu = reinterpret_cast<int*>(ws + o_nu);
-  P.sb = reinterpret_cast<double*>(ws + o_sb);
-  P.sbi = reinterpret_cast<double*>(ws + o_sbi);
-  P.b0 = reinterpret_cast<int8_t*>(ws + o_b0);
-  P.b_hi = reinterpret_cast<uint16_t*>(ws + o_bhi);
-  P.b_odd = reinterpret_cast<uint16_t*>(ws + o_bodd_f);
-  P.bodd = reinterpret_cast<int8_t*>(ws + o_bodd);
-  P.bodd_stride = static_cast<long long>(b_stride);
-  oz2_host_consts(16, &P.consts, nullptr);
   cudaStream_t st = g.stream;
   const bool timed = g.timing && g.ev_made;
   g.ev_valid = false;
@@ -407,7 +442,7 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
   // trans: B is stored N x K (each column of the operand is a contiguous row), which is the
   // layout the row scan and the non-transposing split of a left-hand operand read
   if (trans) B200_CHECK(launch_scan_rows(dB, N, K, P.bmax, st));
-  else if (view) B200_CHECK(launch_scan_view(*view, N, reinterpret_cast<double*>(ws + o_pix), P.bmax, st));
+  else if (view) B200_CHECK(launch_scan_view(*view, N, reinterpret_cast<double*>(ws + L.pix), P.bmax, st));
   else B200_CHECK(launch_scan_cols(dB, K, N, reinterpret_cast<unsigned long long*>(P.bmax), st));
   B200_CHECK(launch_scales(P.bmax, N, 52, P.nu, P.sb, P.sbi, st));
   B200_MARK(1);
@@ -417,11 +452,44 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
   B200_MARK(2);
   if (timed) ++g.n_evb;
   g.launches += 3;
-  if (make_plane_map(&P.mB0, P.b0, q.K0, N, 1, static_cast<long long>(N) * q.K0, bn)) return -1;
-  if (make_plane_map(&P.mB1, P.bodd, q.Kp, N, n_odd, P.bodd_stride, bn)) return -1;
-  if (make_plane_map(&P.mB1_half, P.bodd, q.Kp, N, n_odd, P.bodd_stride, kBM)) return -1;
+  if (oz2_b_maps(q, bn)) return -1;
   P.valid = true;
   ++g.prep_token;
+  return 0;
+}
+
+// A block of columns [col0, col0 + ncols) of a right-hand operand of N columns, prepared into a
+// caller-owned buffer laid out as oz2_b_layout lays out the whole operand: the ranks of the
+// multi-GPU driver each prepare their share of a panel's columns and exchange the pieces.
+// dB points at the first of those columns, rows ldb elements apart.
+static int oz2_prepare_b_columns(const double* dB, long long ldb, long long K, long long N, long long col0,
+                                 long long ncols, uint8_t* ws) {
+  if (oz2_check_shape(1, K, N, 16) || K > kMaxPreparedK) return -1;
+  if (col0 < 0 || ncols <= 0 || col0 + ncols > N || ldb < ncols) return -1;
+  const Oz2Geom q = oz2_geometry(1, K, N, 256);
+  const int n_odd = 15;
+  const BLayout L = oz2_b_layout(q, 0);
+  double* bmax = reinterpret_cast<double*>(ws + L.bmax) + col0;
+  int* nu = reinterpret_cast<int*>(ws + L.nu) + col0;
+  double* sb = reinterpret_cast<double*>(ws + L.sb) + col0;
+  double* sbi = reinterpret_cast<double*>(ws + L.sbi) + col0;
+  Oz2DeviceConsts hc;
+  oz2_host_consts(16, &hc, nullptr);
+  cudaStream_t st = g.stream;
+  const bool timed = g.timing && g.ev_made;
+  B200_MARK(0);
+  B200_CHECK(launch_scan_cols(dB, K, ncols, reinterpret_cast<unsigned long long*>(bmax), st, ldb));
+  B200_CHECK(launch_scales(bmax, ncols, 52, nu, sb, sbi, st));
+  B200_MARK(1);
+  SplitPlanes pb{ncols, K, q.Kp, q.K0, q.n_chunks, n_odd,
+                 reinterpret_cast<int8_t*>(ws + L.b0) + col0 * q.K0,
+                 reinterpret_cast<uint16_t*>(ws + L.bhi + static_cast<size_t>(col0) * L.flag_row_bytes),
+                 reinterpret_cast<uint16_t*>(ws + L.boddf + static_cast<size_t>(col0) * L.flag_row_bytes),
+                 reinterpret_cast<int8_t*>(ws + L.bodd) + col0 * q.Kp, static_cast<long long>(L.b_stride)};
+  B200_CHECK(launch_split_b(dB, sb, ncols, pb, hc, st, nullptr, ldb));
+  B200_MARK(2);
+  if (timed) ++g.n_evb;
+  g.launches += 3;
   return 0;
 }
 
@@ -1321,6 +1389,49 @@ int eshkol_b200_matmul_backward_f64_host(const double* grad_out, const double* A
 int eshkol_b200_prepare_b_f64_device(const double* dB, uint64_t K, uint64_t N) {
   if (!g.ready || !dB || K == 0 || N == 0) return -1;
   return oz2_prepare_b(dB, static_cast<long long>(K), static_cast<long long>(N), 256);
+}
+
+uint64_t eshkol_b200_prepared_b_bytes(uint64_t K, uint64_t N) {
+  if (K == 0 || N == 0) return 0;
+  return oz2_b_layout(oz2_geometry(1, static_cast<long long>(K), static_cast<long long>(N), 256), 0).total;
+}
+
+int eshkol_b200_prepare_b_columns_f64_device(const double* dB, uint64_t ldb, uint64_t K, uint64_t N, uint64_t col0,
+                                             uint64_t ncols, void* planes) {
+  if (!g.ready || !dB || !planes) return -1;
+  return oz2_prepare_b_columns(dB, static_cast<long long>(ldb), static_cast<long long>(K), static_cast<long long>(N),
+                               static_cast<long long>(col0), static_cast<long long>(ncols),
+                               static_cast<uint8_t*>(planes));
+}
+
+int eshkol_b200_prepared_b_regions(uint64_t K_, uint64_t N_, uint64_t col0, uint64_t ncols, uint64_t out[7][4]) {
+  if (!out || K_ == 0 || N_ == 0 || ncols == 0 || col0 + ncols > N_) return -1;
+  const Oz2Geom q = oz2_geometry(1, static_cast<long long>(K_), static_cast<long long>(N_), 256);
+  const BLayout L = oz2_b_layout(q, 0);
+  const uint64_t c0 = col0, n = ncols;
+  const uint64_t rows[7][4] = {
+      {L.nu + c0 * 4, n * 4, 1, n * 4},
+      {L.sb + c0 * 8, n * 8, 1, n * 8},
+      {L.sbi + c0 * 8, n * 8, 1, n * 8},
+      {L.b0 + c0 * static_cast<uint64_t>(q.K0), n * static_cast<uint64_t>(q.K0), 1, n * static_cast<uint64_t>(q.K0)},
+      {L.bhi + c0 * L.flag_row_bytes, n * L.flag_row_bytes, 1, n * L.flag_row_bytes},
+      {L.boddf + c0 * L.flag_row_bytes, n * L.flag_row_bytes, 1, n * L.flag_row_bytes},
+      {L.bodd + c0 * static_cast<uint64_t>(q.Kp), n * static_cast<uint64_t>(q.Kp), 15, L.b_stride}};
+  memcpy(out, rows, sizeof(rows));
+  return 7;
+}
+
+int eshkol_b200_adopt_prepared_b(void* planes, uint64_t K, uint64_t N) {
+  if (!g.ready || !planes || K == 0 || N == 0) return -1;
+  const long long k = static_cast<long long>(K), n = static_cast<long long>(N);
+  if (oz2_check_shape(1, k, n, 16) || k > kMaxPreparedK) return -1;
+  const Oz2Geom q = oz2_geometry(1, k, n, 256);
+  g.prep.valid = false;
+  oz2_bind_b(static_cast<uint8_t*>(planes), q, oz2_b_layout(q, 0), 256);
+  if (oz2_b_maps(q, 256)) return -1;
+  g.prep.valid = true;
+  ++g.prep_token;
+  return 0;
 }
 
 int eshkol_b200_prepare_a_f64_device(const double* dA, uint64_t M, uint64_t K, uint64_t n_cols_hint) {

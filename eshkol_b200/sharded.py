@@ -34,6 +34,26 @@ def panel_columns(N: int, panels: int, taper) -> list[tuple[int, int]]:
     if taper in (True, "half") and panels >= 2 and w % 512 == 0:
         h = w // 2
         return [(0, h)] + [(h + i * w, w) for i in range(panels - 1)] + [(N - h, h)]
+    if taper == "gentle" and panels >= 2 and w % 2048 == 0:
+        # widths grow by half from w/8 (a panel of residue planes is twice the bytes of its f64
+        # columns, so its exchange hides behind the products of the panel before it only up to a
+        # ratio of about 1.5), stay at about w, and halve down to w/8 at the end
+        up, x = [], w // 8
+        while x < w * 3 // 4:
+            up.append(x)
+            x = (x * 3 // 2 + 255) // 256 * 256
+        down = [w // 2, w // 4, w // 8]
+        mid_total = N - sum(up) - sum(down)
+        n_mid = max(1, -(-mid_total // w))
+        mid = (mid_total // n_mid) // 256 * 256
+        if mid <= 0:
+            return equal
+        widths = up + [mid] * (n_mid - 1) + [mid_total - mid * (n_mid - 1)] + down
+        out, c0 = [], 0
+        for wd in widths:
+            out.append((c0, wd))
+            c0 += wd
+        return out
     if taper == "geometric" and panels >= 2 and w % 2048 == 0:
         ramp = [w // 8, w // 4, w // 2]
         mid_total = N - 2 * sum(ramp)
@@ -156,7 +176,7 @@ class ShardedGemm:
 
     def __init__(self, M: int, K: int, N: int, device, *, tier: int = 0, param: int = 0, src: int = 0,
                  group=None, gemm: Optional[Callable] = None, panels: int = 1, comm_sms: int = 0,
-                 transport: str = "collectives", taper=False):
+                 transport: str = "collectives", taper=False, share_split: bool = False):
         self.M, self.K, self.N = M, K, N
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -179,6 +199,10 @@ class ShardedGemm:
             raise ValueError(f"unknown transport {transport!r}")
         self.transport = "collectives"
         self.Cp = None
+        # share_split (copy-engine transport): every rank scans and splits 1/world of a panel's
+        # columns and the ranks exchange the residue planes, instead of every rank splitting all of B
+        self.split_shared = False
+        self._share_wanted = bool(share_split)
         if transport == "copy_engine" and self.world > 1 and self.backend.on_device:
             # the panel buffer of B and C itself are library allocations the peers open; products
             # write their block of C in place and the peers pull it from there
@@ -328,6 +352,41 @@ class ShardedGemm:
         self._ev_packed = make_events(P)   # on the source rank: panel p packed
         self._ev_slice = make_events(P)    # this rank's K-slice of panel p is in its Bp
         self._ev_block = make_events(P)    # this rank's block of C, panel p, is computed
+        if self._share_wanted and self.backend.prepared:
+            # one buffer of residue planes per panel (the whole prepared B stays resident: 16.3
+            # bytes per element), opened by every peer; this rank writes its share of the columns
+            def make_planes():
+                self._blk_P = [self._DeviceBlock(lib, (int(lib.eshkol_b200_prepared_b_bytes(self.K, wd) + 7) // 8,),
+                                                 self.device) for _, wd in self.cols]
+                return [b.handle() for b in self._blk_P]
+            mine_p = attempt(make_planes)
+            hp = exchange(mine_p)
+            self._addr_P = [None] * W
+            for q in range(W):
+                if q == R:
+                    if mine_p is not None:
+                        self._addr_P[q] = [b.ptr for b in self._blk_P]
+                elif hp[q] is None:
+                    failure.append(f"rank {q} exported no plane buffers")
+                else:
+                    self._addr_P[q] = [attempt(import_mem, h) for h in hp[q]]
+            self._ev_planes = make_events(P)   # this rank's columns of panel p are split
+            self._cparts = [row_partition(wd, W) for _, wd in self.cols]
+            self._regions = []
+            for p, (_, wd) in enumerate(self.cols):
+                per_rank = []
+                for q in range(W):
+                    c0, n = self._cparts[p][q]
+                    out = (ctypes.c_uint64 * 28)()
+                    if n and lib.eshkol_b200_prepared_b_regions(self.K, wd, c0, n, out) != 7:
+                        failure.append("prepared_b_regions failed")
+                    per_rank.append([tuple(int(out[4 * i + j]) for j in range(4)) for i in range(7)] if n else [])
+                self._regions.append(per_rank)
+            if not failure:
+                ncmax = max(n for parts in self._cparts for _, n in parts)
+                # this rank's f64 columns of the panels in flight (the source reads its own B in place)
+                self._bcol = [torch.empty((self.K, ncmax), dtype=torch.float64, device=self.device) for _ in range(3)]
+                self.split_shared = True
         if failure:
             raise RuntimeError(failure[0])
         flat = self._blk_B.tensor
@@ -358,8 +417,13 @@ class ShardedGemm:
                 for q, addr in enumerate(table or []):
                     if addr and q != self.rank:
                         lib.eshkol_b200_ipc_close_mem(addr)
+            for q, addrs in enumerate(getattr(self, "_addr_P", None) or []):
+                if q != self.rank:
+                    for addr in addrs or []:
+                        if addr:
+                            lib.eshkol_b200_ipc_close_mem(addr)
             for table in (getattr(self, "_ev_packed", None), getattr(self, "_ev_slice", None),
-                          getattr(self, "_ev_block", None)):
+                          getattr(self, "_ev_block", None), getattr(self, "_ev_planes", None)):
                 for evs in table or []:
                     for ev in evs or []:
                         if ev:
@@ -372,7 +436,12 @@ class ShardedGemm:
                 if blk is not None:
                     blk.free()
                     setattr(self, name, None)
+            for blk in getattr(self, "_blk_P", None) or []:
+                blk.free()
+            self._blk_P = None
+            self._bcol = None
         self._addr_B = self._addr_C = self._ev_packed = self._ev_slice = self._ev_block = None
+        self._addr_P = self._ev_planes = None
         self.Bp = self.C = self.Cp = None
 
     def _record(self, ev: int, stream) -> None:
@@ -493,6 +562,120 @@ class ShardedGemm:
         dist.barrier(group=self.ctl)
         return self.C
 
+    def _copy2d(self, dst: int, dpitch: int, src: int, spitch: int, width: int, rows: int, stream) -> None:
+        if self.backend.lib.eshkol_b200_copy2d_async(dst, dpitch, src, spitch, width, rows, stream.cuda_stream) != 0:
+            raise RuntimeError("copy2d_async failed")
+
+    def _step_shared_split(self, A_rows: torch.Tensor, B_src: Optional[torch.Tensor]) -> torch.Tensor:
+        """The copy-engine step with the split of B shared: rank r scans and splits columns
+        [c0_r, c0_r + n_r) of every panel (1/world of the work every rank did before) into its
+        place of the panel's plane buffer and pulls the other ranks' pieces from their buffers.
+        Host calls run two panels ahead of the products; one host barrier per panel orders the
+        calls of an interprocess event's record before the peers' calls of its wait."""
+        P, R, W = self.panels, self.rank, self.world
+        lib_h = self.backend.lib
+        cur = torch.cuda.current_stream(self.device)
+        lib = self.backend.stream
+        if self._side is None:
+            self._side = torch.cuda.Stream(self.device)
+        x1, x2, xo, pool = self._x1, self._x2, self._side, self._pull_streams
+        self._mark("start", cur)
+        for st in (x1, x2, xo, *pool):
+            st.wait_stream(cur)
+        lib.wait_stream(cur)
+        if self.rows:
+            self.backend.begin(A_rows, max(wd for _, wd in self.cols))
+            self._mark("A prepared", lib)
+        if R == self.src:
+            if not (B_src.is_contiguous() and B_src.shape == (self.K, self.N)):
+                raise ValueError("B must be a contiguous K x N matrix")
+            for p, (c0, wd) in enumerate(self.cols):
+                self._copy2d(self._addr_B[R] + self.K * c0 * 8, wd * 8, B_src.data_ptr() + c0 * 8, self.N * 8,
+                             wd * 8, self.K, x1)
+                self._mark(f"packed {p}", x1)
+                self._record(self._ev_packed[R][p], x1)
+        dist.barrier(group=self.ctl)
+        bcol_free = [None] * len(self._bcol)
+
+        def stage_prep(p: int) -> None:
+            c0p, wd = self.cols[p]
+            c0, n = self._cparts[p][R]
+            if n:
+                if R == self.src:
+                    src_ptr, ldb = B_src.data_ptr() + (c0p + c0) * 8, self.N
+                else:
+                    slot = p % len(self._bcol)
+                    if bcol_free[slot] is not None:
+                        x1.wait_event(bcol_free[slot])  # the split that read this slot is through
+                    self._wait(self._ev_packed[self.src][p], x1)
+                    self._copy2d(self._bcol[slot].data_ptr(), n * 8, self._addr_B[self.src] + (self.K * c0p + c0) * 8,
+                                 wd * 8, n * 8, self.K, x1)
+                    got = torch.cuda.Event()
+                    got.record(x1)
+                    lib.wait_event(got)
+                    src_ptr, ldb = self._bcol[slot].data_ptr(), n
+                if lib_h.eshkol_b200_prepare_b_columns_f64_device(src_ptr, ldb, self.K, wd, c0, n, self._blk_P[p].ptr) != 0:
+                    raise RuntimeError("prepare_b_columns failed")
+                if R != self.src:
+                    done = torch.cuda.Event()
+                    done.record(lib)
+                    bcol_free[p % len(self._bcol)] = done
+            self._mark(f"own columns {p} split", lib)
+            self._record(self._ev_planes[R][p], lib)
+
+        ahead = 2
+        for p in range(min(ahead, P)):
+            stage_prep(p)
+        for p in range(P):
+            dist.barrier(group=self.ctl)
+            c0p, wd = self.cols[p]
+            for i in range(1, W):
+                q = (R + i) % W
+                if not self._regions[p][q]:
+                    continue
+                st = pool[i % len(pool)]
+                self._wait(self._ev_planes[q][p], st)
+                for off, width, rows, pitch in self._regions[p][q]:
+                    self._copy2d(self._blk_P[p].ptr + off, pitch, self._addr_P[q][p] + off, pitch, width, rows, st)
+            for st in pool:
+                x2.wait_stream(st)
+            arrived = torch.cuda.Event()
+            arrived.record(x2)
+            self._mark(f"planes {p} arrived", x2)
+            if self.rows:
+                lib.wait_event(arrived)
+                self._mark(f"panel {p} products start", lib)
+                if lib_h.eshkol_b200_adopt_prepared_b(self._blk_P[p].ptr, self.K, wd) != 0:
+                    raise RuntimeError("adopt_prepared_b failed")
+                c = self.C[self.row0:self.row0 + self.rows, c0p:c0p + wd]
+                opts = self.backend.api.make_opts(self.backend.tier, self.backend.param, ldc=c.stride(0))
+                if lib_h.eshkol_b200_multiply_prepared_f64_device(c.data_ptr(), ctypes.byref(opts)) != 0:
+                    raise RuntimeError("multiply failed")
+                self._mark(f"panel {p} products done", lib)
+            self._record(self._ev_block[R][p], lib)
+            if p + ahead < P:
+                stage_prep(p + ahead)
+        dist.barrier(group=self.ctl)
+        for p in range(P):
+            for i in range(1, W):
+                q = (R + i) % W
+                if self.parts[q][1] == 0:
+                    continue
+                st = pool[i % len(pool)]
+                self._wait(self._ev_block[q][p], st)
+                self._pull_c_block(q, p, st)
+            for st in pool:
+                xo.wait_stream(st)
+            self._mark(f"panel {p} gathered", xo)
+        cur.wait_stream(lib)
+        cur.wait_stream(xo)
+        cur.wait_stream(x1)
+        cur.wait_stream(x2)
+        self.backend.finish()
+        cur.synchronize()
+        dist.barrier(group=self.ctl)  # nobody overwrites a buffer a peer may still be reading
+        return self.C
+
     def _unpack(self, p: int) -> None:
         """gathered panel p, [rank][row][column in panel] -> its columns of the row-major C"""
         w = self.width
@@ -537,6 +720,8 @@ class ShardedGemm:
         if self.rank == self.src and B_src is None:
             raise ValueError("the source rank must pass B")
         if self.transport == "copy_engine":
+            if self.split_shared:
+                return self._step_shared_split(A_rows, B_src)
             return self._step_copy_engine(A_rows, B_src)
         self._mark("start", cur)
         if dev:

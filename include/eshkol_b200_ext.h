@@ -165,6 +165,31 @@ int eshkol_b200_gemm_prepared_f64_device(const double* dA, double* dC, uint64_t 
 int eshkol_b200_prepare_a_f64_device(const double* dA, uint64_t M, uint64_t K, uint64_t n_cols_hint);
 int eshkol_b200_multiply_prepared_f64_device(double* dC, const EshkolB200GemmOpts* opts);
 
+/* A right-hand operand prepared in pieces, by several GPUs (no counterpart in the reference,
+ * which is single-device).  Preparing B -- the column scan and the split into 16 residue
+ * planes -- is the same work on every GPU that multiplies its own rows of A by that B; these
+ * entry points let each of G ranks prepare 1/G of a panel's columns and fetch the other ranks'
+ * pieces with the copy engines instead (16.3 bytes per element where the f64 panel is 8, but
+ * none of it on the SMs).
+ *   prepared_b_bytes      size of the buffer that holds a whole prepared K x N operand; the
+ *                         caller allocates it (eshkol_b200_mem_alloc, so that peers can open it)
+ *   prepare_b_columns     scans and splits columns [col0, col0 + ncols) of that operand into
+ *                         their places in `planes`; dB points at the first of those columns,
+ *                         consecutive rows ldb elements apart.  Asynchronous
+ *   prepared_b_regions    the seven pieces of those columns inside the buffer, each as
+ *                         {byte offset, bytes per row, rows, pitch}: shifts and both scale
+ *                         vectors, the modulus-256 plane, its two flag planes, and the 15 odd
+ *                         planes as one pitched region -- what a peer copies (copy2d_async)
+ *   adopt_prepared_b      declares that `planes` now holds the complete operand: it becomes the
+ *                         library's prepared right-hand operand (multiply_prepared uses it).
+ *                         The buffer stays the caller's and must outlive its use.
+ * All return 0 / -1 (regions: the number of regions). */
+uint64_t eshkol_b200_prepared_b_bytes(uint64_t K, uint64_t N);
+int eshkol_b200_prepare_b_columns_f64_device(const double* dB, uint64_t ldb, uint64_t K, uint64_t N, uint64_t col0,
+                                             uint64_t ncols, void* planes);
+int eshkol_b200_prepared_b_regions(uint64_t K, uint64_t N, uint64_t col0, uint64_t ncols, uint64_t out[7][4]);
+int eshkol_b200_adopt_prepared_b(void* planes, uint64_t K, uint64_t N);
+
 /* Exact tier on HOST arrays (what eshkol_matmul_dispatch runs for large shapes): B is
  * uploaded and prepared once, then 1024-row blocks of A are uploaded, multiplied and
  * their rows of C downloaded on three streams so PCIe and the tensor cores overlap.
