@@ -231,72 +231,76 @@ __device__ __forceinline__ void chunk_cols(const SplitGeom& g, long long k, long
   *unit = static_cast<long long>(c) * kChunkUnits + (off >> 4);
 }
 
-// A: one thread per 4 consecutive k of one row.  grid = (rows, ceil(Kp/1024)).
+// A: one thread per 8 consecutive k of one row (64 bytes in flight per thread, 8-byte stores);
+// grid = (rows, ceil(Kp/2048)).
+constexpr int kSplitAW = 8;
 __global__ void __launch_bounds__(256) split_a_kernel(const double* __restrict__ A,
                                                       const double* __restrict__ scale,
                                                       const SplitGeom g,
                                                       const __grid_constant__ Oz2DeviceConsts c) {
   const long long row = blockIdx.x;
-  const long long k4 = (static_cast<long long>(blockIdx.y) * 256 + threadIdx.x) * 4;
-  if (k4 >= g.Kp) return;
-  const double* src = A + row * g.K + k4;
-  double a[4];
-  if (k4 + 3 < g.K && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-    const double2 v0 = __ldg(reinterpret_cast<const double2*>(src));
-    const double2 v1 = __ldg(reinterpret_cast<const double2*>(src) + 1);
-    a[0] = v0.x; a[1] = v0.y; a[2] = v1.x; a[3] = v1.y;
+  const long long k8 = (static_cast<long long>(blockIdx.y) * 256 + threadIdx.x) * kSplitAW;
+  if (k8 >= g.Kp) return;
+  const double* src = A + row * g.K + k8;
+  double a[kSplitAW];
+  if (k8 + kSplitAW - 1 < g.K && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+    const double2* s2 = reinterpret_cast<const double2*>(src);
+    const double2 v0 = __ldg(s2), v1 = __ldg(s2 + 1), v2 = __ldg(s2 + 2), v3 = __ldg(s2 + 3);
+    a[0] = v0.x; a[1] = v0.y; a[2] = v1.x; a[3] = v1.y; a[4] = v2.x; a[5] = v2.y; a[6] = v3.x; a[7] = v3.y;
   } else {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) a[e] = (k4 + e < g.K) ? __ldg(src + e) : 0.0;
+    for (int e = 0; e < kSplitAW; ++e) a[e] = (k8 + e < g.K) ? __ldg(src + e) : 0.0;
   }
   const double s = scale[row];
-  double x[4];
-  uint32_t xlo[4];
+  double x[kSplitAW];
+  uint32_t xlo[kSplitAW];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
+  for (int e = 0; e < kSplitAW; ++e) {
     x[e] = trunc(a[e] * s);  // gpu_memory.mm:2541
     xlo[e] = static_cast<uint32_t>(static_cast<long long>(x[e]));
   }
 
-  const long long o = row * g.Kp + k4;
+  const long long o = row * g.Kp + k8;
   // plane 0 is modulus 255, the only one whose residue can come out as +128
   int8_t* dst_odd = g.odd + o;
   {
     const double p_inv = c.p_inv[1];
-    *reinterpret_cast<uint32_t*>(dst_odd) =
+    *reinterpret_cast<uint2*>(dst_odd) = make_uint2(
         pack_bytes4(residue_odd_t<true>(x[0], xlo[0], p_inv, 255), residue_odd_t<true>(x[1], xlo[1], p_inv, 255),
-                    residue_odd_t<true>(x[2], xlo[2], p_inv, 255), residue_odd_t<true>(x[3], xlo[3], p_inv, 255));
+                    residue_odd_t<true>(x[2], xlo[2], p_inv, 255), residue_odd_t<true>(x[3], xlo[3], p_inv, 255)),
+        pack_bytes4(residue_odd_t<true>(x[4], xlo[4], p_inv, 255), residue_odd_t<true>(x[5], xlo[5], p_inv, 255),
+                    residue_odd_t<true>(x[6], xlo[6], p_inv, 255), residue_odd_t<true>(x[7], xlo[7], p_inv, 255)));
   }
 #pragma unroll 7
   for (int l = 1; l < g.n_odd; ++l) {
     const double p_inv = c.p_inv[l + 1];
     const int pi = c.p_i[l + 1];
     dst_odd += g.odd_stride;
-    *reinterpret_cast<uint32_t*>(dst_odd) =
+    *reinterpret_cast<uint2*>(dst_odd) = make_uint2(
         pack_bytes4(residue_odd_t<false>(x[0], xlo[0], p_inv, pi), residue_odd_t<false>(x[1], xlo[1], p_inv, pi),
-                    residue_odd_t<false>(x[2], xlo[2], p_inv, pi), residue_odd_t<false>(x[3], xlo[3], p_inv, pi));
+                    residue_odd_t<false>(x[2], xlo[2], p_inv, pi), residue_odd_t<false>(x[3], xlo[3], p_inv, pi)),
+        pack_bytes4(residue_odd_t<false>(x[4], xlo[4], p_inv, pi), residue_odd_t<false>(x[5], xlo[5], p_inv, pi),
+                    residue_odd_t<false>(x[6], xlo[6], p_inv, pi), residue_odd_t<false>(x[7], xlo[7], p_inv, pi)));
   }
-  // modulus 256: the byte, and the two flag bits of each element gathered into 16-bit
-  // units along k (4 lanes x 4 elements; chunk boundaries are multiples of 16)
-  uint32_t w0 = 0, nib_hi = 0, nib_odd = 0;
+  // modulus 256: the bytes, and the two flag bits of each element gathered into 16-bit
+  // units along k (2 lanes x 8 elements; chunk boundaries are multiples of 16)
+  uint32_t w0 = 0, w1 = 0, b_hi = 0, b_odd = 0;
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
+  for (int e = 0; e < kSplitAW; ++e) {
     const Res256 r = residue_256(xlo[e]);
-    w0 |= r.lo8 << (8 * e);
-    nib_hi |= r.hi << e;
-    nib_odd |= r.odd << e;
+    if (e < 4) w0 |= r.lo8 << (8 * e); else w1 |= r.lo8 << (8 * (e - 4));
+    b_hi |= r.hi << e;
+    b_odd |= r.odd << e;
   }
-  const int sh = 4 * (threadIdx.x & 3);
-  uint32_t u_hi = nib_hi << sh, u_odd = nib_odd << sh;
+  const int sh = 8 * (threadIdx.x & 1);
+  uint32_t u_hi = b_hi << sh, u_odd = b_odd << sh;
   u_hi |= __shfl_xor_sync(0xffffffffu, u_hi, 1);
   u_odd |= __shfl_xor_sync(0xffffffffu, u_odd, 1);
-  u_hi |= __shfl_xor_sync(0xffffffffu, u_hi, 2);
-  u_odd |= __shfl_xor_sync(0xffffffffu, u_odd, 2);
-  if (k4 < g.K) {
+  if (k8 < g.K) {
     long long col, unit;
-    chunk_cols(g, k4, &col, &unit);
-    *reinterpret_cast<uint32_t*>(g.plane0 + row * g.K0 + col) = w0;
-    if ((threadIdx.x & 3) == 0) {
+    chunk_cols(g, k8, &col, &unit);
+    *reinterpret_cast<uint2*>(g.plane0 + row * g.K0 + col) = make_uint2(w0, w1);
+    if ((threadIdx.x & 1) == 0) {
       const long long fo = row * g.n_chunks * kChunkUnits + unit;
       g.flag_hi[fo] = static_cast<uint16_t>(u_hi);
       g.flag_odd[fo] = static_cast<uint16_t>(u_odd);
@@ -411,59 +415,71 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
 }
 
 // ------------------------------------------------------------------------ CRT
-// One thread per 4 consecutive columns of one row.  grid = (M, ceil(N/1024)).
+// One thread per kCrtW consecutive columns of one row.  grid = (M, ceil(N / (256 * kCrtW))).
 // gpu_memory.mm:2632-2640 (S1/S2 in modulus order, fused) and :2650-2653.
+// The kernel is bound by instruction issue, not by HBM (17 bytes in, 8 out per element): eight
+// columns per thread halve the loads and the address arithmetic per element, and the 16
+// independent accumulation chains of a thread keep the FP64 pipe fed.
+constexpr int kCrtW = 8;
 __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
                                                   const __grid_constant__ Oz2DeviceConsts c) {
   const long long i = blockIdx.x;
-  const long long j4 = (static_cast<long long>(blockIdx.y) * 256 + threadIdx.x) * 4;
-  if (j4 >= a.N) return;
-  const long long wo = i * a.ldw + j4;
-  double S1[4] = {0.0, 0.0, 0.0, 0.0}, S2[4] = {0.0, 0.0, 0.0, 0.0};
+  const long long j0 = (static_cast<long long>(blockIdx.y) * 256 + threadIdx.x) * kCrtW;
+  if (j0 >= a.N) return;
+  const long long wo = i * a.ldw + j0;
+  double S1[kCrtW], S2[kCrtW];
   {
     // modulus 256: finish the reduction the products kernel left open -- apply the tie
     // corrections, then centre with the half-even rule (+128 iff the sum is 128 mod 512)
-    const uint2 w = __ldg(reinterpret_cast<const uint2*>(a.w0 + wo));
-    const uint32_t fl = __ldg(a.flip + i * (a.ldw >> 5) + (j4 >> 5)) >> (j4 & 31);
-    const uint32_t raw[4] = {w.x & 0xffffu, w.x >> 16, w.y & 0xffffu, w.y >> 16};
+    const uint4 w = __ldg(reinterpret_cast<const uint4*>(a.w0 + wo));
+    const uint32_t fl = __ldg(a.flip + i * (a.ldw >> 5) + (j0 >> 5)) >> (j0 & 31);
+    const uint32_t raw[kCrtW] = {w.x & 0xffffu, w.x >> 16, w.y & 0xffffu, w.y >> 16,
+                                 w.z & 0xffffu, w.z >> 16, w.w & 0xffffu, w.w >> 16};
     const double s1 = c.sl1[0], s2 = c.sl2[0];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
+    for (int e = 0; e < kCrtW; ++e) {
       const uint32_t x = (raw[e] + (((fl >> e) & 1u) << 8)) & 511u;
       const int v = (x == 128u) ? 128 : static_cast<int>((x + 128u) & 255u) - 128;
       const double wd = static_cast<double>(v);
-      S1[e] = fma(s1, wd, S1[e]);
-      S2[e] = fma(s2, wd, S2[e]);
+      S1[e] = __dmul_rn(s1, wd);  // fma(s1, wd, 0.0): the first term of the sum
+      S2[e] = __dmul_rn(s2, wd);
     }
   }
-  // every plane's word is requested before the first is used (15 loads in flight)
-  uint32_t wv[15];
+  // the planes are fetched in two groups, each group's words requested before its first use
 #pragma unroll
-  for (int l = 1; l < 16; ++l)
-    wv[l - 1] = (l < a.n_mod)
-                    ? __ldg(reinterpret_cast<const uint32_t*>(a.w_odd + (l - 1) * a.w_odd_stride + wo))
-                    : 0u;
+  for (int l0 = 1; l0 < 16; l0 += 8) {
+    uint2 wv[8];
 #pragma unroll
-  for (int l = 1; l < 16; ++l) {
-    if (l < a.n_mod) {
-      // signed byte -> double through the mantissa: (2^52 + (b + 128)) - (2^52 + 128), exact,
-      // on the FP64 add pipe instead of the slower integer-to-double conversion unit
-      const uint32_t w = wv[l - 1] ^ 0x80808080u;
-      const double s1 = c.sl1[l], s2 = c.sl2[l];
+    for (int t = 0; t < 8; ++t) {
+      const int l = l0 + t;
+      wv[t] = (l < 16 && l < a.n_mod)
+                  ? __ldg(reinterpret_cast<const uint2*>(a.w_odd + (l - 1) * a.w_odd_stride + wo))
+                  : make_uint2(0u, 0u);
+    }
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const double wd = __hiloint2double(0x43300000, static_cast<int>((w >> (8 * e)) & 0xffu)) - 4503599627370624.0;
-        S1[e] = fma(s1, wd, S1[e]);
-        S2[e] = fma(s2, wd, S2[e]);
+    for (int t = 0; t < 8; ++t) {
+      const int l = l0 + t;
+      if (l < 16 && l < a.n_mod) {
+        // signed byte -> double through the mantissa: (2^52 + (b + 128)) - (2^52 + 128), exact,
+        // on the FP64 add pipe instead of the slower integer-to-double conversion unit
+        const uint32_t lo = wv[t].x ^ 0x80808080u, hi = wv[t].y ^ 0x80808080u;
+        const double s1 = c.sl1[l], s2 = c.sl2[l];
+#pragma unroll
+        for (int e = 0; e < kCrtW; ++e) {
+          const uint32_t byte = __byte_perm(e < 4 ? lo : hi, 0u, 0x4440 + (e & 3));
+          const double wd = __hiloint2double(0x43300000, static_cast<int>(byte)) - 4503599627370624.0;
+          S1[e] = fma(s1, wd, S1[e]);
+          S2[e] = fma(s2, wd, S2[e]);
+        }
       }
     }
   }
   const double mu_inv = a.inv_scale_a[i];
   const double P1 = c.P1, P2 = c.P2, Pinv = c.Pinv;
-  double out[4];
+  double out[kCrtW];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const long long j = (j4 + e < a.N) ? j4 + e : a.N - 1;
+  for (int e = 0; e < kCrtW; ++e) {
+    const long long j = (j0 + e < a.N) ? j0 + e : a.N - 1;
     const double s = __dadd_rn(S1[e], S2[e]);
     const double Q = round(__dmul_rn(s, Pinv));  // half away from zero, as round()
     const double c1 = fma(-P1, Q, S1[e]);
@@ -476,27 +492,29 @@ __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
   }
   if (a.pixels_per_image > 0) {
 #pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const long long j = j4 + e;
+    for (int e = 0; e < kCrtW; ++e) {
+      const long long j = j0 + e;
       if (j >= a.N) break;
       const long long img = j / a.pixels_per_image, pix = j - img * a.pixels_per_image;
       a.C[(img * a.M + i) * a.pixels_per_image + pix] = out[e];  // [image][row][pixel]
     }
     return;
   }
-  double* dst = a.C + i * a.ldc + j4;
-  if (j4 + 3 < a.N && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
-    // one 32-byte store per thread: whole sectors, a quarter of the store instructions
-    asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst),
-                 "f"(__int_as_float(__double2loint(out[0]))), "f"(__int_as_float(__double2hiint(out[0]))),
-                 "f"(__int_as_float(__double2loint(out[1]))), "f"(__int_as_float(__double2hiint(out[1]))),
-                 "f"(__int_as_float(__double2loint(out[2]))), "f"(__int_as_float(__double2hiint(out[2]))),
-                 "f"(__int_as_float(__double2loint(out[3]))), "f"(__int_as_float(__double2hiint(out[3])))
-                 : "memory");
+  double* dst = a.C + i * a.ldc + j0;
+  if (j0 + kCrtW - 1 < a.N && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+    // 32-byte stores: whole sectors, a quarter of the store instructions
+#pragma unroll
+    for (int h = 0; h < kCrtW / 4; ++h)
+      asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst + 4 * h),
+                   "f"(__int_as_float(__double2loint(out[4 * h]))), "f"(__int_as_float(__double2hiint(out[4 * h]))),
+                   "f"(__int_as_float(__double2loint(out[4 * h + 1]))), "f"(__int_as_float(__double2hiint(out[4 * h + 1]))),
+                   "f"(__int_as_float(__double2loint(out[4 * h + 2]))), "f"(__int_as_float(__double2hiint(out[4 * h + 2]))),
+                   "f"(__int_as_float(__double2loint(out[4 * h + 3]))), "f"(__int_as_float(__double2hiint(out[4 * h + 3])))
+                   : "memory");
   } else {
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
-      if (j4 + e < a.N) dst[e] = out[e];
+    for (int e = 0; e < kCrtW; ++e)
+      if (j0 + e < a.N) dst[e] = out[e];
   }
 }
 
@@ -571,7 +589,7 @@ cudaError_t launch_split_a(const double* A, const double* scale, const SplitPlan
                            const Oz2DeviceConsts& c, cudaStream_t st) {
   cudaError_t e = clear_plane0(p, st);
   if (e != cudaSuccess) return e;
-  const dim3 grid(static_cast<unsigned>(p.rows), static_cast<unsigned>((p.Kp + 1023) / 1024));
+  const dim3 grid(static_cast<unsigned>(p.rows), static_cast<unsigned>((p.Kp + 256 * kSplitAW - 1) / (256 * kSplitAW)));
   if (grid.y > 65535u) return cudaErrorInvalidValue;
   split_a_kernel<<<grid, 256, 0, st>>>(A, scale, make_geom(p), c);
   return cudaGetLastError();
@@ -604,7 +622,7 @@ cudaError_t launch_split_b(const double* B, const double* scale, long long N, co
 
 cudaError_t launch_crt(const CrtArgs& a, const Oz2DeviceConsts& c, cudaStream_t st) {
   if (a.M <= 0 || a.N <= 0) return cudaSuccess;
-  const dim3 grid(static_cast<unsigned>(a.M), static_cast<unsigned>((a.N + 1023) / 1024));
+  const dim3 grid(static_cast<unsigned>(a.M), static_cast<unsigned>((a.N + 256 * kCrtW - 1) / (256 * kCrtW)));
   if (grid.y > 65535u) return cudaErrorInvalidValue;
   crt_kernel<<<grid, 256, 0, st>>>(a, c);
   return cudaGetLastError();

@@ -79,6 +79,8 @@ struct State {
   GemmJob* d_jobs16 = nullptr;  // job table of the 16 modular products, uploaded once
   // row-band pipeline of the one-shot device product: band r+1 is split while band r is
   // multiplied and band r-1 reconstructed, on three streams over two workspace slots
+  bool overlap_prep = false;         // one-shot product: B prepared on a second stream beside A (measured: no gain)
+  cudaEvent_t b_pending = nullptr;   // recorded behind that preparation; the multiplication waits for it
   long long band_rows = 0;  // off unless asked for: measured, the overlap slows the power-capped products as much as it hides
   bool lanes_made = false;
   cudaStream_t s_prep = nullptr, s_post = nullptr;
@@ -411,7 +413,7 @@ static int oz2_b_maps(const Oz2Geom& q, int bn) {
 // with all 16 moduli, where the exponent E is 52 whatever the data; with fewer moduli
 // E depends on the maxima of both operands and the one-shot path below is used.
 static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, bool trans = false,
-                         const Im2colView* view = nullptr) {
+                         const Im2colView* view = nullptr, cudaStream_t on_stream = nullptr) {
   if (oz2_check_shape(1, K, N, 16)) return -1;
   if (K > kMaxPreparedK) {
     fprintf(stderr, "[eshkol-b200] an operand can be prepared on its own only for K <= %lld\n", kMaxPreparedK);
@@ -435,7 +437,7 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
   uint8_t* ws = g.bside;
   oz2_bind_b(ws, q, L, bn);
   State::Prepared& P = g.prep;
-  cudaStream_t st = g.stream;
+  cudaStream_t st = on_stream ? on_stream : g.stream;
   const bool timed = g.timing && g.ev_made;
   g.ev_valid = false;
   B200_MARK(0);
@@ -616,6 +618,11 @@ static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, d
   cudaStream_t st = ln.gemm, sp = ln.post;
   const bool lanes = sp != st;
   cudaEvent_t* tev = ln.tev;
+  if (g.b_pending) {
+    // the right-hand operand was prepared on the side stream
+    B200_CHECK(cudaStreamWaitEvent(st, g.b_pending, 0));
+    g.b_pending = nullptr;
+  }
 
   GemmParams p0 = make_gemm_params();
   p0.tie_bits = tie_bits;
@@ -949,8 +956,25 @@ static int ozaki2_gemm(const double* dA, const double* dB, double* dC, long long
     return ozaki2_gemm_general(dA, dB, dC, M, K, N, n_mod, o);
   }
   if (oz2_check_shape(M, K, N, 16)) return -1;
-  if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256, o.trans_b != 0)) return -1;
+  // Optionally the two operands are prepared side by side on two streams.  Measured at 8192^3
+  // it does not pay (8.70 ms against 8.60 ms one after the other: the column scan beside the
+  // row scan and split runs four times longer), so it is off unless ESHKOL_B200_OVERLAP_PREP=1.
+  cudaStream_t side = nullptr;
+  if (g.overlap_prep && g.band_rows == 0 && make_band_lanes() == 0) {
+    side = g.s_prep;
+    B200_CHECK(cudaEventRecord(g.eb_start, g.stream));
+    B200_CHECK(cudaStreamWaitEvent(side, g.eb_start, 0));
+  }
+  if (oz2_prepare_b(dB, K, N, (o.gemm_tile_n == 128) ? 128 : 256, o.trans_b != 0, nullptr, side)) return -1;
+  if (side) {
+    B200_CHECK(cudaEventRecord(g.eb_done, side));
+    g.b_pending = g.eb_done;
+  }
   const int rc = oz2_gemm_rows(dA, dC, M, o, true);
+  if (g.b_pending) {  // the multiplication never ran: order the stream behind the side stream all the same
+    cudaStreamWaitEvent(g.stream, g.b_pending, 0);
+    g.b_pending = nullptr;
+  }
   g.prep.valid = false;  // dB belongs to the caller and may change before the next call
   return rc;
 }
@@ -1139,6 +1163,8 @@ int eshkol_b200_init(int device) {
   {
     const char* e = getenv("ESHKOL_B200_PAIR_GEMM");
     g.pair_gemm = e && e[0] == '1';
+    e = getenv("ESHKOL_B200_OVERLAP_PREP");
+    g.overlap_prep = e && e[0] == '1';
     e = getenv("ESHKOL_B200_BAND_ROWS");
     if (e && e[0]) eshkol_b200_set_row_bands(atoll(e));
   }
