@@ -379,10 +379,17 @@ def run_b200(args):
         # narrow first and last panels shorten the two transfers nothing hides
         taper = os.environ.get("ESHKOL_B200_TAPER", "gentle" if share else "geometric")
         sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=panels, comm_sms=comm_sms,
-                         transport=transport, taper=taper, share_split=share)
+                         transport=transport, taper=taper, share_split=share, b_in_place=share)
         rows = sg.rows
         A = inputs.uniform(1, (rows, n), device=dev, start=sg.row0 * n)
-        B = inputs.uniform(2, (n, n), device=dev) if rank == 0 else None
+        B = None
+        if rank == 0:
+            # B lives in the buffer the peers have opened, so the source GPU packs nothing
+            B = sg.source_buffer() if sg.b_in_place and sg.split_shared else None
+            if B is not None:
+                B.copy_(inputs.uniform(2, (n, n), device=dev))
+            else:
+                B = inputs.uniform(2, (n, n), device=dev)
         C_local = None
     torch.cuda.synchronize()
 
@@ -641,7 +648,9 @@ def run_b200(args):
         # split again; A is declared changed before every call, as fresh activations would be
         lib.eshkol_gpu_set_residency(1, 32768)
         try:
-            lib.eshkol_matmul_dispatch(hA.data_ptr(), hB.data_ptr(), hC.data_ptr(), n, n, n, 0)
+            for _ in range(3):
+                lib.eshkol_gpu_invalidate(hA.data_ptr(), 0)
+                lib.eshkol_matmul_dispatch(hA.data_ptr(), hB.data_ptr(), hC.data_ptr(), n, n, n, 0)
             moved0 = (ctypes.c_uint64(), ctypes.c_uint64())
             lib.eshkol_b200_transfer_bytes(ctypes.byref(moved0[0]), ctypes.byref(moved0[1]))
             t0 = time.perf_counter()

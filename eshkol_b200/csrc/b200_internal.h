@@ -50,6 +50,11 @@ struct GemmParams {
   int n_chunks;
   // kEpiMod256: per chunk, row and 32 columns, (tie mask, bit-8 mask) of the byte sums
   uint32_t* tie_bits;
+  // kEpiMod256, when tie_list is set: instead of that dense table, only the groups that hold a
+  // tie are recorded, appended through tie_cursor as {row, column word | chunk << 17, tie mask,
+  // bit-8 mask}; the list has room for every group, so nothing can overflow
+  uint4* tie_list;
+  unsigned int* tie_cursor;
   // kEpiF16: the output is the caller's matrix, not a padded plane: rows / columns that exist
   int out_rows, out_cols;
   // set by the launchers: how long a bounded wait may last, and (tests only) whether the
@@ -67,6 +72,8 @@ cudaError_t modgemm_set_attributes();
 // The CUDA-core checker resolves its ties itself; its flip bits must be cleared instead.
 cudaError_t launch_tie_resolve(const GemmParams& prm, uint32_t* flip_bits, int M, int N,
                                cudaStream_t stream);
+// whether a result of this geometry can use the tie list (its packed fields have room)
+inline bool tie_list_fits(long long Np, int n_chunks) { return Np / 32 < (1LL << 17) && n_chunks < (1 << 15); }
 
 // Two-SM variant (b200_modgemm2.cu): pairs of CTAs on 256 x 256 tiles; tmB_half is tiled in
 // boxes of 128 rows.  kEpiModI8 and kEpiRawI32 only.
@@ -92,6 +99,8 @@ inline GemmParams make_gemm_params() {
   p.a_hi = p.a_odd = p.b_odd = p.b_hi = nullptr;
   p.n_chunks = 0;
   p.tie_bits = nullptr;
+  p.tie_list = nullptr;
+  p.tie_cursor = nullptr;
   p.out_rows = p.out_cols = 0;
   p.wait_ns = 2000000000ull;
   p.withhold = 0;

@@ -267,6 +267,7 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             break;
           }
           tc_fence_after();
+          uint32_t tie_g[kHalfCc], bit8_g[kHalfCc];
 #pragma unroll
           for (int c2 = 0; c2 < kHalfCc; ++c2) {
             const int cc = half * kHalfCc + c2;
@@ -286,14 +287,44 @@ modgemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               const uint32_t b8 = pr & 0x01000100u;
               bit8 |= __funnelshift_r(b8, b8, (8 - p2) & 31);
             }
-            uint2* rec = reinterpret_cast<uint2*>(prm.tie_bits) +
-                         ((static_cast<long long>(chunk) * prm.tiles_m * kBM + row) * (prm.ldo / 32) +
-                          static_cast<long long>(it.tn) * (BN / 32) + cc);
-            *rec = make_uint2(tie, bit8);
+            tie_g[c2] = tie;
+            bit8_g[c2] = bit8;
+            if (prm.tie_list == nullptr) {
+              uint2* rec = reinterpret_cast<uint2*>(prm.tie_bits) +
+                           ((static_cast<long long>(chunk) * prm.tiles_m * kBM + row) * (prm.ldo / 32) +
+                            static_cast<long long>(it.tn) * (BN / 32) + cc);
+              *rec = make_uint2(tie, bit8);
+            }
           }
           tc_fence_before();
           mbar_arrive(&acc_empty[buf]);
           ++unit;
+          if (prm.tie_list != nullptr) {
+            // ties are 1 in 256 sums: only the groups of 32 columns that hold one are recorded,
+            // one reservation per warp and chunk
+            uint32_t has[kHalfCc];
+            uint32_t count = 0;
+#pragma unroll
+            for (int c2 = 0; c2 < kHalfCc; ++c2) {
+              has[c2] = __ballot_sync(0xffffffffu, tie_g[c2] != 0u);
+              count += __popc(has[c2]);
+            }
+            if (count != 0u) {
+              uint32_t base = 0;
+              if (lane == 0) base = atomicAdd(prm.tie_cursor, count);
+              base = __shfl_sync(0xffffffffu, base, 0);
+#pragma unroll
+              for (int c2 = 0; c2 < kHalfCc; ++c2) {
+                if (tie_g[c2] != 0u) {
+                  const uint32_t slot = base + __popc(has[c2] & ((1u << lane) - 1u));
+                  const uint32_t cw = static_cast<uint32_t>(it.tn * (BN / 32) + half * kHalfCc + c2);
+                  prm.tie_list[slot] = make_uint4(static_cast<uint32_t>(row), cw | (static_cast<uint32_t>(chunk) << 17),
+                                                  tie_g[c2], bit8_g[c2]);
+                }
+                base += __popc(has[c2]);
+              }
+            }
+          }
           if ((chunk & 63) == 63) {
             // only the sums modulo 512 are wanted: fold before a 16-bit lane can carry into its
             // neighbour (64 chunks add at most 64 * 511 to a lane below 512)
@@ -543,6 +574,45 @@ __global__ void __launch_bounds__(256) tie_resolve_kernel(const uint2* __restric
   if (valid) flip_bits[row * words + cw] = flip;
 }
 
+// The same resolution driven by the list of recorded groups: one warp per record.  The flip
+// words start at zero; records of different chunks may meet in one word, hence the atomic.
+__global__ void __launch_bounds__(256) tie_resolve_list_kernel(const uint4* __restrict__ list,
+                                                               const unsigned int* __restrict__ cursor,
+                                                               uint32_t* __restrict__ flip_bits,
+                                                               GemmParams prm, int M, int N) {
+  const int lane = threadIdx.x & 31;
+  const int words = prm.ldo / 32;
+  const unsigned int n = *cursor;
+  const unsigned int nwarps = (gridDim.x * blockDim.x) >> 5;
+  const uint32_t* a_hi = reinterpret_cast<const uint32_t*>(prm.a_hi);
+  const uint32_t* a_odd = reinterpret_cast<const uint32_t*>(prm.a_odd);
+  const uint32_t* b_hi = reinterpret_cast<const uint32_t*>(prm.b_hi);
+  const uint32_t* b_odd = reinterpret_cast<const uint32_t*>(prm.b_odd);
+  constexpr int kWordsPerChunk = kChunkUnits / 2;  // 32
+  for (unsigned int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n; r += nwarps) {
+    const uint4 rec = __ldg(list + r);
+    const long long row = rec.x;
+    const int cw = static_cast<int>(rec.y & 0x1ffffu), chunk = static_cast<int>(rec.y >> 17);
+    if (row >= M) continue;
+    const long long fa = (row * prm.n_chunks + chunk) * kWordsPerChunk + lane;
+    const uint32_t ahi = __ldg(a_hi + fa), aodd = __ldg(a_odd + fa);
+    uint32_t tie = rec.z, flip = 0;
+    while (tie != 0u) {
+      const int b = __ffs(tie) - 1;  // mask bit p: element 2p, 16+p: 2p+1
+      tie &= tie - 1u;
+      const int e = (b < 16) ? 2 * b : 2 * (b - 16) + 1;
+      const long long col = static_cast<long long>(cw) * 32 + e;
+      if (col >= N) continue;
+      const long long fb = (col * prm.n_chunks + chunk) * kWordsPerChunk + lane;
+      uint32_t x = __popc(ahi & __ldg(b_odd + fb)) ^ __popc(aodd & __ldg(b_hi + fb));
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) x ^= __shfl_xor_sync(0xffffffffu, x, o);
+      flip ^= (((rec.w >> b) & 1u) ^ (x & 1u)) << e;
+    }
+    if (lane == 0 && flip != 0u) atomicXor(flip_bits + row * words + cw, flip);
+  }
+}
+
 }  // namespace
 
 cudaError_t modgemm_set_attributes() {
@@ -582,6 +652,13 @@ cudaError_t launch_modgemm(int bn, int epi, const CUtensorMap& tmA, const CUtens
 
 cudaError_t launch_tie_resolve(const GemmParams& prm, uint32_t* flip_bits, int M, int N,
                                cudaStream_t stream) {
+  if (prm.tie_list != nullptr) {
+    const size_t flip_bytes = static_cast<size_t>(prm.tiles_m) * kBM * (prm.ldo / 32) * sizeof(uint32_t);
+    const cudaError_t e = cudaMemsetAsync(flip_bits, 0, flip_bytes, stream);
+    if (e != cudaSuccess) return e;
+    tie_resolve_list_kernel<<<148 * 8, 256, 0, stream>>>(prm.tie_list, prm.tie_cursor, flip_bits, prm, M, N);
+    return cudaGetLastError();
+  }
   const int words = prm.ldo / 32;
   const long long warps = static_cast<long long>(prm.tiles_m) * kBM * ((words + 31) / 32);
   if (warps <= 0) return cudaSuccess;

@@ -514,8 +514,8 @@ static ALayout oz2_a_layout(const Oz2Geom& q) {
   const size_t w_stride = static_cast<size_t>(q.Mp) * q.Np;
   cv.take(w_stride * 2);
   cv.take(w_stride * n_odd);
-  cv.take(w_stride / 32 * 8 * q.n_chunks);  // tie / bit-8 masks per chunk
-  cv.take(w_stride / 32 * 4);               // flip bits
+  cv.take(1024 + w_stride / 32 * 16 * q.n_chunks);  // tie list: a cursor, then room for a record per group and chunk
+  cv.take(w_stride / 32 * 4);                       // flip bits
   L.total = cv.off;
   return L;
 }
@@ -606,7 +606,7 @@ static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, d
   cv.off = A.end;
   const size_t w_stride = static_cast<size_t>(A.Mp) * P.Np;
   const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
-  const size_t o_tie = cv.take(w_stride / 32 * 8 * A.n_chunks), o_flip = cv.take(w_stride / 32 * 4);
+  const size_t o_tie = cv.take(1024 + w_stride / 32 * 16 * A.n_chunks), o_flip = cv.take(w_stride / 32 * 4);
   if (cv.off > cap) {
     fprintf(stderr, "[eshkol-b200] result of %lld columns exceeds the room reserved when A was prepared\n", P.N);
     return -1;
@@ -625,7 +625,11 @@ static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, d
   }
 
   GemmParams p0 = make_gemm_params();
-  p0.tie_bits = tie_bits;
+  p0.tie_bits = tie_bits + 256;  // the dense table, for shapes whose fields do not fit a list record
+  if (tie_list_fits(P.Np, A.n_chunks) && !o.use_simt_products) {
+    p0.tie_cursor = reinterpret_cast<unsigned int*>(tie_bits);
+    p0.tie_list = reinterpret_cast<uint4*>(tie_bits + 256);
+  }
   p0.tiles_m = A.tiles_m; p0.tiles_n = P.tiles_n; p0.n_jobs = 1;
   p0.kb_per_seg = static_cast<int>(A.K0 / kBK);
   p0.kb_per_unit = kChunkSeg / kBK;
@@ -659,6 +663,7 @@ static int oz2_multiply_at(const State::PreparedA& A, uint8_t* ws, size_t cap, d
     if (tev) B200_CHECK(cudaEventRecord(tev[1], st));
     B200_CHECK(launch_modgemm_simt(kEpiModI8, s1, p1, st));
   } else {
+    if (p0.tie_cursor) B200_CHECK(cudaMemsetAsync(p0.tie_cursor, 0, sizeof(unsigned int), st));
     B200_CHECK(launch_modgemm(P.bn, kEpiMod256, A.mA0, P.mB0, p0, tiles, gemm_sms(), st));
     if (lanes) { B200_CHECK(cudaEventRecord(ln.g0_done, st)); B200_CHECK(cudaStreamWaitEvent(sp, ln.g0_done, 0)); }
     if (tev) B200_CHECK(cudaEventRecord(tev[3], sp));
@@ -837,7 +842,7 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   const size_t o_aodd = cv.take(a_stride * n_odd), o_bodd = cv.take(b_stride * n_odd);
   const size_t w_stride = static_cast<size_t>(q.Mp) * q.Np;
   const size_t o_w0 = cv.take(w_stride * 2), o_wodd = cv.take(w_stride * n_odd);
-  const size_t o_tie = cv.take(w_stride / 32 * 8 * q.n_chunks), o_flip = cv.take(w_stride / 32 * 4);
+  const size_t o_tie = cv.take(1024 + w_stride / 32 * 16 * q.n_chunks), o_flip = cv.take(w_stride / 32 * 4);
   if (ensure_workspace(cv.off) != 0) return -1;
   uint8_t* ws = g.ws;
   uint32_t* tie_bits = reinterpret_cast<uint32_t*>(ws + o_tie);
@@ -891,7 +896,11 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
   p0.kb_per_unit = kChunkSeg / kBK;
   p0.a_hi = a_hi; p0.a_odd = a_oddf; p0.b_odd = b_oddf; p0.b_hi = b_hi;
   p0.n_chunks = q.n_chunks;
-  p0.tie_bits = tie_bits;
+  p0.tie_bits = tie_bits + 256;
+  if (tie_list_fits(q.Np, q.n_chunks) && !o.use_simt_products) {
+    p0.tie_cursor = reinterpret_cast<unsigned int*>(tie_bits);
+    p0.tie_list = reinterpret_cast<uint4*>(tie_bits + 256);
+  }
   p0.group_m = 16;
   p0.jobs = d_jobs;
   p0.out = reinterpret_cast<uint8_t*>(w0);
@@ -920,6 +929,7 @@ static int ozaki2_gemm_general(const double* dA, const double* dB, double* dC, l
     if (make_plane_map(&mB0, b0, q.K0, N, 1, static_cast<long long>(N) * q.K0, bn)) return -1;
     if (make_plane_map(&mA1, aodd, q.Kp, M, n_odd, static_cast<long long>(a_stride), kBM)) return -1;
     if (make_plane_map(&mB1, bodd, q.Kp, N, n_odd, static_cast<long long>(b_stride), bn)) return -1;
+    if (p0.tie_cursor) B200_CHECK(cudaMemsetAsync(p0.tie_cursor, 0, sizeof(unsigned int), st));
     B200_CHECK(launch_modgemm(bn, kEpiMod256, mA0, mB0, p0, tiles, gemm_sms(), st));
     B200_CHECK(launch_tie_resolve(p0, flip_bits, static_cast<int>(M), static_cast<int>(N), st));
     B200_CHECK(launch_modgemm(bn, kEpiModI8, mA1, mB1, p1, tiles * n_odd, gemm_sms(), st));

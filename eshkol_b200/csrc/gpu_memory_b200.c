@@ -546,6 +546,7 @@ typedef struct {
   uint64_t last_use;
   uint64_t prep_token;   /* token of the prepared right-hand operand made from this copy, or 0 */
   int pinned;            /* in use by the call in progress: not evictable */
+  int stale;             /* the host range was written since: the buffer is kept, its contents are not */
 } ResEntry;
 enum { RES_SLOTS = 64 };
 static ResEntry g_res[RES_SLOTS];
@@ -585,12 +586,18 @@ static void res_drop(ResEntry* e) {
   memset(e, 0, sizeof(*e));
 }
 
-static void res_drop_overlapping(const void* host, size_t bytes, const ResEntry* keep) {
+/* every cached range that overlaps [host, host + bytes): the one that is exactly this range keeps
+ * its device buffer and is only marked stale (a host that rewrites a tensor in place, or a result
+ * written to the same place call after call, would otherwise free and allocate the same buffer
+ * every time, and cudaFree synchronises the device); the others are dropped */
+static void res_invalidate_overlapping(const void* host, size_t bytes) {
   const char* lo = (const char*)host;
   const char* hi = lo + (bytes ? bytes : 1);
   for (int i = 0; i < RES_SLOTS; ++i) {
     ResEntry* e = &g_res[i];
-    if (e->host && e != keep && e->host < hi && lo < e->host + e->bytes) res_drop(e);
+    if (!e->host || !(e->host < hi && lo < e->host + e->bytes)) continue;
+    if (e->host == lo && (bytes == 0 || e->bytes == bytes)) { e->stale = 1; e->finger = 0; e->prep_token = 0; }
+    else res_drop(e);
   }
 }
 
@@ -599,9 +606,10 @@ static ResEntry* res_find(const void* host, size_t bytes) {
   for (int i = 0; i < RES_SLOTS; ++i) {
     ResEntry* e = &g_res[i];
     if (e->host == (const char*)host && e->bytes == bytes) {
+      if (e->stale) return NULL;
       if (e->finger != res_fingerprint(host, bytes)) {
-        GPU_LOG("residency: host range %p changed since it was uploaded; dropping the device copy", host);
-        res_drop(e);
+        GPU_LOG("residency: host range %p changed since it was uploaded; its device copy is stale", host);
+        e->stale = 1; e->finger = 0; e->prep_token = 0;
         return NULL;
       }
       e->last_use = ++g_res_clock;
@@ -614,7 +622,15 @@ static ResEntry* res_find(const void* host, size_t bytes) {
 /* a new entry with a device buffer of `bytes`; evicts least recently used copies to stay under
  * the limit; NULL when there is no room (every candidate pinned, or the allocation fails) */
 static ResEntry* res_insert(const void* host, size_t bytes) {
-  res_drop_overlapping(host, bytes, NULL);
+  res_invalidate_overlapping(host, bytes);
+  for (int i = 0; i < RES_SLOTS; ++i) {
+    ResEntry* e = &g_res[i];
+    if (e->host == (const char*)host && e->bytes == bytes) {  /* the stale entry of this very range: reuse its buffer */
+      e->stale = 0; e->finger = 0; e->prep_token = 0; e->pinned = 1;
+      e->last_use = ++g_res_clock;
+      return e;
+    }
+  }
   for (;;) {
     ResEntry* slot = NULL;
     ResEntry* lru = NULL;
@@ -627,7 +643,7 @@ static ResEntry* res_insert(const void* host, size_t bytes) {
       void* d = NULL;
       if (eshkol_b200_mem_alloc(0, bytes, &d) == 0) {
         slot->host = (const char*)host; slot->bytes = bytes; slot->dev = d;
-        slot->finger = 0; slot->prep_token = 0; slot->pinned = 1;
+        slot->finger = 0; slot->prep_token = 0; slot->pinned = 1; slot->stale = 0;
         slot->last_use = ++g_res_clock;
         g_res_bytes += bytes;
         return slot;
@@ -646,7 +662,7 @@ void eshkol_gpu_set_residency(int on, size_t limit_mb) {
 }
 
 void eshkol_gpu_invalidate(const void* host_ptr, size_t bytes) {
-  if (host_ptr) res_drop_overlapping(host_ptr, bytes, NULL);
+  if (host_ptr) res_invalidate_overlapping(host_ptr, bytes);
 }
 
 void eshkol_gpu_residency_clear(void) {

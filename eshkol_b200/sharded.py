@@ -176,7 +176,7 @@ class ShardedGemm:
 
     def __init__(self, M: int, K: int, N: int, device, *, tier: int = 0, param: int = 0, src: int = 0,
                  group=None, gemm: Optional[Callable] = None, panels: int = 1, comm_sms: int = 0,
-                 transport: str = "collectives", taper=False, share_split: bool = False):
+                 transport: str = "collectives", taper=False, share_split: bool = False, b_in_place: bool = False):
         self.M, self.K, self.N = M, K, N
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -203,6 +203,8 @@ class ShardedGemm:
         # columns and the ranks exchange the residue planes, instead of every rank splitting all of B
         self.split_shared = False
         self._share_wanted = bool(share_split)
+        # b_in_place (with share_split): the source keeps B in source_buffer() and nothing is packed
+        self.b_in_place = bool(b_in_place) and bool(share_split)
         if transport == "copy_engine" and self.world > 1 and self.backend.on_device:
             # the panel buffer of B and C itself are library allocations the peers open; products
             # write their block of C in place and the peers pull it from there
@@ -396,6 +398,9 @@ class ShardedGemm:
         self._x1 = torch.cuda.Stream(self.device)
         self._x2 = torch.cuda.Stream(self.device)
         self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(min(4, max(1, W - 1)))]
+        # the blocks of C travel on streams of their own: behind the plane pulls of the last panel
+        # they would not start before the products are nearly over
+        self._gather_streams = [torch.cuda.Stream(self.device) for _ in range(min(4, max(1, W - 1)))]
         self._k_parts = row_partition(self.K, W)
         torch.cuda.synchronize(self.device)
 
@@ -566,6 +571,14 @@ class ShardedGemm:
         if self.backend.lib.eshkol_b200_copy2d_async(dst, dpitch, src, spitch, width, rows, stream.cuda_stream) != 0:
             raise RuntimeError("copy2d_async failed")
 
+    def source_buffer(self) -> Optional[torch.Tensor]:
+        """On the source rank: a K x N tensor inside the buffer the peers have opened.  A caller
+        that keeps (or builds) B there and passes it to step() saves the source GPU the packing
+        of every panel -- the peers then read their columns of B straight out of it."""
+        if self.transport != "copy_engine" or self.rank != self.src or not self.split_shared:
+            return None
+        return self._blk_B.tensor[: self.K * self.N].view(self.K, self.N)
+
     def _step_shared_split(self, A_rows: torch.Tensor, B_src: Optional[torch.Tensor]) -> torch.Tensor:
         """The copy-engine step with the split of B shared: rank r scans and splits columns
         [c0_r, c0_r + n_r) of every panel (1/world of the work every rank did before) into its
@@ -578,21 +591,24 @@ class ShardedGemm:
         lib = self.backend.stream
         if self._side is None:
             self._side = torch.cuda.Stream(self.device)
-        x1, x2, xo, pool = self._x1, self._x2, self._side, self._pull_streams
+        x1, x2, xo, pool, gpool = self._x1, self._x2, self._side, self._pull_streams, self._gather_streams
         self._mark("start", cur)
-        for st in (x1, x2, xo, *pool):
+        for st in (x1, x2, xo, *pool, *gpool):
             st.wait_stream(cur)
         lib.wait_stream(cur)
-        if self.rows:
-            self.backend.begin(A_rows, max(wd for _, wd in self.cols))
-            self._mark("A prepared", lib)
+        # B in place: the source's B already lies in the buffer the peers opened (row pitch N);
+        # otherwise the source packs panel after panel into it (row pitch = the panel's width)
+        direct = self.b_in_place
         if R == self.src:
             if not (B_src.is_contiguous() and B_src.shape == (self.K, self.N)):
                 raise ValueError("B must be a contiguous K x N matrix")
+            if direct and B_src.data_ptr() != self._blk_B.ptr:
+                raise ValueError("b_in_place: the source rank must pass the tensor source_buffer() returned")
             for p, (c0, wd) in enumerate(self.cols):
-                self._copy2d(self._addr_B[R] + self.K * c0 * 8, wd * 8, B_src.data_ptr() + c0 * 8, self.N * 8,
-                             wd * 8, self.K, x1)
-                self._mark(f"packed {p}", x1)
+                if not direct:
+                    self._copy2d(self._addr_B[R] + self.K * c0 * 8, wd * 8, B_src.data_ptr() + c0 * 8, self.N * 8,
+                                 wd * 8, self.K, x1)
+                    self._mark(f"packed {p}", x1)
                 self._record(self._ev_packed[R][p], x1)
         dist.barrier(group=self.ctl)
         bcol_free = [None] * len(self._bcol)
@@ -608,8 +624,12 @@ class ShardedGemm:
                     if bcol_free[slot] is not None:
                         x1.wait_event(bcol_free[slot])  # the split that read this slot is through
                     self._wait(self._ev_packed[self.src][p], x1)
-                    self._copy2d(self._bcol[slot].data_ptr(), n * 8, self._addr_B[self.src] + (self.K * c0p + c0) * 8,
-                                 wd * 8, n * 8, self.K, x1)
+                    if direct:
+                        self._copy2d(self._bcol[slot].data_ptr(), n * 8, self._addr_B[self.src] + (c0p + c0) * 8,
+                                     self.N * 8, n * 8, self.K, x1)
+                    else:
+                        self._copy2d(self._bcol[slot].data_ptr(), n * 8,
+                                     self._addr_B[self.src] + (self.K * c0p + c0) * 8, wd * 8, n * 8, self.K, x1)
                     got = torch.cuda.Event()
                     got.record(x1)
                     lib.wait_event(got)
@@ -624,8 +644,13 @@ class ShardedGemm:
             self._record(self._ev_planes[R][p], lib)
 
         ahead = 2
+        # the first panels' shares are split before this rank's rows of A are: their exchange
+        # then runs beside the preparation of A instead of behind it
         for p in range(min(ahead, P)):
             stage_prep(p)
+        if self.rows:
+            self.backend.begin(A_rows, max(wd for _, wd in self.cols))
+            self._mark("A prepared", lib)
         for p in range(P):
             dist.barrier(group=self.ctl)
             c0p, wd = self.cols[p]
@@ -655,18 +680,12 @@ class ShardedGemm:
             self._record(self._ev_block[R][p], lib)
             if p + ahead < P:
                 stage_prep(p + ahead)
+            # the blocks of C of the panel before this one: every rank has called their records
+            # (they precede this iteration's barrier), so they can be pulled while later panels run
+            if p >= 1:
+                self._gather_panel(p - 1, gpool, xo)
         dist.barrier(group=self.ctl)
-        for p in range(P):
-            for i in range(1, W):
-                q = (R + i) % W
-                if self.parts[q][1] == 0:
-                    continue
-                st = pool[i % len(pool)]
-                self._wait(self._ev_block[q][p], st)
-                self._pull_c_block(q, p, st)
-            for st in pool:
-                xo.wait_stream(st)
-            self._mark(f"panel {p} gathered", xo)
+        self._gather_panel(P - 1, gpool, xo)
         cur.wait_stream(lib)
         cur.wait_stream(xo)
         cur.wait_stream(x1)
@@ -675,6 +694,20 @@ class ShardedGemm:
         cur.synchronize()
         dist.barrier(group=self.ctl)  # nobody overwrites a buffer a peer may still be reading
         return self.C
+
+    def _gather_panel(self, p: int, pool, xo) -> None:
+        """pull every other rank's block of panel p of C into its place, once it is computed"""
+        R, W = self.rank, self.world
+        for i in range(1, W):
+            q = (R + i) % W
+            if self.parts[q][1] == 0:
+                continue
+            st = pool[i % len(pool)]
+            self._wait(self._ev_block[q][p], st)
+            self._pull_c_block(q, p, st)
+        for st in pool:
+            xo.wait_stream(st)
+        self._mark(f"panel {p} gathered", xo)
 
     def _unpack(self, p: int) -> None:
         """gathered panel p, [rank][row][column in panel] -> its columns of the row-major C"""
