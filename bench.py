@@ -378,8 +378,14 @@ def run_b200(args):
         share = os.environ.get("ESHKOL_B200_SHARE_SPLIT", "1") == "1"
         # narrow first and last panels shorten the two transfers nothing hides
         taper = os.environ.get("ESHKOL_B200_TAPER", "gentle" if share else "geometric")
-        sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=panels, comm_sms=comm_sms,
-                         transport=transport, taper=taper, share_split=share, b_in_place=share)
+        # the schedule itself runs in C (include/eshkol_b200_multi.h); ESHKOL_B200_DRIVER=python
+        # selects the same schedule written over torch.distributed, which also has the variants
+        if os.environ.get("ESHKOL_B200_DRIVER", "c") == "c" and share and transport == "copy_engine":
+            from eshkol_b200.sharded import CShardedGemm
+            sg = CShardedGemm(n, n, n, dev, rank=rank, world=world)
+        else:
+            sg = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=panels, comm_sms=comm_sms,
+                             transport=transport, taper=taper, share_split=share, b_in_place=share)
         rows = sg.rows
         A = inputs.uniform(1, (rows, n), device=dev, start=sg.row0 * n)
         B = None
@@ -474,6 +480,7 @@ def run_b200(args):
     # ---- a second transport's number for the sharded configuration (NCCL collectives) ----
     collectives = None
     if sg is not None and sg.transport != "collectives" and want("collectives"):
+        from eshkol_b200.sharded import ShardedGemm
         sg_c = ShardedGemm(n, n, n, dev, tier=eb.TIER_OZAKI2, param=16, panels=4, transport="collectives")
         for _ in range(2):
             step(sg_c)

@@ -574,42 +574,64 @@ __global__ void __launch_bounds__(256) tie_resolve_kernel(const uint2* __restric
   if (valid) flip_bits[row * words + cw] = flip;
 }
 
-// The same resolution driven by the list of recorded groups: one warp per record.  The flip
-// words start at zero; records of different chunks may meet in one word, hence the atomic.
+// The same resolution driven by the list of recorded groups: eight lanes per record, four
+// records per warp at a time (the pass is bound by the latency of its dependent loads -- the
+// record, then the row's flags, then each tied column's flags -- so what counts is how many
+// records are in flight).  A lane holds 16 bytes of each 128-byte flag row.  The flip words
+// start at zero; records of different chunks may meet in one word, hence the atomic.
 __global__ void __launch_bounds__(256) tie_resolve_list_kernel(const uint4* __restrict__ list,
                                                                const unsigned int* __restrict__ cursor,
                                                                uint32_t* __restrict__ flip_bits,
                                                                GemmParams prm, int M, int N) {
-  const int lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31, sub = lane & 7;
   const int words = prm.ldo / 32;
   const unsigned int n = *cursor;
-  const unsigned int nwarps = (gridDim.x * blockDim.x) >> 5;
-  const uint32_t* a_hi = reinterpret_cast<const uint32_t*>(prm.a_hi);
-  const uint32_t* a_odd = reinterpret_cast<const uint32_t*>(prm.a_odd);
-  const uint32_t* b_hi = reinterpret_cast<const uint32_t*>(prm.b_hi);
-  const uint32_t* b_odd = reinterpret_cast<const uint32_t*>(prm.b_odd);
-  constexpr int kWordsPerChunk = kChunkUnits / 2;  // 32
-  for (unsigned int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < n; r += nwarps) {
-    const uint4 rec = __ldg(list + r);
+  const unsigned int ngroups = (gridDim.x * blockDim.x) >> 3;
+  const uint4* a_hi = reinterpret_cast<const uint4*>(prm.a_hi);
+  const uint4* a_odd = reinterpret_cast<const uint4*>(prm.a_odd);
+  const uint4* b_hi = reinterpret_cast<const uint4*>(prm.b_hi);
+  const uint4* b_odd = reinterpret_cast<const uint4*>(prm.b_odd);
+  constexpr int kVecPerChunk = kChunkUnits * 2 / 16;  // 8 vectors of 16 bytes per flag row
+  const unsigned int g0 = (blockIdx.x * blockDim.x + threadIdx.x) >> 3;
+  // every group of the warp runs the same number of rounds (the shuffles below are warp-wide)
+  const unsigned int rounds = (n + ngroups - 1) / ngroups;
+  for (unsigned int it = 0; it < rounds; ++it) {
+    const unsigned int r = g0 + it * ngroups;
+    uint4 rec = make_uint4(0u, 0u, 0u, 0u);
+    if (r < n) rec = __ldg(list + r);
     const long long row = rec.x;
     const int cw = static_cast<int>(rec.y & 0x1ffffu), chunk = static_cast<int>(rec.y >> 17);
-    if (row >= M) continue;
-    const long long fa = (row * prm.n_chunks + chunk) * kWordsPerChunk + lane;
-    const uint32_t ahi = __ldg(a_hi + fa), aodd = __ldg(a_odd + fa);
-    uint32_t tie = rec.z, flip = 0;
-    while (tie != 0u) {
-      const int b = __ffs(tie) - 1;  // mask bit p: element 2p, 16+p: 2p+1
-      tie &= tie - 1u;
-      const int e = (b < 16) ? 2 * b : 2 * (b - 16) + 1;
-      const long long col = static_cast<long long>(cw) * 32 + e;
-      if (col >= N) continue;
-      const long long fb = (col * prm.n_chunks + chunk) * kWordsPerChunk + lane;
-      uint32_t x = __popc(ahi & __ldg(b_odd + fb)) ^ __popc(aodd & __ldg(b_hi + fb));
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) x ^= __shfl_xor_sync(0xffffffffu, x, o);
-      flip ^= (((rec.w >> b) & 1u) ^ (x & 1u)) << e;
+    uint32_t tie = (r < n && row < M) ? rec.z : 0u;
+    uint4 ahi = make_uint4(0u, 0u, 0u, 0u), aodd = ahi;
+    if (tie != 0u) {
+      const long long fa = (row * prm.n_chunks + chunk) * kVecPerChunk + sub;
+      ahi = __ldg(a_hi + fa);
+      aodd = __ldg(a_odd + fa);
     }
-    if (lane == 0 && flip != 0u) atomicXor(flip_bits + row * words + cw, flip);
+    uint32_t flip = 0;
+    while (__any_sync(0xffffffffu, tie != 0u)) {
+      uint32_t x = 0;
+      int b = 0, e = 0;
+      bool live = false;
+      if (tie != 0u) {
+        b = __ffs(tie) - 1;  // mask bit p: element 2p, 16+p: 2p+1
+        tie &= tie - 1u;
+        e = (b < 16) ? 2 * b : 2 * (b - 16) + 1;
+        const long long col = static_cast<long long>(cw) * 32 + e;
+        if (col < N) {
+          live = true;
+          const long long fb = (col * prm.n_chunks + chunk) * kVecPerChunk + sub;
+          const uint4 bo = __ldg(b_odd + fb), bh = __ldg(b_hi + fb);
+          x = __popc(ahi.x & bo.x) ^ __popc(ahi.y & bo.y) ^ __popc(ahi.z & bo.z) ^ __popc(ahi.w & bo.w) ^
+              __popc(aodd.x & bh.x) ^ __popc(aodd.y & bh.y) ^ __popc(aodd.z & bh.z) ^ __popc(aodd.w & bh.w);
+        }
+      }
+      x ^= __shfl_xor_sync(0xffffffffu, x, 1);
+      x ^= __shfl_xor_sync(0xffffffffu, x, 2);
+      x ^= __shfl_xor_sync(0xffffffffu, x, 4);
+      if (live) flip ^= (((rec.w >> b) & 1u) ^ (x & 1u)) << e;
+    }
+    if (sub == 0 && flip != 0u) atomicXor(flip_bits + row * words + cw, flip);
   }
 }
 

@@ -1022,14 +1022,20 @@ static int oz2_matmul_host(const double* hA, const double* hB, double* hC, long 
   if (oz2_check_shape(M, K, N, 16)) return -1;
   long long bm = 1024;
   if (M <= 2048) bm = M;  // too small to be worth splitting
-  // Row blocks: whole blocks of bm rows, then a taper (half of what is left, rounded to a
-  // tile, until at most 256 rows remain) so that what is still to do once the last byte of A
+  // Row blocks: a short ramp (256, 256, 512 rows: the first rows of C start their way back after
+  // a quarter of a block's upload and products, and the download is the stream everything else
+  // has to hide behind), whole blocks of bm rows, then a taper (half of what is left, rounded to
+  // a tile, until at most 256 rows remain) so that what is still to do once the last byte of A
   // has crossed the link -- one block's products and its way back -- is a small block.
-  long long blk_r0[272], blk_rows[272];
+  long long blk_r0[280], blk_rows[280];
   int nblk = 0;
   {
     if (M / bm > 250) bm = round_up((M + 249) / 250, 256);
     long long r0 = 0;
+    if (M > 4096 && bm >= 1024) {
+      const long long ramp[3] = {256, 256, 512};
+      for (long long w : ramp) { blk_r0[nblk] = r0; blk_rows[nblk++] = w; r0 += w; }
+    }
     while (M - r0 > bm) { blk_r0[nblk] = r0; blk_rows[nblk++] = bm; r0 += bm; }
     long long left = M - r0;
     while (M > 2048 && left > 256) {

@@ -81,6 +81,78 @@ def row_partition(M: int, world: int) -> list[tuple[int, int]]:
     return out
 
 
+class CShardedGemm:
+    """The same sharded product driven entirely from C (include/eshkol_b200_multi.h): the ranks
+    meet in a POSIX shared-memory segment, which carries the CUDA IPC handles and the host
+    barriers, so a host that is not Python can do exactly this.  This class only adapts the C
+    handle to the surface of ShardedGemm that the benchmark and the tests use; `name` must be the
+    same fresh string on every rank (torch.distributed, when initialised, is used for nothing but
+    agreeing on it)."""
+
+    transport = "copy_engine (C driver, shared-memory rendezvous)"
+    split_shared = True
+    b_in_place = True
+
+    def __init__(self, M: int, K: int, N: int, device, *, rank: int = 0, world: int = 1, src: int = 0,
+                 name: Optional[str] = None):
+        from . import api
+        self.api = api
+        self.lib = api.load_library()
+        self.M, self.K, self.N = M, K, N
+        self.rank, self.world, self.src = rank, world, src
+        self.device = torch.device(device)
+        index = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        if self.lib.eshkol_b200_init(index) != 0:
+            raise RuntimeError("eshkol_b200_init failed: no usable sm_100 device")
+        if name is None:
+            import os
+            token = [os.getpid() if rank == 0 else 0]
+            if world > 1:
+                dist.broadcast_object_list(token, src=0)
+            name = f"/eshkol-b200-{token[0]}"
+        self.name = name
+        handle = ctypes.c_void_p()
+        if self.lib.eshkol_b200_sharded_open(name.encode(), rank, world, M, K, N, src, ctypes.byref(handle)) != 0:
+            raise RuntimeError("eshkol_b200_sharded_open failed")
+        self._h = handle
+        r0, rr = ctypes.c_uint64(), ctypes.c_uint64()
+        self.lib.eshkol_b200_sharded_rows(self._h, ctypes.byref(r0), ctypes.byref(rr))
+        self.row0, self.rows = int(r0.value), int(rr.value)
+        self.parts = row_partition(M, world)
+        self.cols = panel_columns(N, 4, "gentle")
+        self.panels = len(self.cols)
+        self.C = self._view(self.lib.eshkol_b200_sharded_c_buffer(self._h), (M, N))
+        b = self.lib.eshkol_b200_sharded_b_buffer(self._h)
+        self._B = self._view(b, (K, N)) if b else None
+
+    def _view(self, ptr: int, shape) -> torch.Tensor:
+        class _Block:
+            pass
+        blk = _Block()
+        blk.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": "<f8", "data": (int(ptr), False),
+                                        "version": 2, "strides": None}
+        return torch.as_tensor(blk, device=self.device)
+
+    def source_buffer(self) -> Optional[torch.Tensor]:
+        return self._B
+
+    def step(self, A_rows: torch.Tensor, B_src: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if self.rank == self.src and (B_src is None or B_src.data_ptr() != self._B.data_ptr()):
+            raise ValueError("the source rank must pass the tensor source_buffer() returned")
+        if A_rows.shape != (self.rows, self.K) or not A_rows.is_contiguous():
+            raise ValueError(f"rank {self.rank} expects {self.rows} x {self.K} contiguous rows of A")
+        torch.cuda.current_stream(self.device).synchronize()  # A (and B) are complete before the call
+        if self.lib.eshkol_b200_sharded_step(self._h, A_rows.data_ptr()) != 0:
+            raise RuntimeError("eshkol_b200_sharded_step failed")
+        return self.C
+
+    def close(self) -> None:
+        if self._h is not None:
+            self.C = self._B = None
+            self.lib.eshkol_b200_sharded_close(self._h)
+            self._h = None
+
+
 class _DeviceBackend:
     """The library's device GEMM, with both operands prepared separately when the exact
     tier allows it: A once per step, each column panel of B as it arrives.  The library

@@ -363,6 +363,31 @@ def test_sharded_driver_on_one_device(gpu_lib, tier, param):
     sg.close()
 
 
+def test_c_sharded_driver_on_one_device(gpu_lib):
+    """The multi-GPU schedule as a C host drives it (include/eshkol_b200_multi.h), with one rank:
+    shared-memory session, B in the session's buffer, this rank's columns of every panel split
+    into the panel's plane buffer, the panel adopted and multiplied, two steps in a row.  Same
+    bits as one product.  (With more ranks the same calls run in every process; the benchmark's
+    multi-GPU leg goes through this entry point.)"""
+    import os
+    import torch
+    from eshkol_b200.sharded import CShardedGemm
+    M, K, N = 384, 1500, 8192  # N / 4 a multiple of 2048: the panels ramp as in the benchmark
+    A = torch.from_numpy(inputs.full53(93, (M, K))).cuda()
+    B = inputs.full53(94, (K, N))
+    sg = CShardedGemm(M, K, N, torch.device("cuda", torch.cuda.current_device()), name=f"/eshkol-b200-test-{os.getpid()}")
+    try:
+        assert sg.panels > 4 and sum(w for _, w in sg.cols) == N
+        buf = sg.source_buffer()
+        buf.copy_(torch.from_numpy(B))
+        for _ in range(2):
+            C = sg.step(A, buf).clone()
+        want = gu.gemm(A.cpu().numpy(), B)
+        assert gu.same_bits(C.cpu().numpy(), want)
+    finally:
+        sg.close()
+
+
 def test_sharded_configuration_depth_sampled_rows(gpu_lib):
     """K = 32768 (33 extraction chunks), the depth of the multi-GPU configuration: a few rows
     of A against 2048 columns of B, bit for bit against the oracle."""
