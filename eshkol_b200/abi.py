@@ -180,6 +180,9 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_sharded_c_buffer", vp, [vp])
     sig("eshkol_b200_sharded_step", ctypes.c_int, [vp, vp])
     sig("eshkol_b200_sharded_close", ctypes.c_int, [vp])
+    sig("eshkol_b200_debug_rendezvous", ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                       ctypes.c_int, ctypes.c_double])
+    sig("eshkol_b200_debug_fail_allocation", None, [ctypes.c_int])
     sig("eshkol_b200_debug_fetch", ctypes.c_int, [ctypes.c_int, ctypes.c_int, vp, u64, ctypes.POINTER(u64)])
     sig("eshkol_b200_debug_choose_tier", None, [u64, u64, u64, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)])
     _lib = lib

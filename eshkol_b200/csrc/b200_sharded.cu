@@ -32,6 +32,7 @@
 #include <new>
 
 #include "../../include/eshkol_b200_ext.h"
+#include "../../include/eshkol_b200_testing.h"
 
 namespace {
 
@@ -115,6 +116,56 @@ int barrier(EshkolB200Sharded* s) {
     }
   }
   return c->failed.load() ? -1 : 0;
+}
+
+// The shared segment: rank 0 creates it afresh, the others wait for it to appear and to be
+// initialised.  0 / -1.
+int join_segment(EshkolB200Sharded* s) {
+  const char* name = s->name;
+  const int rank = s->rank;
+  int fd = -1;
+  const double t0 = now_s();
+  if (rank == 0) {
+    shm_unlink(name);
+    fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
+    if (fd < 0 || ftruncate(fd, sizeof(Ctl)) != 0) {
+      fprintf(stderr, "[eshkol-b200] rank 0: cannot create the session segment %s\n", name);
+      if (fd >= 0) close(fd);
+      return -1;
+    }
+  } else {
+    for (;;) {
+      fd = shm_open(name, O_RDWR, 0600);
+      struct stat sb;
+      if (fd >= 0 && fstat(fd, &sb) == 0 && static_cast<size_t>(sb.st_size) >= sizeof(Ctl)) break;
+      if (fd >= 0) close(fd);
+      fd = -1;
+      if (now_s() - t0 > s->timeout_s) {
+        fprintf(stderr, "[eshkol-b200] rank %d: the session segment %s never appeared\n", rank, name);
+        return -1;
+      }
+      usleep(1000);
+    }
+  }
+  void* map = mmap(nullptr, sizeof(Ctl), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
+  close(fd);
+  if (map == MAP_FAILED) return -1;
+  s->ctl = static_cast<Ctl*>(map);
+  if (rank == 0) {
+    s->ctl->arrived.store(0); s->ctl->generation.store(0); s->ctl->failed.store(0);
+    s->ctl->magic.store(kMagic);
+  } else {
+    while (s->ctl->magic.load() != kMagic) {
+      if (now_s() - t0 > s->timeout_s) {
+        fail(s, "the session segment was never initialised");
+        munmap(map, sizeof(Ctl));
+        s->ctl = nullptr;
+        return -1;
+      }
+      usleep(1000);
+    }
+  }
+  return 0;
 }
 
 // (first, count) of part r when n items are cut into `world` contiguous parts
@@ -235,46 +286,7 @@ int eshkol_b200_sharded_open(const char* name, int rank, int world, uint64_t M_,
   const char* te = getenv("ESHKOL_B200_BARRIER_TIMEOUT_S");
   s->timeout_s = (te && atof(te) > 0.0) ? atof(te) : 60.0;
 
-  // ---- the shared segment: rank 0 creates it afresh, the others wait for it ----
-  int fd = -1;
-  const double t0 = now_s();
-  if (rank == 0) {
-    shm_unlink(name);
-    fd = shm_open(name, O_CREAT | O_EXCL | O_RDWR, 0600);
-    if (fd < 0 || ftruncate(fd, sizeof(Ctl)) != 0) {
-      fprintf(stderr, "[eshkol-b200] rank 0: cannot create the session segment %s\n", name);
-      if (fd >= 0) close(fd);
-      delete s;
-      return -1;
-    }
-  } else {
-    for (;;) {
-      fd = shm_open(name, O_RDWR, 0600);
-      struct stat sb;
-      if (fd >= 0 && fstat(fd, &sb) == 0 && static_cast<size_t>(sb.st_size) >= sizeof(Ctl)) break;
-      if (fd >= 0) close(fd);
-      fd = -1;
-      if (now_s() - t0 > s->timeout_s) {
-        fprintf(stderr, "[eshkol-b200] rank %d: the session segment %s never appeared\n", rank, name);
-        delete s;
-        return -1;
-      }
-      usleep(1000);
-    }
-  }
-  void* map = mmap(nullptr, sizeof(Ctl), PROT_READ | PROT_WRITE, MAP_SHARED, fd, 0);
-  close(fd);
-  if (map == MAP_FAILED) { delete s; return -1; }
-  s->ctl = static_cast<Ctl*>(map);
-  if (rank == 0) {
-    s->ctl->arrived.store(0); s->ctl->generation.store(0); s->ctl->failed.store(0);
-    s->ctl->magic.store(kMagic);
-  } else {
-    while (s->ctl->magic.load() != kMagic) {
-      if (now_s() - t0 > s->timeout_s) { fail(s, "the session segment was never initialised"); munmap(map, sizeof(Ctl)); delete s; return -1; }
-      usleep(1000);
-    }
-  }
+  if (join_segment(s) != 0) { delete s; return -1; }
 
   // ---- geometry ----
   s->P = make_panels(s->N, s->col0, s->width);
@@ -354,6 +366,32 @@ int eshkol_b200_sharded_open(const char* name, int rank, int world, uint64_t M_,
   if (barrier(s) != 0) return -1;
   *out = s;
   return 0;
+}
+
+// Tests only: the rendezvous and the barriers of a session without any GPU work.  Runs
+// `barriers` barriers; a rank given fail_at = k marks the session failed instead of entering
+// barrier k and leaves (what a rank does whose step hit an error), leave_at = k makes it leave
+// without a word.  Returns 0, or -1 as soon as a barrier gives up.
+int eshkol_b200_debug_rendezvous(const char* name, int rank, int world, int barriers, int fail_at, int leave_at,
+                                 double timeout_s) {
+  if (!name || world < 1 || world > kMaxRanks || rank < 0 || rank >= world || strlen(name) >= sizeof(EshkolB200Sharded::name))
+    return -1;
+  EshkolB200Sharded* s = new (std::nothrow) EshkolB200Sharded();
+  if (!s) return -1;
+  memset(static_cast<void*>(s), 0, sizeof(*s));
+  snprintf(s->name, sizeof(s->name), "%s", name);
+  s->rank = rank; s->world = world;
+  s->timeout_s = timeout_s > 0.0 ? timeout_s : 60.0;
+  if (join_segment(s) != 0) { delete s; return -1; }
+  int rc = 0;
+  for (int k = 0; k < barriers && rc == 0; ++k) {
+    if (k == leave_at) break;
+    if (k == fail_at) { fail(s, "told to fail"); rc = -1; break; }
+    rc = barrier(s);
+  }
+  munmap(s->ctl, sizeof(Ctl));
+  delete s;
+  return rc;
 }
 
 int eshkol_b200_sharded_rows(const EshkolB200Sharded* s, uint64_t* row0, uint64_t* rows) {

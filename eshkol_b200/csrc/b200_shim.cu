@@ -134,6 +134,16 @@ struct Carver {
   }
 };
 
+static int g_dbg_fail_alloc = 0;  // tests: the n-th device allocation from now fails (0 = off)
+// every device allocation of the library goes through here
+static cudaError_t lib_malloc(void** p, size_t bytes) {
+  if (g_dbg_fail_alloc > 0 && --g_dbg_fail_alloc == 0) {
+    *p = nullptr;
+    return cudaErrorMemoryAllocation;
+  }
+  return cudaMalloc(p, bytes);
+}
+
 static int ensure_workspace(size_t bytes) {
   if (bytes <= g.ws_bytes) return 0;
   B200_CHECK(cudaStreamSynchronize(g.stream));
@@ -143,10 +153,10 @@ static int ensure_workspace(size_t bytes) {
   g.last.valid = false;
   g.prepA.valid = false;
   const size_t want = bytes + (bytes >> 4);  // a little headroom against regrowth
-  cudaError_t e = cudaMalloc(&g.ws, want);
+  cudaError_t e = lib_malloc(reinterpret_cast<void**>(&g.ws), want);
   if (e != cudaSuccess) {
     cudaGetLastError();
-    e = cudaMalloc(&g.ws, bytes);
+    e = lib_malloc(reinterpret_cast<void**>(&g.ws), bytes);
     if (e != cudaSuccess) {
       fprintf(stderr, "[eshkol-b200] workspace allocation of %zu bytes failed: %s\n", bytes,
               cudaGetErrorString(e));
@@ -166,7 +176,7 @@ uint8_t* aux_reserve(size_t bytes) {
   if (g.aux) cudaFree(g.aux);
   g.aux = nullptr;
   g.aux_bytes = 0;
-  if (cudaMalloc(&g.aux, bytes) != cudaSuccess) {
+  if (lib_malloc(reinterpret_cast<void**>(&g.aux), bytes) != cudaSuccess) {
     fprintf(stderr, "[eshkol-b200] scratch allocation of %zu bytes failed\n", bytes);
     cudaGetLastError();
     return nullptr;
@@ -181,7 +191,7 @@ static uint8_t* tbuf_reserve(size_t bytes) {
   if (g.tbuf) cudaFree(g.tbuf);
   g.tbuf = nullptr;
   g.tbuf_bytes = 0;
-  if (cudaMalloc(&g.tbuf, bytes) != cudaSuccess) {
+  if (lib_malloc(reinterpret_cast<void**>(&g.tbuf), bytes) != cudaSuccess) {
     fprintf(stderr, "[eshkol-b200] scratch allocation of %zu bytes failed\n", bytes);
     cudaGetLastError();
     return nullptr;
@@ -427,7 +437,7 @@ static int oz2_prepare_b(const double* dB, long long K, long long N, int bn, boo
     B200_CHECK(cudaStreamSynchronize(g.stream));
     if (g.bside) B200_CHECK(cudaFree(g.bside));
     g.bside = nullptr; g.bside_bytes = 0;
-    if (cudaMalloc(&g.bside, L.total) != cudaSuccess) {
+    if (lib_malloc(reinterpret_cast<void**>(&g.bside), L.total) != cudaSuccess) {
       fprintf(stderr, "[eshkol-b200] allocation of %zu bytes for the prepared operand failed\n", L.total);
       cudaGetLastError();
       return -1;
@@ -1517,7 +1527,7 @@ int eshkol_b200_mem_alloc(int kind, size_t bytes, void** out_ptr) {
   if (!g.ready || !out_ptr || bytes == 0) return -1;
   cudaError_t e;
   switch (kind) {
-    case 0: e = cudaMalloc(out_ptr, bytes); break;
+    case 0: e = lib_malloc(out_ptr, bytes); break;
     case 1: e = cudaMallocManaged(out_ptr, bytes); break;
     case 2: e = cudaMallocHost(out_ptr, bytes); break;
     default: return -1;
@@ -1808,6 +1818,7 @@ int eshkol_b200_get_phase_totals(float ms[7], int counts[3]) {
 }
 
 void eshkol_b200_debug_set_wait_limit_ns(unsigned long long ns) { g_dbg_wait_ns = ns; }
+void eshkol_b200_debug_fail_allocation(int nth) { g_dbg_fail_alloc = nth > 0 ? nth : 0; }
 void eshkol_b200_debug_withhold_arrival(int on) { g_dbg_withhold = on ? 1 : 0; }
 
 uint64_t eshkol_b200_launch_count(void) { return g.launches; }

@@ -41,6 +41,19 @@ void eshkol_b200_debug_gemm_calibrate(int idx, double work_flop, double measured
 void eshkol_b200_debug_set_wait_limit_ns(unsigned long long ns);
 void eshkol_b200_debug_withhold_arrival(int on);
 
+/* Tests only: the nth device allocation the library makes from now on fails as if the device
+ * were out of memory (0 switches the hook off).  The call that needed it must fail loudly --
+ * -1, or NaN from a void dispatcher -- and the library must stay usable. */
+void eshkol_b200_debug_fail_allocation(int nth);
+
+/* Tests only: the rendezvous and the host barriers of a multi-GPU session
+ * (eshkol_b200_multi.h) without any GPU work.  Every rank runs `barriers` barriers; a rank given
+ * fail_at = k marks the session failed instead of entering barrier k, a rank given leave_at = k
+ * leaves silently before it.  Returns 0, or -1 as soon as one of this rank's barriers gives up
+ * (a failed peer: at once; a missing peer: after timeout_s). */
+int eshkol_b200_debug_rendezvous(const char* name, int rank, int world, int barriers, int fail_at, int leave_at,
+                                 double timeout_s);
+
 #ifdef __cplusplus
 }
 #endif

@@ -342,6 +342,52 @@ def test_buffer_api_rejects_buffers_smaller_than_their_operands(gpu_lib):
         lib.eshkol_gpu_free(ctypes.byref(x))
 
 
+def test_an_allocation_failure_is_loud_and_leaves_the_library_usable(gpu_lib):
+    """Host-side failure injection: the n-th device allocation of the library is made to fail, as
+    an exhausted device would.  The device entry point returns -1, the void dispatcher fills C
+    with NaN instead of leaving a number of unknown provenance, and the very next call works."""
+    import torch
+    lib = gpu_lib
+    n = 700  # a shape no earlier test used, so the product has to grow the library's scratch
+    A = inputs.uniform(77, (n + 3000, n))
+    B = inputs.uniform(78, (n, n + 5000))
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    dC = torch.zeros((A.shape[0], B.shape[1]), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    lib.eshkol_gpu_residency_clear()
+    lib.eshkol_b200_shutdown()           # drop every grow-only block: the next product must allocate
+    assert lib.eshkol_b200_init(torch.cuda.current_device()) == 0
+    lib.eshkol_b200_debug_fail_allocation(1)
+    try:
+        rc = lib.eshkol_b200_gemm_f64_device(dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), A.shape[0], n, B.shape[1], None)
+        assert rc == -1
+    finally:
+        lib.eshkol_b200_debug_fail_allocation(0)
+    assert api.sync_status() == 0
+    # the dispatcher: every allocation of the call fails in turn until the call gets through
+    old = lib.eshkol_gpu_get_threshold()
+    lib.eshkol_gpu_set_threshold(1)
+    try:
+        failures = 0
+        for nth in range(1, 8):
+            C = np.zeros((64, 96))
+            lib.eshkol_gpu_residency_clear()
+            lib.eshkol_b200_shutdown()
+            assert lib.eshkol_b200_init(torch.cuda.current_device()) == 0
+            lib.eshkol_b200_debug_fail_allocation(nth)
+            lib.eshkol_matmul_dispatch(A[:64].ctypes.data, B[:, :96].copy().ctypes.data, C.ctypes.data, 64, n, 96, 0)
+            lib.eshkol_b200_debug_fail_allocation(0)
+            if np.isnan(C).all():
+                failures += 1
+            else:
+                assert gu.same_bits(C, ol.oz2_exact(A[:64], np.ascontiguousarray(B[:, :96]), 52))
+        assert failures >= 1
+    finally:
+        lib.eshkol_b200_debug_fail_allocation(0)
+        lib.eshkol_gpu_set_threshold(old)
+    assert gu.same_bits(gu.gemm(A[:64], B[:, :96]), ol.oz2_exact(A[:64], np.ascontiguousarray(B[:, :96]), 52))
+
+
 def test_reduced_tiers_refuse_k_beyond_their_int32_bound(gpu_lib):
     """One int8 product of the slice tier is exact only while K * 127^2 < 2^31
     (lib/backend/gpu/gpu_memory_cuda.cpp:351-361): the slice and fast tiers say so and return -1;

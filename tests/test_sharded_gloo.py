@@ -80,3 +80,63 @@ def test_transport_argument():
     assert torch.equal(sg.step(A, B), A @ B)
     with pytest.raises(ValueError):
         ShardedGemm(8, 4, 6, "cpu", gemm=gemm, transport="carrier-pigeon")
+
+
+def _rendezvous_worker(name, rank, world, barriers, fail_at, leave_at, timeout_s, q):
+    import ctypes
+    import eshkol_b200 as eb
+    lib = ctypes.CDLL(eb.library_path())
+    lib.eshkol_b200_debug_rendezvous.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                                 ctypes.c_int, ctypes.c_double]
+    import time
+    t0 = time.perf_counter()
+    rc = lib.eshkol_b200_debug_rendezvous(name.encode(), rank, world, barriers, fail_at, leave_at, timeout_s)
+    q.put((rank, rc, time.perf_counter() - t0))
+
+
+def _run_rendezvous(world, barriers, fail_rank=-1, fail_at=-1, leave_rank=-1, leave_at=-1, timeout_s=2.0):
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    name = f"/eshkol-b200-cputest-{os.getpid()}-{_free_port()}"
+    procs = [ctx.Process(target=_rendezvous_worker,
+                         args=(name, r, world, barriers, fail_at if r == fail_rank else -1,
+                               leave_at if r == leave_rank else -1, timeout_s, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    out = dict()
+    for _ in procs:
+        r, rc, dt = q.get(timeout=60)
+        out[r] = (rc, dt)
+    for p in procs:
+        p.join(timeout=30)
+    try:
+        os.unlink("/dev/shm" + name)
+    except OSError:
+        pass
+    return out
+
+
+def test_c_session_barriers_all_ranks_arrive():
+    """The shared-memory rendezvous of the C multi-GPU driver (include/eshkol_b200_multi.h), without
+    any GPU: four processes meet in the segment and pass 200 barriers."""
+    out = _run_rendezvous(4, 200)
+    assert all(rc == 0 for rc, _ in out.values()), out
+
+
+def test_c_session_a_failed_rank_releases_the_others_at_once():
+    """A rank whose step hit an error marks the session failed and leaves; the others' next
+    barrier returns -1 instead of waiting for it (host-side failure detection: nothing on a GPU
+    is made to fail)."""
+    out = _run_rendezvous(3, 50, fail_rank=1, fail_at=20, timeout_s=20.0)
+    assert all(rc == -1 for rc, _ in out.values()), out
+    assert all(dt < 10.0 for _, dt in out.values()), out  # well before the 20 s timeout
+
+
+def test_c_session_a_rank_that_leaves_is_noticed_by_timeout():
+    """A rank that leaves between steps without a word: the others' barrier gives up after its
+    timeout and returns -1; the rank that left saw no error."""
+    out = _run_rendezvous(3, 50, leave_rank=2, leave_at=10, timeout_s=1.5)
+    assert out[2][0] == 0
+    assert out[0][0] == -1 and out[1][0] == -1
+    assert all(1.0 < out[r][1] < 20.0 for r in (0, 1)), out
