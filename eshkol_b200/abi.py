@@ -107,6 +107,13 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_gpu_get_threshold", ctypes.c_size_t, [])
     sig("eshkol_gpu_should_use", ctypes.c_int, [ctypes.c_size_t])
     sig("eshkol_gpu_elementwise_f64", ctypes.c_int, [bufp, bufp, bufp, u64, ctypes.c_int])
+    sig("eshkol_gpu_reduce_f64", ctypes.c_int, [bufp, bufp, u64, ctypes.c_int])
+    sig("eshkol_gpu_reduce_axis_f64", ctypes.c_int, [bufp, bufp, u64, ctypes.POINTER(u64), u64, ctypes.c_int])
+    sig("eshkol_gpu_transpose_f64", ctypes.c_int, [bufp, bufp, u64, u64])
+    sig("eshkol_gpu_softmax_f64", ctypes.c_int, [bufp, bufp, u64, u64])
+    sig("eshkol_gpu_normalize_f64", ctypes.c_int, [bufp, bufp, u64, u64, ctypes.c_double, ctypes.c_double, ctypes.c_double])
+    sig("eshkol_gpu_batchnorm_backward_f64", ctypes.c_int, [bufp] * 8 + [u64, u64])
+    sig("eshkol_gpu_layernorm_backward_f64", ctypes.c_int, [bufp] * 6 + [u64, u64])
     sig("eshkol_matmul_dispatch", None, [vp, vp, vp, u64, u64, u64, i32])
     sig("eshkol_batch_matmul_dispatch", None, [vp, vp, vp, i64, i64, i64, i64, i32])
     sig("eshkol_gpu_conv2d_f64", ctypes.c_int, [vp, i64, i64, i64, i64, vp, i64, i64, i64, i64, i64, vp, i32])
@@ -137,6 +144,13 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_copy_h2d", ctypes.c_int, [vp, vp, ctypes.c_size_t])
     sig("eshkol_b200_copy_d2h", ctypes.c_int, [vp, vp, ctypes.c_size_t])
     sig("eshkol_b200_elementwise_f64_device", ctypes.c_int, [vp, vp, vp, u64, ctypes.c_int])
+    sig("eshkol_b200_reduce_f64_device", ctypes.c_int, [vp, vp, u64, ctypes.c_int])
+    sig("eshkol_b200_reduce_axis_f64_device", ctypes.c_int, [vp, vp, u64, u64, u64, ctypes.c_int])
+    sig("eshkol_b200_transpose_f64_device", ctypes.c_int, [vp, vp, u64, u64])
+    sig("eshkol_b200_softmax_f64_device", ctypes.c_int, [vp, vp, u64, u64])
+    sig("eshkol_b200_normalize_f64_device", ctypes.c_int, [vp, vp, u64, u64, ctypes.c_double, ctypes.c_double, ctypes.c_double])
+    sig("eshkol_b200_batchnorm_backward_f64_device", ctypes.c_int, [vp] * 8 + [u64, u64])
+    sig("eshkol_b200_layernorm_backward_f64_device", ctypes.c_int, [vp] * 6 + [u64, u64])
     sig("eshkol_b200_sync_status", ctypes.c_int, [])
     sig("eshkol_b200_set_pair_gemm", None, [ctypes.c_int])
     sig("eshkol_b200_set_sm_limit", None, [ctypes.c_int])

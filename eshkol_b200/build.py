@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libeshkol_gpu_b200.so")
 
-CU_SOURCES = ["b200_modgemm.cu", "b200_modgemm2.cu", "b200_ozaki2.cu", "b200_tiers.cu", "b200_shim.cu", "b200_static_scratch.cu", "b200_staging.cu", "b200_sharded.cu"]
+CU_SOURCES = ["b200_modgemm.cu", "b200_modgemm2.cu", "b200_ozaki2.cu", "b200_tiers.cu", "b200_shim.cu", "b200_static_scratch.cu", "b200_staging.cu", "b200_sharded.cu", "b200_operators.cu"]
 C_SOURCES = ["gpu_memory_b200.c", "rt_conv2d_b200.c"]
 HEADERS = ["b200_common.cuh", "b200_internal.h", "b200_ozaki2.h", "b200_residue.cuh", "b200_tiers.h"]
 

@@ -452,25 +452,72 @@ int eshkol_gpu_elementwise_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPU
   return eshkol_b200_sync_status() == 0 ? 0 : -1;
 }
 
-/* ----------------------------------------- operators outside this path ---- */
+/* ------------------------------------------------ the other operators ---- */
+/* Device buffers only, like the reference's CUDA branch (gpu_memory_cuda.cpp:1229-1560); where
+ * the reference then falls back to a CPU loop on host_ptr, these return -1 and the caller's own
+ * CPU path runs (vm_gpu_dispatch.h treats any non-zero result that way). */
+static int on_device(const EshkolGPUBuffer* b, uint64_t doubles, const char* who) {
+  if (!b || !b->device_ptr || g_backend != ESHKOL_GPU_CUDA) return 0;
+  if (b->size_bytes / 8 < doubles) {
+    fprintf(stderr, "[GPU] %s: a buffer holds fewer than %llu doubles\n", who, (unsigned long long)doubles);
+    return 0;
+  }
+  return 1;
+}
+static int operator_done(EshkolGPUBuffer* out) {
+  if (out->flags & FLAG_WRAPPED) out->flags |= FLAG_DIRTY;
+  return eshkol_b200_sync_status() == 0 ? 0 : -1;
+}
+
 int eshkol_gpu_reduce_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t n, EshkolReduceOp op) {
-  (void)in; (void)out; (void)n; (void)op; return -1;
+  if (!in || !out || n == 0) return -1;
+  if (!on_device(in, n, "eshkol_gpu_reduce_f64") || !on_device(out, 1, "eshkol_gpu_reduce_f64")) return -1;
+  if (eshkol_b200_reduce_f64_device((const double*)in->device_ptr, (double*)out->device_ptr, n, (int)op)) return -1;
+  return operator_done(out);
 }
 int eshkol_gpu_reduce_axis_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t rank,
                                const uint64_t* shape, uint64_t axis, EshkolReduceOp op) {
-  (void)in; (void)out; (void)rank; (void)shape; (void)axis; (void)op; return -1;
+  if (!in || !out || !shape || rank == 0 || axis >= rank) return -1;
+  uint64_t outer = 1, inner = 1;
+  for (uint64_t i = 0; i < axis; ++i) outer *= shape[i];
+  for (uint64_t i = axis + 1; i < rank; ++i) inner *= shape[i];
+  const uint64_t len = shape[axis];
+  if (outer == 0 || inner == 0 || len == 0) return -1;
+  if (!on_device(in, outer * len * inner, "eshkol_gpu_reduce_axis_f64") ||
+      !on_device(out, outer * inner, "eshkol_gpu_reduce_axis_f64"))
+    return -1;
+  if (eshkol_b200_reduce_axis_f64_device((const double*)in->device_ptr, (double*)out->device_ptr, outer, len,
+                                         inner, (int)op))
+    return -1;
+  return operator_done(out);
 }
 int eshkol_gpu_transpose_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t rows, uint64_t cols) {
-  (void)in; (void)out; (void)rows; (void)cols; return -1;
+  if (!in || !out || rows == 0 || cols == 0) return -1;
+  if (!on_device(in, rows * cols, "eshkol_gpu_transpose_f64") || !on_device(out, rows * cols, "eshkol_gpu_transpose_f64"))
+    return -1;
+  if (eshkol_b200_transpose_f64_device((const double*)in->device_ptr, (double*)out->device_ptr, rows, cols)) return -1;
+  return operator_done(out);
 }
 int eshkol_gpu_softmax_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t num_slices,
                            uint64_t slice_len) {
-  (void)in; (void)out; (void)num_slices; (void)slice_len; return -1;
+  if (!in || !out || num_slices == 0 || slice_len == 0) return -1;
+  if (!on_device(in, num_slices * slice_len, "eshkol_gpu_softmax_f64") ||
+      !on_device(out, num_slices * slice_len, "eshkol_gpu_softmax_f64"))
+    return -1;
+  if (eshkol_b200_softmax_f64_device((const double*)in->device_ptr, (double*)out->device_ptr, num_slices, slice_len))
+    return -1;
+  return operator_done(out);
 }
 int eshkol_gpu_normalize_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t num_slices,
                              uint64_t slice_len, double gamma, double beta, double epsilon) {
-  (void)in; (void)out; (void)num_slices; (void)slice_len; (void)gamma; (void)beta; (void)epsilon;
-  return -1;
+  if (!in || !out || num_slices == 0 || slice_len == 0) return -1;
+  if (!on_device(in, num_slices * slice_len, "eshkol_gpu_normalize_f64") ||
+      !on_device(out, num_slices * slice_len, "eshkol_gpu_normalize_f64"))
+    return -1;
+  if (eshkol_b200_normalize_f64_device((const double*)in->device_ptr, (double*)out->device_ptr, num_slices,
+                                       slice_len, gamma, beta, epsilon))
+    return -1;
+  return operator_done(out);
 }
 /* tier of one GEMM of a conv2d gradient: what the forward product of that shape would get */
 static void conv_grad_opts(uint64_t M, uint64_t K, uint64_t N, EshkolB200GemmOpts* o) {
@@ -526,15 +573,50 @@ int eshkol_gpu_conv2d_backward_kernel_f64(EshkolGPUBuffer* grad_out, EshkolGPUBu
   if (grad_kernel->flags & FLAG_WRAPPED) grad_kernel->flags |= FLAG_DIRTY;
   return eshkol_b200_sync_status() == 0 ? 0 : -1;
 }
-int eshkol_gpu_batchnorm_backward_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
-    EshkolGPUBuffer* d, EshkolGPUBuffer* e, EshkolGPUBuffer* f, EshkolGPUBuffer* g2,
-    EshkolGPUBuffer* h, uint64_t n0, uint64_t n1) {
-  (void)a; (void)b; (void)c; (void)d; (void)e; (void)f; (void)g2; (void)h; (void)n0; (void)n1;
-  return -1;
+int eshkol_gpu_batchnorm_backward_f64(EshkolGPUBuffer* grad_out, EshkolGPUBuffer* saved_input,
+    EshkolGPUBuffer* saved_mean, EshkolGPUBuffer* saved_inv_std, EshkolGPUBuffer* saved_gamma,
+    EshkolGPUBuffer* grad_input, EshkolGPUBuffer* grad_gamma, EshkolGPUBuffer* grad_beta,
+    uint64_t batch_size, uint64_t feature_size) {
+  /* gpu_memory.h:426; kernel lib/backend/gpu/gpu_cuda_kernels.cu:489-521 */
+  static const char* who = "eshkol_gpu_batchnorm_backward_f64";
+  if (!grad_out || !saved_input || !saved_mean || !saved_inv_std || !saved_gamma || !grad_input || !grad_gamma ||
+      !grad_beta || batch_size == 0 || feature_size == 0)
+    return -1;
+  const uint64_t all = batch_size * feature_size;
+  if (!on_device(grad_out, all, who) || !on_device(saved_input, all, who) || !on_device(saved_mean, feature_size, who) ||
+      !on_device(saved_inv_std, feature_size, who) || !on_device(saved_gamma, feature_size, who) ||
+      !on_device(grad_input, all, who) || !on_device(grad_gamma, feature_size, who) ||
+      !on_device(grad_beta, feature_size, who))
+    return -1;
+  if (eshkol_b200_batchnorm_backward_f64_device((const double*)grad_out->device_ptr,
+          (const double*)saved_input->device_ptr, (const double*)saved_mean->device_ptr,
+          (const double*)saved_inv_std->device_ptr, (const double*)saved_gamma->device_ptr,
+          (double*)grad_input->device_ptr, (double*)grad_gamma->device_ptr, (double*)grad_beta->device_ptr,
+          batch_size, feature_size))
+    return -1;
+  if (grad_gamma->flags & FLAG_WRAPPED) grad_gamma->flags |= FLAG_DIRTY;
+  if (grad_beta->flags & FLAG_WRAPPED) grad_beta->flags |= FLAG_DIRTY;
+  return operator_done(grad_input);
 }
-int eshkol_gpu_layernorm_backward_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* c,
-    EshkolGPUBuffer* d, EshkolGPUBuffer* e, EshkolGPUBuffer* f, uint64_t n0, uint64_t n1) {
-  (void)a; (void)b; (void)c; (void)d; (void)e; (void)f; (void)n0; (void)n1; return -1;
+int eshkol_gpu_layernorm_backward_f64(EshkolGPUBuffer* grad_out, EshkolGPUBuffer* saved_input,
+    EshkolGPUBuffer* saved_mean, EshkolGPUBuffer* saved_inv_std, EshkolGPUBuffer* saved_gamma,
+    EshkolGPUBuffer* grad_input, uint64_t num_samples, uint64_t feature_size) {
+  /* gpu_memory.h:437; kernel lib/backend/gpu/gpu_cuda_kernels.cu:524-555 */
+  static const char* who = "eshkol_gpu_layernorm_backward_f64";
+  if (!grad_out || !saved_input || !saved_mean || !saved_inv_std || !saved_gamma || !grad_input ||
+      num_samples == 0 || feature_size == 0)
+    return -1;
+  const uint64_t all = num_samples * feature_size;
+  if (!on_device(grad_out, all, who) || !on_device(saved_input, all, who) || !on_device(saved_mean, num_samples, who) ||
+      !on_device(saved_inv_std, num_samples, who) || !on_device(saved_gamma, feature_size, who) ||
+      !on_device(grad_input, all, who))
+    return -1;
+  if (eshkol_b200_layernorm_backward_f64_device((const double*)grad_out->device_ptr,
+          (const double*)saved_input->device_ptr, (const double*)saved_mean->device_ptr,
+          (const double*)saved_inv_std->device_ptr, (const double*)saved_gamma->device_ptr,
+          (double*)grad_input->device_ptr, num_samples, feature_size))
+    return -1;
+  return operator_done(grad_input);
 }
 
 /* ------------------------------------------------- residency of operands ---- */

@@ -261,6 +261,30 @@ int eshkol_b200_copy_d2h(void* host_dst, const void* device_src, size_t bytes);
 int eshkol_b200_elementwise_f64_device(const double* a, const double* b, double* out,
                                        uint64_t n, int op);
 
+/* The backend's other tensor operators on device-resident doubles (asynchronous on the library
+ * stream; -1 on bad arguments).  Arithmetic follows the reference's kernels in
+ * lib/backend/gpu/gpu_cuda_kernels.cu -- reduce :76-141 (op: 0 sum, 1 product, 2 min, 3 max,
+ * 4 mean; min / max ignore NaN), axis reduce :147-180 (the tensor seen as
+ * [outer][axis_len][inner]), transpose :189-213, softmax :319-343 (a zero sum divides by 1),
+ * normalize :364-389 (population variance, rsqrt), batchnorm / layernorm backward :489-555 --
+ * with sums shared by the threads of a warp or block, so they agree with the reference's serial
+ * sums to rounding, not bit for bit.  softmax and normalize may run in place. */
+int eshkol_b200_reduce_f64_device(const double* in, double* out, uint64_t n, int op);
+int eshkol_b200_reduce_axis_f64_device(const double* in, double* out, uint64_t outer, uint64_t axis_len,
+                                       uint64_t inner, int op);
+int eshkol_b200_transpose_f64_device(const double* in, double* out, uint64_t rows, uint64_t cols);
+int eshkol_b200_softmax_f64_device(const double* in, double* out, uint64_t num_slices, uint64_t slice_len);
+int eshkol_b200_normalize_f64_device(const double* in, double* out, uint64_t num_slices, uint64_t slice_len,
+                                     double gamma, double beta, double epsilon);
+int eshkol_b200_batchnorm_backward_f64_device(const double* grad_out, const double* saved_input,
+                                              const double* saved_mean, const double* saved_inv_std,
+                                              const double* saved_gamma, double* grad_input, double* grad_gamma,
+                                              double* grad_beta, uint64_t batch, uint64_t features);
+int eshkol_b200_layernorm_backward_f64_device(const double* grad_out, const double* saved_input,
+                                              const double* saved_mean, const double* saved_inv_std,
+                                              const double* saved_gamma, double* grad_input, uint64_t samples,
+                                              uint64_t features);
+
 /* Waits for the stream, then returns 0 if every kernel since the previous call
  * completed normally, a positive kernel status code if a bounded wait inside a
  * kernel ran out, or -1 on a CUDA error. */

@@ -113,11 +113,11 @@ typedef enum {
 int eshkol_gpu_elementwise_f64(EshkolGPUBuffer* a, EshkolGPUBuffer* b, EshkolGPUBuffer* out,
                                uint64_t n, EshkolElementwiseOp op);          /* gpu_memory.h:322 */
 
-/* The operators below are not on the matmul / conv2d path.  They are exported so
- * the library links wherever the reference's backend object did, and they return
- * -1, which every caller in the reference already treats as "run the CPU version"
- * (the same answer its no-GPU build gives for the backward operators,
- * lib/backend/gpu/gpu_memory_stub.cpp:399-449). */
+/* The backend's other tensor operators.  They run on device buffers (every buffer needs a
+ * device_ptr and room for its tensor) as the CUDA branch of the reference does
+ * (lib/backend/gpu/gpu_memory_cuda.cpp:1229-1560); anything else returns -1, which every
+ * caller in the reference treats as "run the CPU version".  Sums are shared by the threads of
+ * a warp or block, so results agree with the reference's serial kernels to rounding. */
 int eshkol_gpu_reduce_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t n,
                           EshkolReduceOp op);                                /* gpu_memory.h:335 */
 int eshkol_gpu_reduce_axis_f64(EshkolGPUBuffer* in, EshkolGPUBuffer* out, uint64_t rank,
