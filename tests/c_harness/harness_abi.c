@@ -7,7 +7,9 @@
  *   c_harness link                     take the address of every function of the header
  *   c_harness run M K N out_dir        eshkol_matmul_dispatch and the VM's vm_gpu_try_matmul on
  *                                      arena-like operands that are 8- but not 16-byte aligned;
- *                                      results go to out_dir/dispatch.bin and out_dir/vm.bin
+ *                                      results go to out_dir/dispatch.bin and out_dir/vm.bin;
+ *                                      the VM's softmax, transpose, add and reductions of A go to
+ *                                      out_dir/vm_softmax.bin, vm_transpose.bin, vm_add.bin, vm_reduce.bin
  */
 #include <eshkol/backend/gpu/gpu_memory.h>
 
@@ -17,6 +19,8 @@
 
 /* harness_vm.c: lib/backend/vm_gpu_dispatch.h compiled as the VM compiles it */
 int harness_vm_matmul(const double* a, const double* b, double* c, long M, long K, long N);
+int harness_vm_operators(const double* a, long rows, long cols, double* softmax_out, double* transpose_out,
+                         double* sum_out, double reduced[4]);
 
 /* the runtime's 48-bit generator (lib/core/prng.cpp:45-58, 76-80), entries 2u - 1 */
 static void fill_uniform(double* dst, size_t n, unsigned long long seed) {
@@ -96,6 +100,22 @@ int main(int argc, char** argv) {
     return 6;
   }
   if (write_file(dir, "vm.bin", C, (size_t)M * N)) return 7;
+  {
+    /* the VM's softmax / transpose / add / reduce try-functions on A */
+    const size_t n = (size_t)M * K;
+    double* out = (double*)malloc(3 * n * sizeof(double));
+    double reduced[4];
+    if (!out) return 4;
+    const int rc = harness_vm_operators(A, M, K, out, out + n, out + 2 * n, reduced);
+    if (rc != 0) {
+      fprintf(stderr, "a vm_gpu_try_* operator declined or failed (%d)\n", rc);
+      return 8;
+    }
+    if (write_file(dir, "vm_softmax.bin", out, n) || write_file(dir, "vm_transpose.bin", out + n, n) ||
+        write_file(dir, "vm_add.bin", out + 2 * n, n) || write_file(dir, "vm_reduce.bin", reduced, 4))
+      return 9;
+    free(out);
+  }
   eshkol_gpu_shutdown();
   free(ba); free(bb); free(bc);
   printf("ok\n");

@@ -59,3 +59,35 @@ int harness_vm_matmul(const double* a, const double* b, double* c, long M, long 
   memcpy(c, out->data, (size_t)M * N * sizeof(double));
   return 0;
 }
+
+static void as_matrix(VmTensor* t, const double* data, long rows, long cols) {
+  memset(t, 0, sizeof(*t));
+  t->n_dims = 2;
+  t->shape = t->inline_shape;
+  t->shape[0] = rows; t->shape[1] = cols;
+  t->total = (int64_t)rows * cols;
+  t->data = (double*)data;
+}
+
+/* the VM's other try-functions on one rows x cols matrix: softmax over the last axis, transpose,
+ * a + a, and the four reductions the VM asks for (sum 0, min 2, max 3, mean 4) */
+int harness_vm_operators(const double* a, long rows, long cols, double* softmax_out, double* transpose_out,
+                         double* sum_out, double reduced[4]) {
+  VmTensor t;
+  as_matrix(&t, a, rows, cols);
+  g_vm_gpu.threshold = 1;
+  VmTensor* s = vm_gpu_try_softmax(NULL, &t);
+  VmTensor* tr = vm_gpu_try_transpose(NULL, &t);
+  VmTensor* add = vm_gpu_try_binary(NULL, &t, &t, 0);
+  if (!s || !tr || !add) return -1;
+  if (tr->shape[0] != cols || tr->shape[1] != rows) return -2;
+  memcpy(softmax_out, s->data, (size_t)t.total * sizeof(double));
+  memcpy(transpose_out, tr->data, (size_t)t.total * sizeof(double));
+  memcpy(sum_out, add->data, (size_t)t.total * sizeof(double));
+  static const int ops[4] = {0, 2, 3, 4};
+  for (int i = 0; i < 4; ++i) {
+    reduced[i] = vm_gpu_try_reduce(&t, ops[i]);
+    if (isnan(reduced[i])) return -3;
+  }
+  return 0;
+}

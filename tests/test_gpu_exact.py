@@ -467,6 +467,15 @@ def test_c_host_built_against_the_reference_headers(gpu_lib, tmp_path):
     for name in ("dispatch.bin", "vm.bin"):
         got = np.fromfile(str(tmp_path / name), dtype=np.float64).reshape(M, N)
         assert gu.same_bits(got, want), name
+    # the VM's other try-functions (softmax, transpose, add, reduce) on A through the same library
+    from oracle import operators_ref as ops
+    load = lambda name, shape: np.fromfile(str(tmp_path / name), dtype=np.float64).reshape(shape)
+    assert np.array_equal(load("vm_transpose.bin", (K, M)), A.T)
+    assert np.array_equal(load("vm_add.bin", (M, K)), A + A)
+    assert np.allclose(load("vm_softmax.bin", (M, K)), ops.softmax(A), rtol=1e-13, atol=0)
+    red = load("vm_reduce.bin", (4,))
+    assert abs(red[0] - A.sum()) < 1e-9 and red[1] == A.min() and red[2] == A.max()
+    assert abs(red[3] - A.mean()) < 1e-14
 
 
 @pytest.mark.parametrize("shape", [(130, 300, 70), (257, 1100, 129), (64, 64, 64)])
