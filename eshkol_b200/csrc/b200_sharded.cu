@@ -72,8 +72,9 @@ struct EshkolB200Sharded {
   double* bcol[kSlots];
   cudaEvent_t bcol_free[kSlots];
   bool bcol_used[kSlots];
-  cudaStream_t x1, x2, pool[kPool];
+  cudaStream_t x1, x2, pool[kPool], gpool[kPool];
   int npool;
+  int ahead;  // panels of B whose planes are on their way while one is multiplied
   cudaEvent_t ev_got[kMaxPanels], ev_arrived[kMaxPanels], ev_tmp[kPool];
 };
 
@@ -175,6 +176,24 @@ void partition(long long n, int world, int r, long long* first, long long* count
   *count = base + (r < extra ? 1 : 0);
 }
 
+// A panel's columns cut into one contiguous share per rank, in rank order.  The source rank
+// also sends every other rank its f64 columns, so its link carries more than the others';
+// its share (and with it the planes it serves to every peer) is src_weight of theirs.
+void column_shares(long long wd, int world, int src, double src_weight, long long* first, long long* count) {
+  if (world == 1) { first[0] = 0; count[0] = wd; return; }
+  long long n0 = static_cast<long long>(static_cast<double>(wd) * src_weight / (world - 1 + src_weight));
+  if (n0 < 0) n0 = 0;
+  if (n0 > wd) n0 = wd;
+  const long long rest = wd - n0, base = rest / (world - 1), extra = rest % (world - 1);
+  long long c = 0;
+  int k = 0;
+  for (int r = 0; r < world; ++r) {
+    count[r] = (r == src) ? n0 : base + (k++ < extra ? 1 : 0);
+    first[r] = c;
+    c += count[r];
+  }
+}
+
 // Column panels: widths grow by half from w/8 (w = N/4), stay near w, halve down to w/8.  A
 // panel of residue planes is twice the bytes of its f64 columns, so its exchange hides behind
 // the products of the panel before it only up to a ratio of about 1.5.
@@ -248,13 +267,35 @@ int stage_prep(EshkolB200Sharded* s, int p) {
   return 0;
 }
 
+// pull the other ranks' shares of panel p's planes into their places; ev_arrived[p] follows them
+int pull_planes(EshkolB200Sharded* s, int p) {
+  const int R = s->rank, W = s->world;
+  for (int i = 1; i < W; ++i) {
+    const int q = (R + i) % W;
+    if (s->partn[p][q] == 0) continue;
+    cudaStream_t st = s->pool[i % s->npool];
+    SH_CHECK(cudaStreamWaitEvent(st, s->ev_planes[q][p], 0));
+    for (int g = 0; g < 7; ++g) {
+      const uint64_t* rg = s->regions[p][q][g];
+      if (copy2d(s, static_cast<char*>(s->blk_p[p]) + rg[0], rg[3], s->addr_p[q][p] + rg[0], rg[3], rg[1], rg[2], st))
+        return -1;
+    }
+  }
+  for (int i = 0; i < s->npool; ++i) {
+    SH_CHECK(cudaEventRecord(s->ev_tmp[i], s->pool[i]));
+    SH_CHECK(cudaStreamWaitEvent(s->x2, s->ev_tmp[i], 0));
+  }
+  SH_CHECK(cudaEventRecord(s->ev_arrived[p], s->x2));
+  return 0;
+}
+
 // pull every other rank's block of panel p of C into its place, once it is computed
 int gather_panel(EshkolB200Sharded* s, int p) {
   const int R = s->rank, W = s->world;
   for (int i = 1; i < W; ++i) {
     const int q = (R + i) % W;
     if (s->rows[q] == 0) continue;
-    cudaStream_t st = s->pool[i % s->npool];
+    cudaStream_t st = s->gpool[i % s->npool];
     SH_CHECK(cudaStreamWaitEvent(st, s->ev_block[q][p], 0));
     const size_t off = static_cast<size_t>(s->row0[q] * s->N + s->col0[p]) * 8;
     if (copy2d(s, static_cast<char*>(s->blk_c) + off, static_cast<size_t>(s->N) * 8, s->addr_c[q] + off,
@@ -291,9 +332,16 @@ int eshkol_b200_sharded_open(const char* name, int rank, int world, uint64_t M_,
   // ---- geometry ----
   s->P = make_panels(s->N, s->col0, s->width);
   for (int r = 0; r < world; ++r) partition(s->M, world, r, &s->row0[r], &s->rows[r]);
+  double src_weight = 0.5;
+  if (const char* e = getenv("ESHKOL_B200_SRC_SHARE")) {
+    if (e[0]) src_weight = atof(e);
+    if (!(src_weight >= 0.0)) src_weight = 0.0;
+    if (src_weight > 1.0) src_weight = 1.0;
+  }
+  for (int p = 0; p < s->P; ++p)
+    column_shares(s->width[p], world, src_rank, src_weight, s->part0[p], s->partn[p]);
   for (int p = 0; p < s->P; ++p)
     for (int r = 0; r < world; ++r) {
-      partition(s->width[p], world, r, &s->part0[p][r], &s->partn[p][r]);
       if (s->partn[p][r] > 0 &&
           eshkol_b200_prepared_b_regions(K_, static_cast<uint64_t>(s->width[p]), static_cast<uint64_t>(s->part0[p][r]),
                                          static_cast<uint64_t>(s->partn[p][r]), s->regions[p][r]) != 7) {
@@ -335,7 +383,14 @@ int eshkol_b200_sharded_open(const char* name, int rank, int world, uint64_t M_,
   SH_CHECK(cudaStreamCreateWithFlags(&s->x2, cudaStreamNonBlocking));
   for (int i = 0; i < s->npool; ++i) {
     SH_CHECK(cudaStreamCreateWithFlags(&s->pool[i], cudaStreamNonBlocking));
+    SH_CHECK(cudaStreamCreateWithFlags(&s->gpool[i], cudaStreamNonBlocking));
     SH_CHECK(cudaEventCreateWithFlags(&s->ev_tmp[i], cudaEventDisableTiming));
+  }
+  {
+    const char* e = getenv("ESHKOL_B200_AHEAD");
+    s->ahead = (e && e[0]) ? atoi(e) : 4;
+    if (s->ahead < 2) s->ahead = 2;
+    if (s->ahead > kMaxPanels) s->ahead = kMaxPanels;
   }
 
   // ---- exchange: every rank has published its handles, then opens the peers' ----
@@ -409,18 +464,19 @@ double* eshkol_b200_sharded_c_buffer(EshkolB200Sharded* s) { return s ? static_c
 
 int eshkol_b200_sharded_step(EshkolB200Sharded* s, const double* dA_rows) {
   if (!s) return -1;
-  const int R = s->rank, W = s->world, P = s->P;
+  const int R = s->rank, P = s->P;
   const long long my_rows = s->rows[R];
   if (my_rows > 0 && !dA_rows) return fail(s, "no rows of A were passed");
   cudaStream_t lib = static_cast<cudaStream_t>(eshkol_b200_stream());
   for (int i = 0; i < kSlots; ++i) s->bcol_used[i] = false;
   // every rank is in the step: B on the source rank is complete, nobody reads last step's buffers
   if (barrier(s) != 0) return -1;
-  const int ahead = 2;
-  // the first panels' shares are split before this rank's rows of A are: their exchange then
-  // runs beside the preparation of A instead of behind it
-  for (int p = 0; p < ahead && p < P; ++p)
-    if (stage_prep(s, p)) return -1;
+  const int ahead = s->ahead;
+  // the first two panels' shares are split before this rank's rows of A are: their exchange
+  // then runs beside the preparation of A instead of behind it
+  int prepared = 0, pulled = 0;
+  while (prepared < 2 && prepared < P)
+    if (stage_prep(s, prepared++)) return -1;
   long long wmax = 0;
   for (int p = 0; p < P; ++p) if (s->width[p] > wmax) wmax = s->width[p];
   if (my_rows > 0 &&
@@ -428,26 +484,15 @@ int eshkol_b200_sharded_step(EshkolB200Sharded* s, const double* dA_rows) {
                                        static_cast<uint64_t>(wmax)) != 0)
     return fail(s, "prepare_a failed");
   for (int p = 0; p < P; ++p) {
-    // an imported event's wait sees the most recent record the owner has CALLED: the barrier
-    // puts every rank's record of panel p's planes (and of the block of panel p-1) before the
-    // waits enqueued below
+    // An imported event's wait sees the most recent record the owner has CALLED, so this
+    // barrier stands between every rank's calls of the records so far (the planes of the
+    // panels staged up to here, the block of panel p - 1) and the peers' calls of their waits.
     if (barrier(s) != 0) return -1;
-    for (int i = 1; i < W; ++i) {
-      const int q = (R + i) % W;
-      if (s->partn[p][q] == 0) continue;
-      cudaStream_t st = s->pool[i % s->npool];
-      SH_CHECK(cudaStreamWaitEvent(st, s->ev_planes[q][p], 0));
-      for (int g = 0; g < 7; ++g) {
-        const uint64_t* rg = s->regions[p][q][g];
-        if (copy2d(s, static_cast<char*>(s->blk_p[p]) + rg[0], rg[3], s->addr_p[q][p] + rg[0], rg[3], rg[1], rg[2], st))
-          return -1;
-      }
-    }
-    for (int i = 0; i < s->npool; ++i) {
-      SH_CHECK(cudaEventRecord(s->ev_tmp[i], s->pool[i]));
-      SH_CHECK(cudaStreamWaitEvent(s->x2, s->ev_tmp[i], 0));
-    }
-    SH_CHECK(cudaEventRecord(s->ev_arrived[p], s->x2));
+    // Planes of up to `ahead` panels are on their way while a panel is multiplied: beside the
+    // products a link moves about 60 % of what it moves alone, and with one panel in flight
+    // the products waited for the planes.
+    while (pulled < prepared)
+      if (pull_planes(s, pulled++)) return -1;
     if (my_rows > 0) {
       SH_CHECK(cudaStreamWaitEvent(lib, s->ev_arrived[p], 0));
       if (eshkol_b200_adopt_prepared_b(s->blk_p[p], static_cast<uint64_t>(s->K), static_cast<uint64_t>(s->width[p])) != 0)
@@ -459,15 +504,18 @@ int eshkol_b200_sharded_step(EshkolB200Sharded* s, const double* dA_rows) {
       if (eshkol_b200_multiply_prepared_f64_device(c, &o) != 0) return fail(s, "multiply failed");
     }
     SH_CHECK(cudaEventRecord(s->ev_block[R][p], lib));
-    if (p + ahead < P && stage_prep(s, p + ahead)) return -1;
-    // the blocks of the panel before this one share the streams of the plane pulls, behind the
-    // planes just enqueued: on streams of their own the strided block copies take the copy
-    // engines from the planes the products are about to need
+    // behind the products of panel p: the shares of the panels up to p + ahead
+    while (prepared < P && prepared <= p + ahead)
+      if (stage_prep(s, prepared++)) return -1;
+    // the blocks of the panel before this one, on streams of their own
     if (p >= 1 && gather_panel(s, p - 1)) return -1;
   }
   if (barrier(s) != 0) return -1;
   if (gather_panel(s, P - 1)) return -1;
-  for (int i = 0; i < s->npool; ++i) SH_CHECK(cudaStreamSynchronize(s->pool[i]));
+  for (int i = 0; i < s->npool; ++i) {
+    SH_CHECK(cudaStreamSynchronize(s->pool[i]));
+    SH_CHECK(cudaStreamSynchronize(s->gpool[i]));
+  }
   SH_CHECK(cudaStreamSynchronize(s->x1));
   SH_CHECK(cudaStreamSynchronize(s->x2));
   if (eshkol_b200_sync_status() != 0) return fail(s, "a kernel of the step reported a failure");
@@ -507,6 +555,7 @@ int eshkol_b200_sharded_close(EshkolB200Sharded* s) {
   if (s->x2) cudaStreamDestroy(s->x2);
   for (int i = 0; i < s->npool; ++i) {
     if (s->pool[i]) cudaStreamDestroy(s->pool[i]);
+    if (s->gpool[i]) cudaStreamDestroy(s->gpool[i]);
     if (s->ev_tmp[i]) cudaEventDestroy(s->ev_tmp[i]);
   }
   if (s->rank == 0) shm_unlink(s->name);

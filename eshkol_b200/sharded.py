@@ -11,6 +11,7 @@ has no multi-device code; this is the sharding the 32768^3 row-sharded configura
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Callable, Optional
 
 import torch
@@ -78,6 +79,26 @@ def row_partition(M: int, world: int) -> list[tuple[int, int]]:
         rows = base + (1 if r < extra else 0)
         out.append((start, rows))
         start += rows
+    return out
+
+
+def column_shares(width: int, world: int, src: int, src_weight: float) -> list[tuple[int, int]]:
+    """(first column, column count) per rank of one panel, contiguous, in rank order.  The source
+    rank also sends every other rank its f64 columns, so its link carries more than the others';
+    its share (and with it the planes it serves to every peer) is src_weight of theirs."""
+    if world == 1:
+        return [(0, width)]
+    n0 = min(width, max(0, int(width * src_weight / (world - 1 + src_weight))))
+    base, extra = divmod(width - n0, world - 1)
+    out, start, k = [], 0, 0
+    for r in range(world):
+        if r == src:
+            n = n0
+        else:
+            n = base + (1 if k < extra else 0)
+            k += 1
+        out.append((start, n))
+        start += n
     return out
 
 
@@ -277,6 +298,9 @@ class ShardedGemm:
         self._share_wanted = bool(share_split)
         # b_in_place (with share_split): the source keeps B in source_buffer() and nothing is packed
         self.b_in_place = bool(b_in_place) and bool(share_split)
+        # share_split: how many panels beyond the one being multiplied have their shares split
+        # (and, a host barrier later, their planes on the way)
+        self.ahead = max(2, int(os.environ.get("ESHKOL_B200_AHEAD", "4") or 4))
         if transport == "copy_engine" and self.world > 1 and self.backend.on_device:
             # the panel buffer of B and C itself are library allocations the peers open; products
             # write their block of C in place and the peers pull it from there
@@ -445,7 +469,8 @@ class ShardedGemm:
                 else:
                     self._addr_P[q] = [attempt(import_mem, h) for h in hp[q]]
             self._ev_planes = make_events(P)   # this rank's columns of panel p are split
-            self._cparts = [row_partition(wd, W) for _, wd in self.cols]
+            w_src = min(1.0, max(0.0, float(os.environ.get("ESHKOL_B200_SRC_SHARE", "0.5") or 0.5)))
+            self._cparts = [column_shares(wd, W, self.src, w_src) for _, wd in self.cols]
             self._regions = []
             for p, (_, wd) in enumerate(self.cols):
                 per_rank = []
@@ -470,12 +495,10 @@ class ShardedGemm:
         self._x1 = torch.cuda.Stream(self.device)
         self._x2 = torch.cuda.Stream(self.device)
         self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(min(4, max(1, W - 1)))]
-        # The blocks of C share the streams of the plane pulls, each panel's blocks enqueued behind
-        # the planes of the panel after it: on streams of their own the strided block copies take
-        # the copy engines from the planes the products are about to need (measured on 4 GPUs:
-        # planes then move at 180 GB/s instead of 500 and every panel's products wait for them);
-        # enqueued only after the last panel they would not start before the products are over.
-        self._gather_streams = self._pull_streams
+        # The blocks of C move on streams of their own.  With the planes of several panels on
+        # their way ahead of the products (self.ahead) the block copies no longer take the copy
+        # engines from planes the products are about to need.
+        self._gather_streams = [torch.cuda.Stream(self.device) for _ in self._pull_streams]
         self._k_parts = row_partition(self.K, W)
         torch.cuda.synchronize(self.device)
 
@@ -718,32 +741,48 @@ class ShardedGemm:
             self._mark(f"own columns {p} split", lib)
             self._record(self._ev_planes[R][p], lib)
 
-        ahead = 2
-        # the first panels' shares are split before this rank's rows of A are: their exchange
+        ahead = self.ahead
+        # the first two panels' shares are split before this rank's rows of A are: their exchange
         # then runs beside the preparation of A instead of behind it
-        for p in range(min(ahead, P)):
-            stage_prep(p)
+        prepared = pulled = 0
+        while prepared < min(2, P):
+            stage_prep(prepared)
+            prepared += 1
         if self.rows:
             self.backend.begin(A_rows, max(wd for _, wd in self.cols))
             self._mark("A prepared", lib)
-        for p in range(P):
-            dist.barrier(group=self.ctl)
-            c0p, wd = self.cols[p]
+        arrived = [None] * P
+
+        def pull_planes(p: int) -> None:
             for i in range(1, W):
                 q = (R + i) % W
                 if not self._regions[p][q]:
                     continue
                 st = pool[i % len(pool)]
                 self._wait(self._ev_planes[q][p], st)
+                self._mark(f"planes {p} of rank {q} ready", st)
                 for off, width, rows, pitch in self._regions[p][q]:
                     self._copy2d(self._blk_P[p].ptr + off, pitch, self._addr_P[q][p] + off, pitch, width, rows, st)
+                self._mark(f"planes {p} of rank {q} here", st)
             for st in pool:
                 x2.wait_stream(st)
-            arrived = torch.cuda.Event()
-            arrived.record(x2)
+            arrived[p] = torch.cuda.Event()
+            arrived[p].record(x2)
             self._mark(f"planes {p} arrived", x2)
+
+        for p in range(P):
+            # every rank has called the records so far (the planes of the panels staged up to
+            # here, the block of panel p - 1) before any peer calls their waits
+            dist.barrier(group=self.ctl)
+            c0p, wd = self.cols[p]
+            # planes of up to `ahead` panels are on their way while a panel is multiplied: beside
+            # the products a link moves about 60 % of what it moves alone, and with one panel in
+            # flight the products waited for the planes
+            while pulled < prepared:
+                pull_planes(pulled)
+                pulled += 1
             if self.rows:
-                lib.wait_event(arrived)
+                lib.wait_event(arrived[p])
                 self._mark(f"panel {p} products start", lib)
                 if lib_h.eshkol_b200_adopt_prepared_b(self._blk_P[p].ptr, self.K, wd) != 0:
                     raise RuntimeError("adopt_prepared_b failed")
@@ -753,10 +792,12 @@ class ShardedGemm:
                     raise RuntimeError("multiply failed")
                 self._mark(f"panel {p} products done", lib)
             self._record(self._ev_block[R][p], lib)
-            if p + ahead < P:
-                stage_prep(p + ahead)
-            # the blocks of C of the panel before this one: every rank has called their records
-            # (they precede this iteration's barrier), so they can be pulled while later panels run
+            # behind the products of panel p: the shares of the panels up to p + ahead
+            while prepared < P and prepared <= p + ahead:
+                stage_prep(prepared)
+                prepared += 1
+            # the blocks of C of the panel before this one, on streams of their own: every rank
+            # has called their records (they precede this iteration's barrier)
             if p >= 1:
                 self._gather_panel(p - 1, gpool, xo)
         dist.barrier(group=self.ctl)
@@ -779,7 +820,9 @@ class ShardedGemm:
                 continue
             st = pool[i % len(pool)]
             self._wait(self._ev_block[q][p], st)
+            self._mark(f"block {p} of rank {q} ready", st)
             self._pull_c_block(q, p, st)
+            self._mark(f"block {p} of rank {q} here", st)
         for st in pool:
             xo.wait_stream(st)
         self._mark(f"panel {p} gathered", xo)

@@ -140,3 +140,25 @@ def test_c_session_a_rank_that_leaves_is_noticed_by_timeout():
     assert out[2][0] == 0
     assert out[0][0] == -1 and out[1][0] == -1
     assert all(1.0 < out[r][1] < 20.0 for r in (0, 1)), out
+
+
+def test_column_shares_cover_the_panel_and_lighten_the_source():
+    """The shares of a panel's columns are contiguous, in rank order and complete; the source
+    rank's share is the stated fraction of the others' (none at weight 0, equal at weight 1)."""
+    from eshkol_b200.sharded import column_shares
+    for width, world, src, w in [(5120, 8, 0, 0.5), (1024, 8, 3, 0.5), (4096, 4, 0, 0.0), (4096, 4, 1, 1.0),
+                                 (1000, 3, 2, 0.25), (7, 8, 0, 0.5), (256, 1, 0, 0.5)]:
+        parts = column_shares(width, world, src, w)
+        assert len(parts) == world
+        assert parts[0][0] == 0 and sum(n for _, n in parts) == width
+        for (a, n), (b, _) in zip(parts, parts[1:]):
+            assert a + n == b
+        if world > 1:
+            others = [n for r, (_, n) in enumerate(parts) if r != src]
+            assert max(others) - min(others) <= 1
+            if w == 0.0:
+                assert parts[src][1] == 0
+            if w == 1.0:
+                assert abs(parts[src][1] - others[0]) <= 1
+            if 0.0 < w < 1.0 and width >= 64 * world:
+                assert abs(parts[src][1] - w * others[0]) <= 1 + w
