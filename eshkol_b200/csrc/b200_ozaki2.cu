@@ -14,6 +14,7 @@
 #include "b200_common.cuh"
 #include "b200_internal.h"
 #include "b200_ozaki2.h"
+#include <stdlib.h>
 #include "b200_residue.cuh"
 
 #include <math.h>
@@ -421,12 +422,20 @@ __global__ void __launch_bounds__(256) split_b_kernel(const double* __restrict__
 // columns per thread halve the loads and the address arithmetic per element, and the 16
 // independent accumulation chains of a thread keep the FP64 pipe fed.
 constexpr int kCrtW = 8;
+// kMode 0: 16 moduli, no bias, no activation, row-major C (decided at launch); 1: the general
+// form without GELU; 2: with it.  The general form carries the run-time switches of the epilogue
+// (and, for GELU, eight inlined exponentials and divisions) through the whole kernel -- 0.78
+// against 0.41 ms at 8192^2 -- so the plain product, which is what a GEMM call is, has its own
+// instance.
+template <int kMode>
 __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
                                                   const __grid_constant__ Oz2DeviceConsts c) {
+  constexpr bool kPlain = kMode == 0;
   const long long i = blockIdx.x;
   const long long j0 = (static_cast<long long>(blockIdx.y) * 256 + threadIdx.x) * kCrtW;
   if (j0 >= a.N) return;
   const long long wo = i * a.ldw + j0;
+  const int n_mod = kPlain ? 16 : a.n_mod;
   double S1[kCrtW], S2[kCrtW];
   {
     // modulus 256: finish the reduction the products kernel left open -- apply the tie
@@ -452,18 +461,18 @@ __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
 #pragma unroll
     for (int t = 0; t < 8; ++t) {
       const int l = l0 + t;
-      wv[t] = (l < 16 && l < a.n_mod)
+      wv[t] = (l < 16 && l < n_mod)
                   ? __ldg(reinterpret_cast<const uint2*>(a.w_odd + (l - 1) * a.w_odd_stride + wo))
                   : make_uint2(0u, 0u);
     }
 #pragma unroll
     for (int t = 0; t < 8; ++t) {
       const int l = l0 + t;
-      if (l < 16 && l < a.n_mod) {
+      if (l < 16 && l < n_mod) {
+        const double s1 = c.sl1[l], s2 = c.sl2[l];
         // signed byte -> double through the mantissa: (2^52 + (b + 128)) - (2^52 + 128), exact,
         // on the FP64 add pipe instead of the slower integer-to-double conversion unit
         const uint32_t lo = wv[t].x ^ 0x80808080u, hi = wv[t].y ^ 0x80808080u;
-        const double s1 = c.sl1[l], s2 = c.sl2[l];
 #pragma unroll
         for (int e = 0; e < kCrtW; ++e) {
           const uint32_t byte = __byte_perm(e < 4 ? lo : hi, 0u, 0x4440 + (e & 3));
@@ -476,21 +485,37 @@ __global__ void __launch_bounds__(256) crt_kernel(const CrtArgs a,
   }
   const double mu_inv = a.inv_scale_a[i];
   const double P1 = c.P1, P2 = c.P2, Pinv = c.Pinv;
+  double sb[kCrtW];
+  if (j0 + kCrtW - 1 < a.N && (reinterpret_cast<uintptr_t>(a.inv_scale_b + j0) & 15) == 0) {
+#pragma unroll
+    for (int h = 0; h < kCrtW / 2; ++h) {
+      const double2 t = __ldg(reinterpret_cast<const double2*>(a.inv_scale_b + j0) + h);
+      sb[2 * h] = t.x;
+      sb[2 * h + 1] = t.y;
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < kCrtW; ++e) sb[e] = a.inv_scale_b[(j0 + e < a.N) ? j0 + e : a.N - 1];
+  }
   double out[kCrtW];
 #pragma unroll
   for (int e = 0; e < kCrtW; ++e) {
-    const long long j = (j0 + e < a.N) ? j0 + e : a.N - 1;
     const double s = __dadd_rn(S1[e], S2[e]);
-    const double Q = round(__dmul_rn(s, Pinv));  // half away from zero, as round()
+    const double q = __dmul_rn(s, Pinv);
+    const double Q = round(q);  // half away from zero
     const double c1 = fma(-P1, Q, S1[e]);
     const double c2 = fma(-P2, Q, S2[e]);
-    double v = __dmul_rn(__dmul_rn(__dadd_rn(c1, c2), mu_inv), a.inv_scale_b[j]);
-    if (a.bias_mode == 1) v = __dadd_rn(v, a.bias[i]);
-    else if (a.bias_mode == 2) v = __dadd_rn(v, a.bias[j]);
-    v = apply_activation(v, a.activation);
+    double v = __dmul_rn(__dmul_rn(__dadd_rn(c1, c2), mu_inv), sb[e]);
+    if (!kPlain) {
+      const long long j = (j0 + e < a.N) ? j0 + e : a.N - 1;
+      if (a.bias_mode == 1) v = __dadd_rn(v, a.bias[i]);
+      else if (a.bias_mode == 2) v = __dadd_rn(v, a.bias[j]);
+      if (kMode == 2) v = apply_activation(v, a.activation);
+      else if (a.activation == 1) v = (v > 0.0) ? v : 0.0;  // apply_activation's ReLU
+    }
     out[e] = v;
   }
-  if (a.pixels_per_image > 0) {
+  if (!kPlain && a.pixels_per_image > 0) {
 #pragma unroll
     for (int e = 0; e < kCrtW; ++e) {
       const long long j = j0 + e;
@@ -624,7 +649,12 @@ cudaError_t launch_crt(const CrtArgs& a, const Oz2DeviceConsts& c, cudaStream_t 
   if (a.M <= 0 || a.N <= 0) return cudaSuccess;
   const dim3 grid(static_cast<unsigned>(a.M), static_cast<unsigned>((a.N + 256 * kCrtW - 1) / (256 * kCrtW)));
   if (grid.y > 65535u) return cudaErrorInvalidValue;
-  crt_kernel<<<grid, 256, 0, st>>>(a, c);
+  if (a.n_mod == 16 && a.bias_mode == 0 && a.activation == 0 && a.pixels_per_image == 0)
+    crt_kernel<0><<<grid, 256, 0, st>>>(a, c);
+  else if (a.activation == 0 || a.activation == 1)
+    crt_kernel<1><<<grid, 256, 0, st>>>(a, c);
+  else
+    crt_kernel<2><<<grid, 256, 0, st>>>(a, c);
   return cudaGetLastError();
 }
 

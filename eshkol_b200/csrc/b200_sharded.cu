@@ -36,7 +36,7 @@
 
 namespace {
 
-constexpr int kMaxRanks = 16, kMaxPanels = 24, kSlots = 3, kPool = 4;
+constexpr int kMaxRanks = 16, kMaxPanels = 24, kSlots = 3, kPool = 8;
 constexpr uint32_t kMagic = 0xE5B20001u;
 
 struct Ctl {  // the shared-memory segment
@@ -378,7 +378,14 @@ int eshkol_b200_sharded_open(const char* name, int rank, int world, uint64_t M_,
       s->bcol[i] = static_cast<double*>(d);
       SH_CHECK(cudaEventCreateWithFlags(&s->bcol_free[i], cudaEventDisableTiming));
     }
-  s->npool = world - 1 < kPool ? (world - 1 > 0 ? world - 1 : 1) : kPool;
+  {
+    // streams the pulls of one panel are spread over (each peer's copies stay on one stream)
+    const char* e = getenv("ESHKOL_B200_POOL");
+    int want = (e && e[0]) ? atoi(e) : 4;
+    if (want < 1) want = 1;
+    if (want > kPool) want = kPool;
+    s->npool = world - 1 < want ? (world - 1 > 0 ? world - 1 : 1) : want;
+  }
   SH_CHECK(cudaStreamCreateWithFlags(&s->x1, cudaStreamNonBlocking));
   SH_CHECK(cudaStreamCreateWithFlags(&s->x2, cudaStreamNonBlocking));
   for (int i = 0; i < s->npool; ++i) {
@@ -388,7 +395,7 @@ int eshkol_b200_sharded_open(const char* name, int rank, int world, uint64_t M_,
   }
   {
     const char* e = getenv("ESHKOL_B200_AHEAD");
-    s->ahead = (e && e[0]) ? atoi(e) : 4;
+    s->ahead = (e && e[0]) ? atoi(e) : 2;
     if (s->ahead < 2) s->ahead = 2;
     if (s->ahead > kMaxPanels) s->ahead = kMaxPanels;
   }
@@ -488,9 +495,9 @@ int eshkol_b200_sharded_step(EshkolB200Sharded* s, const double* dA_rows) {
     // barrier stands between every rank's calls of the records so far (the planes of the
     // panels staged up to here, the block of panel p - 1) and the peers' calls of their waits.
     if (barrier(s) != 0) return -1;
-    // Planes of up to `ahead` panels are on their way while a panel is multiplied: beside the
-    // products a link moves about 60 % of what it moves alone, and with one panel in flight
-    // the products waited for the planes.
+    // The planes of every panel staged so far are on their way: `ahead` panels beyond the one
+    // being multiplied.  Two is the measured optimum on 8 GPUs; with more in flight the host
+    // calls of one iteration (some 50 pitched copies per panel) fall behind the device.
     while (pulled < prepared)
       if (pull_planes(s, pulled++)) return -1;
     if (my_rows > 0) {

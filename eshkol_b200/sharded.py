@@ -300,7 +300,7 @@ class ShardedGemm:
         self.b_in_place = bool(b_in_place) and bool(share_split)
         # share_split: how many panels beyond the one being multiplied have their shares split
         # (and, a host barrier later, their planes on the way)
-        self.ahead = max(2, int(os.environ.get("ESHKOL_B200_AHEAD", "4") or 4))
+        self.ahead = max(2, int(os.environ.get("ESHKOL_B200_AHEAD", "2") or 2))
         if transport == "copy_engine" and self.world > 1 and self.backend.on_device:
             # the panel buffer of B and C itself are library allocations the peers open; products
             # write their block of C in place and the peers pull it from there
@@ -494,7 +494,8 @@ class ShardedGemm:
         self.C = self._blk_C.tensor
         self._x1 = torch.cuda.Stream(self.device)
         self._x2 = torch.cuda.Stream(self.device)
-        self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(min(4, max(1, W - 1)))]
+        n_pool = min(8, max(1, int(os.environ.get("ESHKOL_B200_POOL", "4") or 4)))
+        self._pull_streams = [torch.cuda.Stream(self.device) for _ in range(min(n_pool, max(1, W - 1)))]
         # The blocks of C move on streams of their own.  With the planes of several panels on
         # their way ahead of the products (self.ahead) the block copies no longer take the copy
         # engines from planes the products are about to need.
@@ -775,9 +776,9 @@ class ShardedGemm:
             # here, the block of panel p - 1) before any peer calls their waits
             dist.barrier(group=self.ctl)
             c0p, wd = self.cols[p]
-            # planes of up to `ahead` panels are on their way while a panel is multiplied: beside
-            # the products a link moves about 60 % of what it moves alone, and with one panel in
-            # flight the products waited for the planes
+            # the planes of every panel staged so far are on their way: `ahead` panels beyond the
+            # one being multiplied (two is the measured optimum on 8 GPUs; with more in flight the
+            # host calls of one iteration fall behind the device)
             while pulled < prepared:
                 pull_planes(pulled)
                 pulled += 1
