@@ -22,6 +22,12 @@ import sys
 import threading
 import time
 
+# More hardware work queues than CUDA's default of 8: the sharded step keeps a dozen streams busy,
+# and streams that share a queue wait for each other's event waits (a false dependency: a
+# product then starts only when another panel's transfer has arrived).  Read when the CUDA
+# context is created, so it has to be in the environment before torch initialises CUDA.
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 

@@ -282,6 +282,7 @@ class ShardedGemm:
         self.backend = _CallableBackend(gemm) if gemm is not None else _DeviceBackend(tier, param, self.device, comm_sms if self.world > 1 else 0)
         self._side = None
         self.trace = None  # set to [] to collect (label, CUDA event) marks of the next step
+        self.host_trace = []  # (label, host seconds) of the traced step
         self.panels = panels if (panels > 0 and N % panels == 0) else 1
         self.width = N // self.panels
         # column range of every panel: equal widths, or (copy-engine transport only) narrower
@@ -633,6 +634,7 @@ class ShardedGemm:
             arrived.append(ev)
             self._mark(f"B panel {p} arrived", x2)
         for p in range(P):
+            self._host_mark(f"pulls of {p} called")
             if self.rows:
                 lib.wait_event(arrived[p])
                 self._mark(f"panel {p} products start", lib)
@@ -774,7 +776,9 @@ class ShardedGemm:
         for p in range(P):
             # every rank has called the records so far (the planes of the panels staged up to
             # here, the block of panel p - 1) before any peer calls their waits
+            self._host_mark(f"iteration {p}")
             dist.barrier(group=self.ctl)
+            self._host_mark(f"barrier {p} passed")
             c0p, wd = self.cols[p]
             # the planes of every panel staged so far are on their way: `ahead` panels beyond the
             # one being multiplied (two is the measured optimum on 8 GPUs; with more in flight the
@@ -782,6 +786,7 @@ class ShardedGemm:
             while pulled < prepared:
                 pull_planes(pulled)
                 pulled += 1
+            self._host_mark(f"pulls of {p} called")
             if self.rows:
                 lib.wait_event(arrived[p])
                 self._mark(f"panel {p} products start", lib)
@@ -793,14 +798,17 @@ class ShardedGemm:
                     raise RuntimeError("multiply failed")
                 self._mark(f"panel {p} products done", lib)
             self._record(self._ev_block[R][p], lib)
+            self._host_mark(f"products {p} called")
             # behind the products of panel p: the shares of the panels up to p + ahead
             while prepared < P and prepared <= p + ahead:
                 stage_prep(prepared)
                 prepared += 1
             # the blocks of C of the panel before this one, on streams of their own: every rank
             # has called their records (they precede this iteration's barrier)
+            self._host_mark(f"stages after {p} called")
             if p >= 1:
                 self._gather_panel(p - 1, gpool, xo)
+        self._host_mark("loop done")
         dist.barrier(group=self.ctl)
         self._gather_panel(P - 1, gpool, xo)
         cur.wait_stream(lib)
@@ -837,6 +845,12 @@ class ShardedGemm:
         else:
             for r, (r0, rows) in enumerate(self.parts):
                 dst[r0:r0 + rows].copy_(self.Cp[p, r, :rows])
+
+    def _host_mark(self, label: str) -> None:
+        """host time of a point of the traced step (beside the device marks of _mark)"""
+        if self.trace is not None:
+            import time
+            self.host_trace.append((label, time.perf_counter()))
 
     def _mark(self, label: str, stream) -> None:
         if self.trace is not None and stream is not None:
