@@ -496,8 +496,8 @@ int eshkol_b200_sharded_step(EshkolB200Sharded* s, const double* dA_rows) {
     // panels staged up to here, the block of panel p - 1) and the peers' calls of their waits.
     if (barrier(s) != 0) return -1;
     // The planes of every panel staged so far are on their way: `ahead` panels beyond the one
-    // being multiplied.  Two is the measured optimum on 8 GPUs; with more in flight the host
-    // calls of one iteration (some 50 pitched copies per panel) fall behind the device.
+    // being multiplied.  Two is the measured optimum on 8 GPUs (with three or four in flight
+    // the step was slower there).
     while (pulled < prepared)
       if (pull_planes(s, pulled++)) return -1;
     if (my_rows > 0) {

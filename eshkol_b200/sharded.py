@@ -781,8 +781,8 @@ class ShardedGemm:
             self._host_mark(f"barrier {p} passed")
             c0p, wd = self.cols[p]
             # the planes of every panel staged so far are on their way: `ahead` panels beyond the
-            # one being multiplied (two is the measured optimum on 8 GPUs; with more in flight the
-            # host calls of one iteration fall behind the device)
+            # one being multiplied (two is the measured optimum on 8 GPUs: with three or four in
+            # flight the step was slower there)
             while pulled < prepared:
                 pull_planes(pulled)
                 pulled += 1
