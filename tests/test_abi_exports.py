@@ -192,3 +192,23 @@ def test_calls_fail_loudly_without_a_device():
     # the void dispatcher must not leave a plausible number behind
     c = eb.matmul_dispatch(a, a)
     assert np.isnan(c).all()
+    # the other operators: -1 from the buffer level and from the device level, nothing computed
+    out = np.full((4, 4), 7.0)
+    hb = eb.EshkolGPUBuffer()
+    hb.host_ptr = a.ctypes.data
+    hb.size_bytes = a.nbytes
+    ob = eb.EshkolGPUBuffer()
+    ob.host_ptr = out.ctypes.data
+    ob.size_bytes = out.nbytes
+    dims = (ctypes.c_uint64 * 2)(4, 4)
+    assert lib.eshkol_gpu_reduce_f64(ctypes.byref(hb), ctypes.byref(ob), 16, 0) == -1
+    assert lib.eshkol_gpu_reduce_axis_f64(ctypes.byref(hb), ctypes.byref(ob), 2, dims, 0, 0) == -1
+    assert lib.eshkol_gpu_transpose_f64(ctypes.byref(hb), ctypes.byref(ob), 4, 4) == -1
+    assert lib.eshkol_gpu_softmax_f64(ctypes.byref(hb), ctypes.byref(ob), 4, 4) == -1
+    assert lib.eshkol_gpu_normalize_f64(ctypes.byref(hb), ctypes.byref(ob), 4, 4, 1.0, 0.0, 1e-5) == -1
+    assert lib.eshkol_gpu_batchnorm_backward_f64(*([ctypes.byref(hb)] * 5 + [ctypes.byref(ob)] * 3), 4, 4) == -1
+    assert lib.eshkol_gpu_layernorm_backward_f64(*([ctypes.byref(hb)] * 5 + [ctypes.byref(ob)]), 4, 4) == -1
+    assert lib.eshkol_b200_reduce_f64_device(a.ctypes.data, out.ctypes.data, 16, 0) == -1
+    assert lib.eshkol_b200_softmax_f64_device(a.ctypes.data, out.ctypes.data, 4, 4) == -1
+    assert lib.eshkol_b200_transpose_f64_device(a.ctypes.data, out.ctypes.data, 4, 4) == -1
+    assert (out == 7.0).all()
