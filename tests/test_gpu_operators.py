@@ -14,13 +14,19 @@ pytestmark = pytest.mark.gpu
 
 
 def dev(x):
+    """x on the device, complete before the library's own (non-blocking) stream may read it"""
     import torch
-    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    t = torch.from_numpy(np.ascontiguousarray(x)).cuda()
+    torch.cuda.synchronize()
+    return t
 
 
 def empty(shape):
+    """NaN-filled output, the fill complete before the library's stream writes into it"""
     import torch
-    return torch.full(tuple(shape), float("nan"), dtype=torch.float64, device="cuda")
+    t = torch.full(tuple(shape), float("nan"), dtype=torch.float64, device="cuda")
+    torch.cuda.synchronize()
+    return t
 
 
 def done():
