@@ -212,3 +212,18 @@ def test_calls_fail_loudly_without_a_device():
     assert lib.eshkol_b200_softmax_f64_device(a.ctypes.data, out.ctypes.data, 4, 4) == -1
     assert lib.eshkol_b200_transpose_f64_device(a.ctypes.data, out.ctypes.data, 4, 4) == -1
     assert (out == 7.0).all()
+
+
+def test_public_headers_are_plain_c(tmp_path):
+    """Every header under include/ compiles as C99 on its own (the hosts are C programs)."""
+    import glob
+    import shutil
+    import subprocess
+    if shutil.which("gcc") is None:
+        pytest.skip("no C compiler")
+    for h in sorted(glob.glob(os.path.join(ROOT, "include", "*.h"))):
+        src = tmp_path / (os.path.basename(h) + ".c")
+        src.write_text(f'#include "{h}"\nint main(void) {{ return 0; }}\n')
+        r = subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-Werror", "-fsyntax-only", str(src)],
+                           capture_output=True, text=True)
+        assert r.returncode == 0, h + "\n" + r.stderr
