@@ -197,6 +197,8 @@ def load_library() -> ctypes.CDLL:
     sig("eshkol_b200_debug_rendezvous", ctypes.c_int, [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                                        ctypes.c_int, ctypes.c_double])
     sig("eshkol_b200_debug_fail_allocation", None, [ctypes.c_int])
+    sig("eshkol_b200_debug_sharded_plan", ctypes.c_int, [u64, ctypes.c_int, ctypes.c_int, ctypes.c_double, ctypes.c_int]
+        + [ctypes.POINTER(u64)] * 4)
     sig("eshkol_b200_debug_fetch", ctypes.c_int, [ctypes.c_int, ctypes.c_int, vp, u64, ctypes.POINTER(u64)])
     sig("eshkol_b200_debug_choose_tier", None, [u64, u64, u64, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)])
     _lib = lib

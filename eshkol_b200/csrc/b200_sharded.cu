@@ -456,6 +456,28 @@ int eshkol_b200_debug_rendezvous(const char* name, int rank, int world, int barr
   return rc;
 }
 
+// Tests only, no GPU: the plan a session of this shape would follow -- the column panels
+// (first column and width of each, at most `capacity`) and, per panel, every rank's share of
+// its columns (first[p * world + r], count[p * world + r]).  Returns the number of panels.
+int eshkol_b200_debug_sharded_plan(uint64_t N, int world, int src, double src_weight, int capacity,
+                                   uint64_t* col0, uint64_t* width, uint64_t* first, uint64_t* count) {
+  if (!col0 || !width || !first || !count || world < 1 || world > kMaxRanks || src < 0 || src >= world || N == 0)
+    return -1;
+  long long c0[kMaxPanels], wd[kMaxPanels], f[kMaxRanks], n[kMaxRanks];
+  const int P = make_panels(static_cast<long long>(N), c0, wd);
+  if (P > capacity) return -1;
+  for (int p = 0; p < P; ++p) {
+    col0[p] = static_cast<uint64_t>(c0[p]);
+    width[p] = static_cast<uint64_t>(wd[p]);
+    column_shares(wd[p], world, src, src_weight, f, n);
+    for (int r = 0; r < world; ++r) {
+      first[p * world + r] = static_cast<uint64_t>(f[r]);
+      count[p * world + r] = static_cast<uint64_t>(n[r]);
+    }
+  }
+  return P;
+}
+
 int eshkol_b200_sharded_rows(const EshkolB200Sharded* s, uint64_t* row0, uint64_t* rows) {
   if (!s) return -1;
   if (row0) *row0 = static_cast<uint64_t>(s->row0[s->rank]);

@@ -46,6 +46,13 @@ void eshkol_b200_debug_withhold_arrival(int on);
  * -1, or NaN from a void dispatcher -- and the library must stay usable. */
 void eshkol_b200_debug_fail_allocation(int nth);
 
+/* Tests only, no GPU: the plan a multi-GPU session of N columns would follow -- its column
+ * panels (first column, width; at most `capacity` of them) and every rank's share of each
+ * panel's columns (first[p * world + r], count[p * world + r]) when the source rank's share is
+ * src_weight of the others'.  Returns the number of panels, -1 on bad arguments. */
+int eshkol_b200_debug_sharded_plan(uint64_t N, int world, int src, double src_weight, int capacity,
+                                   uint64_t* col0, uint64_t* width, uint64_t* first, uint64_t* count);
+
 /* Tests only: the rendezvous and the host barriers of a multi-GPU session
  * (eshkol_b200_multi.h) without any GPU work.  Every rank runs `barriers` barriers; a rank given
  * fail_at = k marks the session failed instead of entering barrier k, a rank given leave_at = k

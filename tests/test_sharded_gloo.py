@@ -162,3 +162,24 @@ def test_column_shares_cover_the_panel_and_lighten_the_source():
                 assert abs(parts[src][1] - others[0]) <= 1
             if 0.0 < w < 1.0 and width >= 64 * world:
                 assert abs(parts[src][1] - w * others[0]) <= 1 + w
+
+
+def test_the_c_driver_and_the_python_driver_follow_the_same_plan():
+    """The schedule exists twice, in C (b200_sharded.cu) and over torch.distributed (sharded.py):
+    both cut B into the same column panels and give every rank the same share of each."""
+    import ctypes
+    import eshkol_b200 as eb
+    from eshkol_b200.sharded import column_shares, panel_columns
+    lib = eb.load_library()
+    u64 = ctypes.c_uint64
+    for N, world, src, w in [(32768, 8, 0, 0.5), (32768, 4, 0, 0.5), (32768, 2, 1, 1.0), (8192, 8, 3, 0.0),
+                             (16384, 4, 0, 0.25), (1000, 4, 0, 0.5), (4096, 1, 0, 0.5)]:
+        col0, width = (u64 * 24)(), (u64 * 24)()
+        first, count = (u64 * (24 * world))(), (u64 * (24 * world))()
+        P = lib.eshkol_b200_debug_sharded_plan(N, world, src, w, 24, col0, width, first, count)
+        want = panel_columns(N, 4, "gentle")
+        assert P == len(want), (N, world)
+        assert [(int(col0[p]), int(width[p])) for p in range(P)] == want
+        for p, (_, wd) in enumerate(want):
+            shares = column_shares(wd, world, src, w)
+            assert [(int(first[p * world + r]), int(count[p * world + r])) for r in range(world)] == shares
